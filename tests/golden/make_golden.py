@@ -1,0 +1,130 @@
+"""Generate tests/golden/*.npz by running the UPSTREAM modules on CPU.
+
+Usage:  python tests/golden/make_golden.py            (needs an upstream checkout;
+        see oracle/ref_shim.py for where it is looked up)
+
+For every case of oracle/cases.py (parity grid, config 0, a small GeGLU case)
+this builds the upstream MoeficationMoE + MoeficationRouter, loads the seeded
+tensors into it, runs forward in 'dynk_max' mode with the experts in 'masked'
+(dense) and 'naive' (sparse loop) modes, and stores what the upstream code
+returned: router scores, the 0/1 routing tensor (bit-packed) and the output
+(all rows for small cases, an evenly strided row subset for large ones),
+together with digests of the seeded inputs so that a drifting random generator
+is detected instead of being reported as a parity failure.
+"""
+from __future__ import annotations
+
+import sys
+from pathlib import Path
+
+import numpy as np
+import torch
+
+ROOT = Path(__file__).resolve().parents[2]
+sys.path.insert(0, str(ROOT))
+
+from oracle import cases as C                      # noqa: E402
+from oracle import d2d_oracle as O                 # noqa: E402
+from oracle.ref_shim import load_reference         # noqa: E402
+
+ACT = {"relu": torch.nn.ReLU, "gelu": torch.nn.GELU, "tanh": torch.nn.Tanh,
+       "leaky_relu": torch.nn.LeakyReLU}
+MAX_OUT_ELEMS = 32768
+
+
+class _FixedScores(torch.nn.Module):
+    """Router stand-in returning a given score tensor (the mechanism upstream's own
+    override hook uses, architectures/moe/moefication.py:331-339)."""
+
+    def __init__(self, s):
+        super().__init__()
+        self.s = s
+
+    def forward(self, x):
+        return self.s
+
+
+def glu_case() -> C.LayerCase:
+    return C.LayerCase("glu_small", 2, 17, 64, 32, 8, tau=0.4, act="gelu", glu=True,
+                       norm="rms")
+
+
+def glu_case_bf16() -> C.LayerCase:
+    return C.LayerCase("glu_small_bf16", 2, 65, 128, 64, 16, tau=0.4, act="gelu", glu=True,
+                       norm="rms", dtype="bf16")
+
+
+def all_cases():
+    return C.parity_grid() + [C.config0(), glu_case(), glu_case_bf16()]
+
+
+def build_reference_module(ref, c: C.LayerCase, t: dict):
+    dt = c.torch_dtype
+    if c.glu:
+        moe = ref.MoeficationMoE(c.name, c.d, c.E, False, c.H, ACT[c.act],
+                                 experts_class="execute_all", add_intermediate_gating=True)
+        sd = {"experts.layers.0.w": t["w1"], "experts.layers.1.w": t["w2"],
+              "experts.layers.2.w": t["w_up"]}
+    else:
+        moe = ref.MoeficationMoE(c.name, c.d, c.E, True, c.H, ACT[c.act],
+                                 experts_class="custom_kernel",
+                                 add_residual_connection=c.residual)
+        sd = {"experts.w1": t["w1"], "experts.b1": t["b1"], "experts.w2": t["w2"],
+              "last_bias": t["last_bias"]}
+    moe.router = ref.MoeficationRouter(c.d, c.E, width=c.R, depth=2, bias=False,
+                                       activation="relu", output_activation="abs")
+    sd["router.layers.0.weight"] = t["wa"]
+    sd["router.layers.2.weight"] = t["wb"]
+    moe = moe.to(dt)
+    moe.load_state_dict(sd, strict=True)
+    if c.score_override:
+        moe.router = _FixedScores(t["scores"])
+    moe.forward_mode = "dynk_max"
+    moe.tau = c.tau
+    moe.eval()
+    return moe
+
+
+@torch.no_grad()
+def run_case(ref, c: C.LayerCase) -> dict:
+    t = C.make_tensors(c)
+    moe = build_reference_module(ref, c, t)
+    scores = moe.router(t["x"])
+    rec = {"dtype": c.dtype, "N": c.N, "d": c.d, "E": c.E,
+           "dg_x": C.digest(t["x"]), "dg_w1": C.digest(t["w1"]), "dg_wa": C.digest(t["wa"]),
+           "scores": scores.float().reshape(c.N, c.E).numpy()}
+    outs = {}
+    modes = ["execute_all"] if c.glu else ["masked", "naive"]
+    for mode in modes:
+        if not c.glu:
+            moe.experts.forward_mode = mode
+        out, gd = moe(t["x"])
+        rt = gd[c.name][0]
+        assert rt.dtype == scores.dtype and rt.shape == (c.B, c.S, c.E)
+        outs[mode] = out.float().reshape(c.N, c.d)
+        rec["mask_bits"] = O.pack_mask(rt.reshape(c.N, c.E) > 0)
+    stride = max(1, -(-c.N * c.d // MAX_OUT_ELEMS))
+    rows = np.arange(0, c.N, stride, dtype=np.int64)
+    rec["rows"] = rows
+    for mode, o in outs.items():
+        rec[f"out_{mode}"] = o[rows].numpy()
+        rec[f"sum_{mode}"] = np.float64(o.double().sum().item())
+    return rec
+
+
+def main():
+    ref = load_reference()
+    if ref is None:
+        raise SystemExit("no upstream checkout found (set D2DMOE_REFERENCE_ROOT)")
+    torch.set_num_threads(8)
+    outdir = Path(__file__).resolve().parent
+    for c in all_cases():
+        rec = run_case(ref, c)
+        np.savez_compressed(outdir / f"{c.name}.npz", **rec)
+        k = O.unpack_mask(rec["mask_bits"], c.E).sum().item() / c.N
+        print(f"{c.name:24s} N={c.N:5d} d={c.d:4d} E={c.E:3d} {c.dtype} mean_k={k:.2f} "
+              f"rows_saved={len(rec['rows'])}")
+
+
+if __name__ == "__main__":
+    main()
