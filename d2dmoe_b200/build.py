@@ -1,0 +1,83 @@
+"""Build the CUDA library in-tree with nvcc for sm_100a.
+
+    python -m d2dmoe_b200.build        # -> d2dmoe_b200/_lib/libd2dmoe_b200.so
+
+nvcc cross-compiles without a GPU.  The library links the static CUDA runtime, so
+it needs nothing but the driver at load time.
+"""
+from __future__ import annotations
+
+import hashlib
+import os
+import shutil
+import subprocess
+import sys
+from pathlib import Path
+
+PKG = Path(__file__).resolve().parent
+CSRC = PKG / "csrc"
+LIBDIR = PKG / "_lib"
+LIB = LIBDIR / "libd2dmoe_b200.so"
+STAMP = LIBDIR / "build.stamp"
+
+NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
+              "-Xcompiler", "-fPIC"]
+
+
+def _nvcc() -> str:
+    for c in (os.environ.get("NVCC"), shutil.which("nvcc"), "/usr/local/cuda/bin/nvcc"):
+        if c and Path(c).exists():
+            return c
+    raise RuntimeError("nvcc not found: set NVCC or put it on PATH")
+
+
+def sources() -> list[Path]:
+    return sorted(CSRC.glob("*.cu"))
+
+
+def _digest() -> str:
+    h = hashlib.sha256()
+    for p in sorted(list(CSRC.glob("*.cu")) + list(CSRC.glob("*.cuh")) +
+                    [PKG.parent / "include" / "d2dmoe.h"]):
+        h.update(p.name.encode())
+        h.update(p.read_bytes())
+    h.update(" ".join(NVCC_FLAGS).encode())
+    return h.hexdigest()
+
+
+def is_current() -> bool:
+    return LIB.exists() and STAMP.exists() and STAMP.read_text().strip() == _digest()
+
+
+def build(force: bool = False, verbose: bool = False) -> Path:
+    """Compile csrc/*.cu into one shared library; a no-op when sources are unchanged."""
+    if not force and is_current():
+        return LIB
+    LIBDIR.mkdir(exist_ok=True)
+    objs = []
+    procs = []
+    for src in sources():
+        obj = LIBDIR / (src.stem + ".o")
+        cmd = [_nvcc()] + NVCC_FLAGS + ["-c", str(src), "-o", str(obj)]
+        if verbose:
+            cmd[1:1] = ["-Xptxas", "-v"]
+        procs.append((src, subprocess.Popen(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT,
+                                            text=True)))
+        objs.append(obj)
+    failed = False
+    for src, p in procs:
+        out, _ = p.communicate()
+        if p.returncode != 0 or verbose:
+            sys.stderr.write(f"--- {src.name}\n{out}\n")
+        failed |= p.returncode != 0
+    if failed:
+        raise RuntimeError("nvcc failed")
+    link = [_nvcc(), "-gencode", "arch=compute_100a,code=sm_100a", "-shared",
+            "-Xcompiler", "-fPIC", "-o", str(LIB)] + [str(o) for o in objs]
+    subprocess.run(link, check=True)
+    STAMP.write_text(_digest())
+    return LIB
+
+
+if __name__ == "__main__":
+    print(build(force="--force" in sys.argv, verbose="-v" in sys.argv))

@@ -1,0 +1,177 @@
+// extern "C" entry points declared in include/d2dmoe.h: argument validation and
+// dispatch to the kernels.  No device memory is allocated here and no call
+// synchronises with the host.
+#include "d2d_common.cuh"
+#include "d2d_umma_api.cuh"
+
+using namespace d2d;
+
+namespace {
+
+inline bool aligned(const void* p, size_t a) { return (reinterpret_cast<uintptr_t>(p) % a) == 0; }
+inline bool dtype_ok(int dt) { return dt == D2D_F32 || dt == D2D_BF16; }
+
+inline size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
+
+}  // namespace
+
+extern "C" {
+
+int d2d_abi_version(void) { return D2D_ABI_VERSION; }
+
+const char* d2d_strerror(int status) {
+  switch (status) {
+    case D2D_OK: return "ok";
+    case D2D_ERR_BAD_ARG: return "bad argument (null pointer, negative size or misaligned buffer)";
+    case D2D_ERR_UNSUPPORTED: return "shape or dtype not supported by the kernels";
+    case D2D_ERR_LAUNCH: return "CUDA launch failed";
+    case D2D_ERR_WORKSPACE: return "workspace too small (see d2d_workspace_bytes)";
+    case D2D_ERR_INDEX_RANGE: return "device: token index or offset out of range";
+    case D2D_ERR_TIMEOUT: return "device: bounded wait ran out";
+    case D2D_ERR_NO_DEVICE: return "no sm_100 CUDA device is current";
+    default: return "unknown status";
+  }
+}
+
+int d2d_workspace_bytes(int64_t n_max, int E, size_t* bytes) {
+  if (!bytes || n_max < 0 || E < 1) return D2D_ERR_BAD_ARG;
+  *bytes = align_up(compact_workspace_bytes(n_max, E), 256);
+  return D2D_OK;
+}
+
+int d2d_router_mask(const void* x, const void* wa, const void* wb, const void* router_packed_opt,
+                    float thresh_mult, uint32_t* mask_bits, void* scores_opt,
+                    const void* last_bias_opt, int add_residual, void* out_init_opt, int64_t N,
+                    int d, int R, int E, int dtype, int* dev_status, d2d_stream_t stream) {
+  if (!x || !wa || !wb || !mask_bits || N < 0 || d < 1 || R < 1 || E < 1) return D2D_ERR_BAD_ARG;
+  if (!dtype_ok(dtype)) return D2D_ERR_UNSUPPORTED;
+  if (N == 0) return D2D_OK;
+  cudaStream_t s = (cudaStream_t)stream;
+  if (router_packed_opt && umma_router_supported(d, R, E, dtype))
+    return launch_router_mask_umma(x, router_packed_opt, thresh_mult, mask_bits, scores_opt,
+                                   last_bias_opt, add_residual, out_init_opt, N, d, R, E,
+                                   dev_status, s);
+  return launch_router_mask_simt(x, wa, wb, thresh_mult, mask_bits, scores_opt, last_bias_opt,
+                                 add_residual, out_init_opt, N, d, R, E, dtype, dev_status, s);
+}
+
+int d2d_mask_from_scores(const void* scores, float thresh_mult, uint32_t* mask_bits, int64_t N,
+                         int E, int dtype, int* dev_status, d2d_stream_t stream) {
+  if (!scores || !mask_bits || N < 0 || E < 1) return D2D_ERR_BAD_ARG;
+  if (!dtype_ok(dtype)) return D2D_ERR_UNSUPPORTED;
+  if (N == 0) return D2D_OK;
+  return launch_mask_from_scores(scores, thresh_mult, mask_bits, N, E, dtype, dev_status,
+                                 (cudaStream_t)stream);
+}
+
+int d2d_init_out(const void* x, const void* last_bias_opt, int add_residual, void* out, int64_t N,
+                 int d, int dtype, d2d_stream_t stream) {
+  if (!out || N < 0 || d < 1 || (add_residual && !x)) return D2D_ERR_BAD_ARG;
+  if (!dtype_ok(dtype)) return D2D_ERR_UNSUPPORTED;
+  if (N == 0) return D2D_OK;
+  return launch_init_out(x, last_bias_opt, add_residual, out, N, d, dtype, (cudaStream_t)stream);
+}
+
+int d2d_expand_mask(const uint32_t* mask_bits, void* routing_tensor, int64_t N, int E, int dtype,
+                    d2d_stream_t stream) {
+  if (!mask_bits || !routing_tensor || N < 0 || E < 1) return D2D_ERR_BAD_ARG;
+  if (!dtype_ok(dtype)) return D2D_ERR_UNSUPPORTED;
+  if (N == 0) return D2D_OK;
+  return launch_expand_mask(mask_bits, routing_tensor, N, E, dtype, (cudaStream_t)stream);
+}
+
+int d2d_pack_mask(const void* routing_tensor, uint32_t* mask_bits, int64_t N, int E, int dtype,
+                  d2d_stream_t stream) {
+  if (!mask_bits || !routing_tensor || N < 0 || E < 1) return D2D_ERR_BAD_ARG;
+  if (!dtype_ok(dtype)) return D2D_ERR_UNSUPPORTED;
+  if (N == 0) return D2D_OK;
+  return launch_pack_mask(routing_tensor, mask_bits, N, E, dtype, (cudaStream_t)stream);
+}
+
+int d2d_compact(const uint32_t* mask_bits, int32_t* token_idx, int32_t* offsets, int64_t N, int E,
+                void* ws, size_t ws_bytes, int* dev_status, d2d_stream_t stream) {
+  if (!mask_bits || !token_idx || !offsets || !ws || N < 0 || E < 1) return D2D_ERR_BAD_ARG;
+  if (!aligned(ws, 16)) return D2D_ERR_BAD_ARG;
+  if (ws_bytes < compact_workspace_bytes(N, E)) return D2D_ERR_WORKSPACE;
+  return launch_compact(mask_bits, token_idx, offsets, N, E, (int32_t*)ws, dev_status,
+                        (cudaStream_t)stream);
+}
+
+int d2d_experts_ffn(const void* x, const int32_t* token_idx, const int32_t* offsets,
+                    const void* w1, const void* b1_opt, const void* w_up_opt, const void* w2,
+                    const void* experts_packed_opt, const void* last_bias_opt, int add_residual,
+                    int accumulate, void* out, int64_t N, int d, int E, int H, int act, int dtype,
+                    int* dev_status, d2d_stream_t stream) {
+  if (!x || !token_idx || !offsets || !w1 || !w2 || !out || N < 0 || d < 1 || E < 1 || H < 1)
+    return D2D_ERR_BAD_ARG;
+  if (!dtype_ok(dtype) || act < D2D_RELU || act > D2D_GELU_TANH) return D2D_ERR_UNSUPPORTED;
+  if (!aligned(out, 16) || !aligned(x, 16)) return D2D_ERR_BAD_ARG;
+  if (N == 0) return D2D_OK;
+  cudaStream_t s = (cudaStream_t)stream;
+  if (!accumulate) {
+    int rc = launch_init_out(x, last_bias_opt, add_residual, out, N, d, dtype, s);
+    if (rc != D2D_OK) return rc;
+  }
+  if (experts_packed_opt && umma_experts_supported(d, E, H, w_up_opt != nullptr, dtype))
+    return launch_experts_umma(x, token_idx, offsets, experts_packed_opt, out, N, d, E, H,
+                               w_up_opt != nullptr, act, dev_status, s);
+  return launch_experts_simt(x, token_idx, offsets, w1, b1_opt, w_up_opt, w2, out, N, d, E, H, act,
+                             dtype, dev_status, s);
+}
+
+int d2d_moe_forward(const void* x, const void* wa, const void* wb, const void* router_packed_opt,
+                    const void* scores_in_opt, float thresh_mult, const void* w1,
+                    const void* b1_opt, const void* w_up_opt, const void* w2,
+                    const void* experts_packed_opt, const void* last_bias_opt, int add_residual,
+                    void* out, uint32_t* mask_bits, int32_t* token_idx, int32_t* offsets,
+                    int64_t N, int d, int R, int E, int H, int act, int dtype, void* ws,
+                    size_t ws_bytes, int* dev_status, d2d_stream_t stream) {
+  int rc;
+  if (!wa && !scores_in_opt) return D2D_ERR_BAD_ARG;
+  if (N == 0) return D2D_OK;
+  if (scores_in_opt) {
+    rc = d2d_mask_from_scores(scores_in_opt, thresh_mult, mask_bits, N, E, dtype, dev_status,
+                              stream);
+    if (rc != D2D_OK) return rc;
+    rc = d2d_init_out(x, last_bias_opt, add_residual, out, N, d, dtype, stream);
+  } else {
+    rc = d2d_router_mask(x, wa, wb, router_packed_opt, thresh_mult, mask_bits, nullptr,
+                         last_bias_opt, add_residual, out, N, d, R, E, dtype, dev_status, stream);
+  }
+  if (rc != D2D_OK) return rc;
+  rc = d2d_compact(mask_bits, token_idx, offsets, N, E, ws, ws_bytes, dev_status, stream);
+  if (rc != D2D_OK) return rc;
+  return d2d_experts_ffn(x, token_idx, offsets, w1, b1_opt, w_up_opt, w2, experts_packed_opt,
+                         nullptr, 0, /*accumulate=*/1, out, N, d, E, H, act, dtype, dev_status,
+                         stream);
+}
+
+int d2d_prepack_experts_bytes(int d, int E, int H, int glu, int dtype, size_t* bytes) {
+  if (!bytes || d < 1 || E < 1 || H < 1) return D2D_ERR_BAD_ARG;
+  *bytes = umma_experts_supported(d, E, H, glu != 0, dtype) ? umma_experts_packed_bytes(d, E, H, glu != 0) : 0;
+  return D2D_OK;
+}
+
+int d2d_prepack_experts(const void* w1, const void* b1_opt, const void* w_up_opt, const void* w2,
+                        void* packed, int d, int E, int H, int dtype, d2d_stream_t stream) {
+  if (!w1 || !w2 || !packed) return D2D_ERR_BAD_ARG;
+  if (!umma_experts_supported(d, E, H, w_up_opt != nullptr, dtype)) return D2D_ERR_UNSUPPORTED;
+  if (!aligned(packed, 1024)) return D2D_ERR_BAD_ARG;
+  return launch_prepack_experts(w1, b1_opt, w_up_opt, w2, packed, d, E, H, (cudaStream_t)stream);
+}
+
+int d2d_prepack_router_bytes(int d, int R, int E, int dtype, size_t* bytes) {
+  if (!bytes || d < 1 || R < 1 || E < 1) return D2D_ERR_BAD_ARG;
+  *bytes = umma_router_supported(d, R, E, dtype) ? umma_router_packed_bytes(d, R, E) : 0;
+  return D2D_OK;
+}
+
+int d2d_prepack_router(const void* wa, const void* wb, void* packed, int d, int R, int E,
+                       int dtype, d2d_stream_t stream) {
+  if (!wa || !wb || !packed) return D2D_ERR_BAD_ARG;
+  if (!umma_router_supported(d, R, E, dtype)) return D2D_ERR_UNSUPPORTED;
+  if (!aligned(packed, 1024)) return D2D_ERR_BAD_ARG;
+  return launch_prepack_router(wa, wb, packed, d, R, E, (cudaStream_t)stream);
+}
+
+}  // extern "C"

@@ -1,0 +1,166 @@
+// Bit mask -> per-expert token lists + offsets (warp-ballot / prefix-sum compaction).
+//
+// Replaces the upstream index preparation (architectures/moe/moe_layers.py:241-249:
+// int32 cast of the routing tensor, argsort along the token dimension, column sums).
+// The sort only serves to bring each expert's tokens to the front of its column;
+// a compaction gives the same set per expert, here in ascending token order.
+//
+// Two launches over chunks of 1024 tokens:
+//   count   : counts[chunk][e] = tokens of the chunk that keep expert e
+//   scatter : every CTA rebuilds its base from the counts table (sum over earlier
+//             chunks + exclusive scan over experts) and writes its token indices.
+// Integer work, bit-exact by construction; HBM traffic is the mask (read twice)
+// plus 4 bytes per kept token-expert pair.
+#include "d2d_common.cuh"
+
+namespace d2d {
+namespace {
+
+constexpr int NT = 256;
+constexpr int ROWS = 32;                 // 32 rows of 32 tokens per CTA
+constexpr int CHUNK = ROWS * 32;
+constexpr int MAX_E = 256;
+
+__global__ void __launch_bounds__(NT)
+compact_count_kernel(const uint32_t* __restrict__ mask_bits, int32_t* __restrict__ counts,
+                     int64_t N, int E) {
+  __shared__ int cnt[MAX_E];
+  const int tid = threadIdx.x, lane = tid & 31, w = tid >> 5;
+  const int nw = (E + 31) / 32;
+  for (int e = tid; e < E; e += NT) cnt[e] = 0;
+  __syncthreads();
+  for (int r = 0; r < 4; ++r) {
+    const int64_t t = (int64_t)blockIdx.x * CHUNK + (4 * w + r) * 32 + lane;
+    for (int j = 0; j < nw; ++j) {
+      const uint32_t word = t < N ? mask_bits[t * nw + j] : 0u;
+      if (__ballot_sync(0xffffffffu, word != 0u) == 0u) continue;
+      const int nb = min(32, E - 32 * j);
+      for (int b = 0; b < nb; ++b) {
+        const uint32_t v = __ballot_sync(0xffffffffu, (word >> b) & 1u);
+        if (lane == 0 && v) atomicAdd(&cnt[32 * j + b], __popc(v));
+      }
+    }
+  }
+  __syncthreads();
+  for (int e = tid; e < E; e += NT) counts[(int64_t)blockIdx.x * E + e] = cnt[e];
+}
+
+__global__ void __launch_bounds__(NT)
+compact_scatter_kernel(const uint32_t* __restrict__ mask_bits, const int32_t* __restrict__ counts,
+                       int32_t* __restrict__ token_idx, int32_t* __restrict__ offsets, int64_t N,
+                       int E, int nchunks, int* dev_status) {
+  extern __shared__ int sm[];
+  int* cnt = sm;                 // [ROWS][E] -> becomes each row's write base
+  int* tot = cnt + ROWS * E;     // [E]   total per expert, then exclusive offsets
+  int* pre = tot + E;            // [E]   tokens of expert e in earlier chunks
+  const int tid = threadIdx.x, lane = tid & 31, w = tid >> 5;
+  const int nw = (E + 31) / 32;
+  const int chunk = blockIdx.x;
+
+  for (int i = tid; i < ROWS * E; i += NT) cnt[i] = 0;
+  for (int e = tid; e < E; e += NT) {
+    int a = 0, b = 0;
+    for (int c = 0; c < nchunks; ++c) {
+      const int v = counts[(int64_t)c * E + e];
+      if (c < chunk) b += v;
+      a += v;
+    }
+    tot[e] = a;
+    pre[e] = b;
+  }
+  __syncthreads();
+  // per-row popcounts of this chunk
+  for (int r = 0; r < 4; ++r) {
+    const int row = 4 * w + r;
+    const int64_t t = (int64_t)chunk * CHUNK + row * 32 + lane;
+    for (int j = 0; j < nw; ++j) {
+      const uint32_t word = t < N ? mask_bits[t * nw + j] : 0u;
+      if (__ballot_sync(0xffffffffu, word != 0u) == 0u) continue;
+      const int nb = min(32, E - 32 * j);
+      for (int b = 0; b < nb; ++b) {
+        const uint32_t v = __ballot_sync(0xffffffffu, (word >> b) & 1u);
+        if (lane == 0) cnt[row * E + 32 * j + b] = __popc(v);
+      }
+    }
+  }
+  // exclusive scan of the expert totals (E <= 256: one warp, 8 values per lane)
+  if (w == 0) {
+    int v[8], s = 0;
+    for (int k = 0; k < 8; ++k) {
+      const int e = lane * 8 + k;
+      v[k] = e < E ? tot[e] : 0;
+      s += v[k];
+    }
+    int incl = s;
+    for (int o = 1; o < 32; o <<= 1) {
+      const int n = __shfl_up_sync(0xffffffffu, incl, o);
+      if (lane >= o) incl += n;
+    }
+    int run = incl - s;
+    for (int k = 0; k < 8; ++k) {
+      const int e = lane * 8 + k;
+      if (e < E) tot[e] = run;
+      run += v[k];
+    }
+    if (lane == 31) {
+      if (chunk == 0) offsets[E] = incl;
+      if ((int64_t)incl > N * (int64_t)E) report(dev_status, D2D_ERR_INDEX_RANGE);
+    }
+  }
+  __syncthreads();
+  for (int e = tid; e < E; e += NT) {
+    if (chunk == 0) offsets[e] = tot[e];
+    int run = tot[e] + pre[e];
+    for (int row = 0; row < ROWS; ++row) {
+      const int c = cnt[row * E + e];
+      cnt[row * E + e] = run;
+      run += c;
+    }
+  }
+  __syncthreads();
+  for (int r = 0; r < 4; ++r) {
+    const int row = 4 * w + r;
+    const int64_t t = (int64_t)chunk * CHUNK + row * 32 + lane;
+    for (int j = 0; j < nw; ++j) {
+      const uint32_t word = t < N ? mask_bits[t * nw + j] : 0u;
+      if (__ballot_sync(0xffffffffu, word != 0u) == 0u) continue;
+      const int nb = min(32, E - 32 * j);
+      for (int b = 0; b < nb; ++b) {
+        const uint32_t bit = (word >> b) & 1u;
+        const uint32_t v = __ballot_sync(0xffffffffu, bit);
+        if (bit) {
+          const int rank = __popc(v & ((1u << lane) - 1u));
+          token_idx[cnt[row * E + 32 * j + b] + rank] = (int32_t)t;
+        }
+      }
+    }
+  }
+}
+
+}  // namespace
+
+size_t compact_workspace_bytes(int64_t n_max, int E) {
+  const int64_t nchunks = ceil_div64(n_max > 0 ? n_max : 1, CHUNK);
+  return (size_t)nchunks * (size_t)E * sizeof(int32_t);
+}
+
+int launch_compact(const uint32_t* mask_bits, int32_t* token_idx, int32_t* offsets, int64_t N,
+                   int E, int32_t* counts_ws, int* dev_status, cudaStream_t s) {
+  if (E > MAX_E || E < 1) return D2D_ERR_UNSUPPORTED;
+  if (N * (int64_t)E > 0x7fffffffLL) return D2D_ERR_UNSUPPORTED;   // int32 offsets
+  const int64_t nchunks = ceil_div64(N > 0 ? N : 1, CHUNK);
+  compact_count_kernel<<<(unsigned)nchunks, NT, 0, s>>>(mask_bits, counts_ws, N, E);
+  if (cudaGetLastError() != cudaSuccess) return D2D_ERR_LAUNCH;
+  const size_t smem = sizeof(int) * ((size_t)ROWS * E + 2 * (size_t)E);
+  if (smem > 48 * 1024) {
+    if (cudaFuncSetAttribute(compact_scatter_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             (int)smem) != cudaSuccess)
+      return D2D_ERR_LAUNCH;
+  }
+  compact_scatter_kernel<<<(unsigned)nchunks, NT, smem, s>>>(mask_bits, counts_ws, token_idx,
+                                                             offsets, N, E, (int)nchunks,
+                                                             dev_status);
+  return cudaGetLastError() == cudaSuccess ? D2D_OK : D2D_ERR_LAUNCH;
+}
+
+}  // namespace d2d

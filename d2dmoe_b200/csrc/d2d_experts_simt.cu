@@ -1,0 +1,224 @@
+// Grouped expert FFN with fused scatter-add, general-shape FFMA kernel.
+//
+// Serves fp32 (where the upstream kernels forbid TF32,
+// architectures/moe/moe_impls.py:153,288, so the products must be true fp32) and
+// every shape the tensor-core kernel does not cover (d or H not a multiple of 16,
+// H > 128, ...).  One work item = (expert e, 32 rows of its token list):
+//   h   = act(T(x[rows] W1[e]) + b1[e])   (* T(x[rows] W_up[e]) for the gated form)
+//   out[rows] += T(h W2[e])               vector red.global.add in T
+// which fuses architectures/moe/moe_impls.py:93-180 (first layer) and :244-301
+// (second layer + atomic add); the [32, H] hidden tile lives in shared memory.
+#include "d2d_common.cuh"
+
+namespace d2d {
+namespace {
+
+constexpr int NT = 256;
+constexpr int TM = 32;        // rows per work item
+constexpr int KC = 32;        // k-chunk
+constexpr int XP = KC + 4;    // padded x row
+constexpr int CB = 128;       // output columns per pass (4 per lane)
+constexpr int WP = CB + 4;    // padded weight row
+constexpr int MAX_E = 256;
+
+template <typename T, bool GLU>
+__global__ void __launch_bounds__(NT)
+experts_simt_kernel(const T* __restrict__ x, const int32_t* __restrict__ token_idx,
+                    const int32_t* __restrict__ offsets, const T* __restrict__ w1,
+                    const T* __restrict__ b1, const T* __restrict__ w_up,
+                    const T* __restrict__ w2, T* __restrict__ out, int64_t N, int d, int E, int H,
+                    int act, int* dev_status) {
+  extern __shared__ float sm[];
+  float* xs = sm;                              // [TM][XP]
+  float* ws = xs + TM * XP;                    // [KC][WP]
+  float* wu = ws + KC * WP;                    // [KC][WP] (gated form only)
+  float* hs = wu + (GLU ? KC * WP : 0);        // [TM][HP]
+  const int HP = ((H + 3) & ~3) + 4;
+  __shared__ int tstart[MAX_E + 1];
+  __shared__ int rows[TM];
+  const int tid = threadIdx.x, lane = tid & 31, ty = tid >> 5;
+
+  if (tid == 0) {
+    int run = 0;
+    for (int e = 0; e < E; ++e) {
+      tstart[e] = run;
+      const int c = offsets[e + 1] - offsets[e];
+      if (c < 0) { report(dev_status, D2D_ERR_INDEX_RANGE); }
+      run += c > 0 ? (c + TM - 1) / TM : 0;
+    }
+    tstart[E] = run;
+  }
+  __syncthreads();
+  const int total = tstart[E];
+  const bool vec_ok = (d % 4 == 0);
+
+  for (int tile = blockIdx.x; tile < total; tile += gridDim.x) {
+    int lo = 0, hi = E;                 // last e with tstart[e] <= tile
+    while (hi - lo > 1) {
+      const int mid = (lo + hi) >> 1;
+      if (tstart[mid] <= tile) lo = mid; else hi = mid;
+    }
+    const int e = lo;
+    const int r0 = offsets[e] + (tile - tstart[e]) * TM;
+    const int nrows = min(TM, offsets[e + 1] - r0);
+    __syncthreads();
+    if (tid < TM) {
+      int t = tid < nrows ? token_idx[r0 + tid] : -1;
+      if (tid < nrows && (t < 0 || t >= N)) { report(dev_status, D2D_ERR_INDEX_RANGE); t = -1; }
+      rows[tid] = t;
+    }
+    __syncthreads();
+    const T* w1e = w1 + (int64_t)e * d * H;
+    const T* wue = GLU ? w_up + (int64_t)e * d * H : nullptr;
+    const T* w2e = w2 + (int64_t)e * H * d;
+
+    // ---- first layer: hs = act(x W1 + b1) (* x W_up) ------------------------
+    for (int hc = 0; hc < H; hc += CB) {
+      float acc[4][4], accu[4][4];
+#pragma unroll
+      for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) { acc[i][j] = 0.f; accu[i][j] = 0.f; }
+      for (int kc = 0; kc < d; kc += KC) {
+        __syncthreads();
+        for (int i = tid; i < TM * KC; i += NT) {
+          const int r = i / KC, k = i % KC;
+          const int t = rows[r];
+          xs[r * XP + k] = (t >= 0 && kc + k < d) ? DT<T>::to_f(x[(int64_t)t * d + kc + k]) : 0.f;
+        }
+        for (int i = tid; i < KC * CB; i += NT) {
+          const int k = i / CB, c = i % CB;
+          const bool ok = (kc + k < d) && (hc + c < H);
+          ws[k * WP + c] = ok ? DT<T>::to_f(w1e[(int64_t)(kc + k) * H + hc + c]) : 0.f;
+          if (GLU) wu[k * WP + c] = ok ? DT<T>::to_f(wue[(int64_t)(kc + k) * H + hc + c]) : 0.f;
+        }
+        __syncthreads();
+#pragma unroll
+        for (int k4 = 0; k4 < KC; k4 += 4) {
+          float4 xa[4];
+#pragma unroll
+          for (int i = 0; i < 4; ++i)
+            xa[i] = *reinterpret_cast<const float4*>(&xs[(4 * ty + i) * XP + k4]);
+#pragma unroll
+          for (int kk = 0; kk < 4; ++kk) {
+            const float4 wv = *reinterpret_cast<const float4*>(&ws[(k4 + kk) * WP + 4 * lane]);
+            float4 uv = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (GLU) uv = *reinterpret_cast<const float4*>(&wu[(k4 + kk) * WP + 4 * lane]);
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+              const float xv = kk == 0 ? xa[i].x : kk == 1 ? xa[i].y : kk == 2 ? xa[i].z : xa[i].w;
+              acc[i][0] = fmaf(xv, wv.x, acc[i][0]);
+              acc[i][1] = fmaf(xv, wv.y, acc[i][1]);
+              acc[i][2] = fmaf(xv, wv.z, acc[i][2]);
+              acc[i][3] = fmaf(xv, wv.w, acc[i][3]);
+              if (GLU) {
+                accu[i][0] = fmaf(xv, uv.x, accu[i][0]);
+                accu[i][1] = fmaf(xv, uv.y, accu[i][1]);
+                accu[i][2] = fmaf(xv, uv.z, accu[i][2]);
+                accu[i][3] = fmaf(xv, uv.w, accu[i][3]);
+              }
+            }
+          }
+        }
+      }
+#pragma unroll
+      for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const int c = hc + 4 * lane + j;
+          if (c < H) {
+            float h = DT<T>::round(acc[i][j]);
+            if (b1) h = DT<T>::round(h + DT<T>::to_f(b1[(int64_t)e * H + c]));
+            h = DT<T>::round(activate(h, act));
+            if (GLU) h = DT<T>::round(h * DT<T>::round(accu[i][j]));
+            hs[(4 * ty + i) * HP + c] = h;
+          }
+        }
+    }
+
+    // ---- second layer + scatter-add ----------------------------------------
+    for (int dc = 0; dc < d; dc += CB) {
+      float acc[4][4];
+#pragma unroll
+      for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) acc[i][j] = 0.f;
+      for (int kc = 0; kc < H; kc += KC) {
+        __syncthreads();
+        for (int i = tid; i < KC * CB; i += NT) {
+          const int k = i / CB, c = i % CB;
+          ws[k * WP + c] =
+              (kc + k < H && dc + c < d) ? DT<T>::to_f(w2e[(int64_t)(kc + k) * d + dc + c]) : 0.f;
+        }
+        __syncthreads();
+        const int kn = min(KC, H - kc);
+        for (int k = 0; k < kn; ++k) {
+          const float4 wv = *reinterpret_cast<const float4*>(&ws[k * WP + 4 * lane]);
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            const float hv = hs[(4 * ty + i) * HP + kc + k];
+            acc[i][0] = fmaf(hv, wv.x, acc[i][0]);
+            acc[i][1] = fmaf(hv, wv.y, acc[i][1]);
+            acc[i][2] = fmaf(hv, wv.z, acc[i][2]);
+            acc[i][3] = fmaf(hv, wv.w, acc[i][3]);
+          }
+        }
+      }
+      const int c0 = dc + 4 * lane;
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const int t = rows[4 * ty + i];
+        if (t < 0 || c0 >= d) continue;
+        T* o = out + (int64_t)t * d + c0;
+        if (vec_ok) {
+          red_add_v4(o, DT<T>::round(acc[i][0]), DT<T>::round(acc[i][1]),
+                     DT<T>::round(acc[i][2]), DT<T>::round(acc[i][3]));
+        } else {
+#pragma unroll
+          for (int j = 0; j < 4; ++j)
+            if (c0 + j < d) red_add_1(o + j, DT<T>::round(acc[i][j]));
+        }
+      }
+    }
+  }
+}
+
+template <typename T, bool GLU>
+int launch_t(const void* x, const int32_t* token_idx, const int32_t* offsets, const void* w1,
+             const void* b1, const void* w_up, const void* w2, void* out, int64_t N, int d, int E,
+             int H, int act, int* dev_status, cudaStream_t s) {
+  const int HP = ((H + 3) & ~3) + 4;
+  const size_t smem =
+      sizeof(float) * ((size_t)TM * XP + (size_t)KC * WP * (GLU ? 2 : 1) + (size_t)TM * HP);
+  if (smem > 200 * 1024) return D2D_ERR_UNSUPPORTED;
+  auto k = experts_simt_kernel<T, GLU>;
+  if (cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) !=
+      cudaSuccess)
+    return D2D_ERR_LAUNCH;
+  const int64_t max_tiles = ceil_div64(N * (int64_t)E, TM) + E;
+  const int grid = (int)(max_tiles < 148 * 4 ? (max_tiles > 0 ? max_tiles : 1) : 148 * 4);
+  k<<<grid, NT, smem, s>>>((const T*)x, token_idx, offsets, (const T*)w1, (const T*)b1,
+                           (const T*)w_up, (const T*)w2, (T*)out, N, d, E, H, act, dev_status);
+  return cudaGetLastError() == cudaSuccess ? D2D_OK : D2D_ERR_LAUNCH;
+}
+
+}  // namespace
+
+int launch_experts_simt(const void* x, const int32_t* token_idx, const int32_t* offsets,
+                        const void* w1, const void* b1, const void* w_up, const void* w2,
+                        void* out, int64_t N, int d, int E, int H, int act, int dtype,
+                        int* dev_status, cudaStream_t s) {
+  if (E > MAX_E) return D2D_ERR_UNSUPPORTED;
+  if (dtype == D2D_F32) {
+    return w_up ? launch_t<float, true>(x, token_idx, offsets, w1, b1, w_up, w2, out, N, d, E, H,
+                                        act, dev_status, s)
+                : launch_t<float, false>(x, token_idx, offsets, w1, b1, w_up, w2, out, N, d, E, H,
+                                         act, dev_status, s);
+  }
+  return w_up ? launch_t<bf16, true>(x, token_idx, offsets, w1, b1, w_up, w2, out, N, d, E, H, act,
+                                     dev_status, s)
+              : launch_t<bf16, false>(x, token_idx, offsets, w1, b1, w_up, w2, out, N, d, E, H,
+                                      act, dev_status, s);
+}
+
+}  // namespace d2d

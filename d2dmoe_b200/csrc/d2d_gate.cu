@@ -1,0 +1,294 @@
+// Router MLP + dynamic-k rule -> bit-packed expert mask (general-shape kernels),
+// the rule alone on given scores, the 0/1 routing tensor from the bits, and the
+// initial value of the layer output.
+//
+// Upstream semantics restated by these kernels:
+//   scores  = | relu(x Wa^T) Wb^T |        architectures/moe/moefication.py:328-330
+//   keep e  iff  s_e >= T(max_e s * mult)  architectures/moe/moefication.py:80-85
+// Each Linear output is materialised in the tensor dtype T upstream, so the fp32
+// accumulators are rounded to T once after each of the two products, and the
+// threshold is rounded to T before the comparison.
+#include "d2d_common.cuh"
+
+namespace d2d {
+
+namespace {
+
+constexpr int TM = 32;       // tokens per CTA
+constexpr int KC = 32;       // k-chunk staged in shared memory
+constexpr int KP = KC + 4;   // padded row (floats): conflict-free float4 reads
+constexpr int RC = 128;      // router hidden columns per pass
+constexpr int NT = 256;
+
+// max that propagates NaN like torch.max does
+__device__ __forceinline__ float nanmax(float a, float b) {
+  return (a != a || b != b) ? __int_as_float(0x7fc00000) : fmaxf(a, b);
+}
+
+template <typename T>
+__device__ __forceinline__ void gate_row(const float* s, int nw, float mult, int lane,
+                                         uint32_t* mask_row, int E) {
+  // s[j]: this lane's score for expert lane+32j (-inf-like sentinel for e >= E is
+  // handled by the caller passing valid flags through E).
+  float m = -INFINITY;
+  for (int j = 0; j < nw; ++j)
+    if (lane + 32 * j < E) m = nanmax(m, s[j]);
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) m = nanmax(m, __shfl_xor_sync(0xffffffffu, m, o));
+  const float thr = DT<T>::round(__fmul_rn(m, mult));
+  for (int j = 0; j < nw; ++j) {
+    const bool keep = (lane + 32 * j < E) && (s[j] >= thr);
+    const uint32_t w = __ballot_sync(0xffffffffu, keep);
+    if (lane == 0) mask_row[j] = w;
+  }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(NT)
+router_mask_simt_kernel(const T* __restrict__ x, const T* __restrict__ wa,
+                        const T* __restrict__ wb, float mult, uint32_t* __restrict__ mask_bits,
+                        T* __restrict__ scores, const T* __restrict__ last_bias, int add_residual,
+                        T* __restrict__ out_init, int64_t N, int d, int R, int E) {
+  extern __shared__ float sm[];
+  float* xs = sm;                      // [TM][KP]
+  float* wsm = xs + TM * KP;           // [RC][KP]
+  float* hs = wsm + RC * KP;           // [TM][R]
+  const int tid = threadIdx.x, lane = tid & 31, ty = tid >> 5;
+  const int64_t t0 = (int64_t)blockIdx.x * TM;
+
+  for (int rc = 0; rc < R; rc += RC) {
+    float acc[4][4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+#pragma unroll
+      for (int j = 0; j < 4; ++j) acc[i][j] = 0.f;
+    for (int kc = 0; kc < d; kc += KC) {
+      __syncthreads();
+      for (int i = tid; i < TM * KC; i += NT) {
+        const int r = i / KC, k = i % KC;
+        const int64_t t = t0 + r;
+        xs[r * KP + k] = (t < N && kc + k < d) ? DT<T>::to_f(x[t * d + kc + k]) : 0.f;
+      }
+      for (int i = tid; i < RC * KC; i += NT) {
+        const int c = i / KC, k = i % KC;
+        wsm[c * KP + k] =
+            (rc + c < R && kc + k < d) ? DT<T>::to_f(wa[(int64_t)(rc + c) * d + kc + k]) : 0.f;
+      }
+      __syncthreads();
+#pragma unroll
+      for (int k4 = 0; k4 < KC; k4 += 4) {
+        float4 xa[4], wv[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i)
+          xa[i] = *reinterpret_cast<const float4*>(&xs[(4 * ty + i) * KP + k4]);
+#pragma unroll
+        for (int j = 0; j < 4; ++j)
+          wv[j] = *reinterpret_cast<const float4*>(&wsm[(lane + 32 * j) * KP + k4]);
+#pragma unroll
+        for (int i = 0; i < 4; ++i)
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            acc[i][j] = fmaf(xa[i].x, wv[j].x, acc[i][j]);
+            acc[i][j] = fmaf(xa[i].y, wv[j].y, acc[i][j]);
+            acc[i][j] = fmaf(xa[i].z, wv[j].z, acc[i][j]);
+            acc[i][j] = fmaf(xa[i].w, wv[j].w, acc[i][j]);
+          }
+      }
+    }
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const int c = rc + lane + 32 * j;
+        if (c < R) hs[(4 * ty + i) * R + c] = fmaxf(DT<T>::round(acc[i][j]), 0.f);
+      }
+  }
+  __syncthreads();
+
+  // scores + gate: warp ty owns rows 4ty..4ty+3, lane owns experts lane+32j
+  const int nw = (E + 31) / 32;
+  float sc[4][8];   // [row][word]  (E <= 256)
+  for (int j = 0; j < nw; ++j) {
+    const int e = lane + 32 * j;
+    float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
+    if (e < E) {
+      const T* wrow = wb + (int64_t)e * R;
+      const float* h0 = hs + (4 * ty) * R;
+      for (int k = 0; k < R; ++k) {
+        const float w = DT<T>::to_f(wrow[k]);
+        a0 = fmaf(h0[k], w, a0);
+        a1 = fmaf(h0[R + k], w, a1);
+        a2 = fmaf(h0[2 * R + k], w, a2);
+        a3 = fmaf(h0[3 * R + k], w, a3);
+      }
+    }
+    sc[0][j] = fabsf(DT<T>::round(a0));
+    sc[1][j] = fabsf(DT<T>::round(a1));
+    sc[2][j] = fabsf(DT<T>::round(a2));
+    sc[3][j] = fabsf(DT<T>::round(a3));
+  }
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const int64_t t = t0 + 4 * ty + i;
+    if (t >= N) break;   // warp-uniform
+    if (scores)
+      for (int j = 0; j < nw; ++j)
+        if (lane + 32 * j < E) scores[t * E + lane + 32 * j] = DT<T>::from_f(sc[i][j]);
+    gate_row<T>(sc[i], nw, mult, lane, mask_bits + t * nw, E);
+  }
+
+  if (out_init) {
+    const int rows = (int)min((int64_t)TM, N - t0);
+    for (int64_t i = tid; i < (int64_t)rows * d; i += NT) {
+      const int r = (int)(i / d), c = (int)(i % d);
+      float v = last_bias ? DT<T>::to_f(last_bias[c]) : 0.f;
+      if (add_residual) v = DT<T>::round(v) + DT<T>::to_f(x[(t0 + r) * d + c]);
+      out_init[(t0 + r) * d + c] = DT<T>::from_f(v);
+    }
+  }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(NT)
+mask_from_scores_kernel(const T* __restrict__ scores, float mult, uint32_t* __restrict__ mask_bits,
+                        int64_t N, int E) {
+  const int lane = threadIdx.x & 31;
+  const int64_t warp = ((int64_t)blockIdx.x * NT + threadIdx.x) >> 5;
+  const int64_t nwarps = ((int64_t)gridDim.x * NT) >> 5;
+  const int nw = (E + 31) / 32;
+  for (int64_t t = warp; t < N; t += nwarps) {
+    float s[8];
+    for (int j = 0; j < nw; ++j) {
+      const int e = lane + 32 * j;
+      s[j] = e < E ? DT<T>::to_f(scores[t * E + e]) : 0.f;
+    }
+    gate_row<T>(s, nw, mult, lane, mask_bits + t * nw, E);
+  }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(NT)
+init_out_kernel(const T* __restrict__ x, const T* __restrict__ last_bias, int add_residual,
+                T* __restrict__ out, int64_t total, int d) {
+  for (int64_t i = (int64_t)blockIdx.x * NT + threadIdx.x; i < total;
+       i += (int64_t)gridDim.x * NT) {
+    const int c = (int)(i % d);
+    float v = last_bias ? DT<T>::to_f(last_bias[c]) : 0.f;
+    if (add_residual) v = DT<T>::round(v) + DT<T>::to_f(x[i]);
+    out[i] = DT<T>::from_f(v);
+  }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(NT)
+expand_mask_kernel(const uint32_t* __restrict__ mask_bits, T* __restrict__ rt, int64_t total, int E) {
+  const int nw = (E + 31) / 32;
+  for (int64_t i = (int64_t)blockIdx.x * NT + threadIdx.x; i < total;
+       i += (int64_t)gridDim.x * NT) {
+    const int64_t t = i / E;
+    const int e = (int)(i % E);
+    const uint32_t w = mask_bits[t * nw + (e >> 5)];
+    rt[i] = DT<T>::from_f(((w >> (e & 31)) & 1u) ? 1.0f : 0.0f);
+  }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(NT)
+pack_mask_kernel(const T* __restrict__ rt, uint32_t* __restrict__ mask_bits, int64_t N, int E) {
+  const int lane = threadIdx.x & 31;
+  const int64_t warp = ((int64_t)blockIdx.x * NT + threadIdx.x) >> 5;
+  const int64_t nwarps = ((int64_t)gridDim.x * NT) >> 5;
+  const int nw = (E + 31) / 32;
+  for (int64_t t = warp; t < N; t += nwarps)
+    for (int j = 0; j < nw; ++j) {
+      const int e = lane + 32 * j;
+      const bool keep = e < E && DT<T>::to_f(rt[t * E + e]) > 0.0f;
+      const uint32_t w = __ballot_sync(0xffffffffu, keep);
+      if (lane == 0) mask_bits[t * nw + j] = w;
+    }
+}
+
+inline int grid_for(int64_t work, int per_block, int cap) {
+  int64_t g = ceil_div64(work, per_block);
+  if (g < 1) g = 1;
+  if (g > cap) g = cap;
+  return (int)g;
+}
+
+}  // namespace
+
+int launch_router_mask_simt(const void* x, const void* wa, const void* wb, float mult,
+                            uint32_t* mask_bits, void* scores, const void* last_bias,
+                            int add_residual, void* out_init, int64_t N, int d, int R, int E,
+                            int dtype, int* dev_status, cudaStream_t s) {
+  (void)dev_status;
+  if (E > 256 || R > 1024) return D2D_ERR_UNSUPPORTED;
+  const size_t smem = sizeof(float) * ((size_t)TM * KP + (size_t)RC * KP + (size_t)TM * R);
+  const int64_t grid = ceil_div64(N, TM);
+  if (grid > 0x7fffffffLL) return D2D_ERR_UNSUPPORTED;
+  cudaError_t err;
+  if (dtype == D2D_F32) {
+    err = cudaFuncSetAttribute(router_mask_simt_kernel<float>,
+                               cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (err != cudaSuccess) return D2D_ERR_LAUNCH;
+    router_mask_simt_kernel<float><<<(unsigned)grid, NT, smem, s>>>(
+        (const float*)x, (const float*)wa, (const float*)wb, mult, mask_bits, (float*)scores,
+        (const float*)last_bias, add_residual, (float*)out_init, N, d, R, E);
+  } else {
+    err = cudaFuncSetAttribute(router_mask_simt_kernel<bf16>,
+                               cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (err != cudaSuccess) return D2D_ERR_LAUNCH;
+    router_mask_simt_kernel<bf16><<<(unsigned)grid, NT, smem, s>>>(
+        (const bf16*)x, (const bf16*)wa, (const bf16*)wb, mult, mask_bits, (bf16*)scores,
+        (const bf16*)last_bias, add_residual, (bf16*)out_init, N, d, R, E);
+  }
+  return cudaGetLastError() == cudaSuccess ? D2D_OK : D2D_ERR_LAUNCH;
+}
+
+int launch_mask_from_scores(const void* scores, float mult, uint32_t* mask_bits, int64_t N, int E,
+                            int dtype, int* dev_status, cudaStream_t s) {
+  (void)dev_status;
+  if (E > 256) return D2D_ERR_UNSUPPORTED;
+  const int grid = grid_for(N, NT / 32, 148 * 8);
+  if (dtype == D2D_F32)
+    mask_from_scores_kernel<float><<<grid, NT, 0, s>>>((const float*)scores, mult, mask_bits, N, E);
+  else
+    mask_from_scores_kernel<bf16><<<grid, NT, 0, s>>>((const bf16*)scores, mult, mask_bits, N, E);
+  return cudaGetLastError() == cudaSuccess ? D2D_OK : D2D_ERR_LAUNCH;
+}
+
+int launch_init_out(const void* x, const void* last_bias, int add_residual, void* out, int64_t N,
+                    int d, int dtype, cudaStream_t s) {
+  const int64_t total = N * d;
+  const int grid = grid_for(total, NT * 8, 148 * 8);
+  if (dtype == D2D_F32)
+    init_out_kernel<float><<<grid, NT, 0, s>>>((const float*)x, (const float*)last_bias,
+                                               add_residual, (float*)out, total, d);
+  else
+    init_out_kernel<bf16><<<grid, NT, 0, s>>>((const bf16*)x, (const bf16*)last_bias,
+                                              add_residual, (bf16*)out, total, d);
+  return cudaGetLastError() == cudaSuccess ? D2D_OK : D2D_ERR_LAUNCH;
+}
+
+int launch_pack_mask(const void* rt, uint32_t* mask_bits, int64_t N, int E, int dtype,
+                     cudaStream_t s) {
+  const int grid = grid_for(N, NT / 32, 148 * 8);
+  if (dtype == D2D_F32)
+    pack_mask_kernel<float><<<grid, NT, 0, s>>>((const float*)rt, mask_bits, N, E);
+  else
+    pack_mask_kernel<bf16><<<grid, NT, 0, s>>>((const bf16*)rt, mask_bits, N, E);
+  return cudaGetLastError() == cudaSuccess ? D2D_OK : D2D_ERR_LAUNCH;
+}
+
+int launch_expand_mask(const uint32_t* mask_bits, void* rt, int64_t N, int E, int dtype,
+                       cudaStream_t s) {
+  const int64_t total = N * E;
+  const int grid = grid_for(total, NT * 4, 148 * 8);
+  if (dtype == D2D_F32)
+    expand_mask_kernel<float><<<grid, NT, 0, s>>>(mask_bits, (float*)rt, total, E);
+  else
+    expand_mask_kernel<bf16><<<grid, NT, 0, s>>>(mask_bits, (bf16*)rt, total, E);
+  return cudaGetLastError() == cudaSuccess ? D2D_OK : D2D_ERR_LAUNCH;
+}
+
+}  // namespace d2d

@@ -1,0 +1,425 @@
+"""Drop-in PyTorch modules for the upstream MoE-FFN inference layer.
+
+Same constructor arguments, attributes, ``state_dict`` keys/shapes and
+``forward`` signatures as the upstream classes, with the computation done by the
+sm_100a CUDA library:
+
+  MoeficationMoE      <-> architectures/moe/moefication.py:28-101
+  MoeficationRouter   <-> architectures/moe/moefication.py:309-339
+  B200KernelExperts   <-> CustomKernelExperts, architectures/moe/moe_layers.py:136-264
+  B200GluExperts      <-> ExecuteAllExperts with intermediate gating,
+                          architectures/moe/moe_layers.py:50-101
+  MOE_IMPL_MAP        <-> architectures/moe/moe_layers.py:402-407
+
+state_dict of MoeficationMoE(bias=True, experts_class='b200_kernel') + router:
+  last_bias [1,d], experts.w1 [E,d,H], experts.b1 [E,H], experts.w2 [E,H,d],
+  router.layers.0.weight [R,d], router.layers.2.weight [E,R]
+which is what an upstream checkpoint of the 'custom_kernel' layer holds.
+
+There is no CPU path: a forward on CPU tensors raises.
+"""
+from __future__ import annotations
+
+import math
+
+import torch
+from torch import nn
+
+from . import ops
+
+ACTIVATION_TO_NAME = {nn.GELU: "gelu", nn.Tanh: "tanh", nn.ReLU: "relu", nn.LeakyReLU: "leaky_relu"}
+
+
+def _function_module(fn):
+    class _Fn(nn.Module):
+        def forward(self, x):
+            return fn(x)
+    return _Fn
+
+
+# name -> module class, as in common.py:159-169
+ACTIVATION_NAME_MAP = {
+    "relu": nn.ReLU, "gelu": nn.GELU, "sigmoid": nn.Sigmoid, "tanh": nn.Tanh,
+    "leaky_relu": nn.LeakyReLU, "softplus": nn.Softplus, "silu": nn.SiLU,
+    "abs": _function_module(torch.abs), "identity": nn.Identity,
+}
+
+# forward_mode strings of the upstream experts class that mean "the fast GPU path"
+_KERNEL_MODES = ("b200", "triton_atomic", "triton")
+
+
+def _uniform_init(p: torch.Tensor) -> torch.Tensor:
+    """uniform(-1/sqrt(last dim), +1/sqrt(last dim)) (architectures/moe/moe_layers.py:19-24)."""
+    with torch.no_grad():
+        b = 1.0 / math.sqrt(p.size(-1))
+        p.uniform_(-b, b)
+    return p
+
+
+class _WorkspaceCache:
+    """Per-module cache of caller-owned buffers, keyed by (tokens, device)."""
+
+    def __init__(self):
+        self._w = {}
+
+    def get(self, n: int, E: int, device) -> ops.Workspace:
+        key = (n, E, str(device))
+        w = self._w.get(key)
+        if w is None:
+            if len(self._w) > 8:
+                self._w.clear()
+            w = ops.Workspace.allocate(n, E, device)
+            self._w[key] = w
+        return w
+
+
+class _PackedCache:
+    """Packed weight images, rebuilt when any source parameter changes."""
+
+    def __init__(self):
+        self._key = None
+        self._buf = None
+
+    def get(self, params, make):
+        key = tuple((p.data_ptr(), p._version, p.dtype, tuple(p.shape)) for p in params
+                    if p is not None)
+        if key != self._key:
+            self._buf = make()
+            self._key = key
+        return self._buf
+
+
+class ExpertIntermediateActivationExtractionStub(nn.Module):
+    """Parameter-free hook point kept for attribute compatibility
+    (architectures/moe/moe_layers.py:116-125); the fused kernel does not call it."""
+
+
+class ExpertOutputActivationExtractionStub(nn.Module):
+    """Parameter-free hook point (architectures/moe/moe_layers.py:128-133)."""
+
+
+class ExpertsLayer(nn.Module):
+    pass
+
+
+class B200KernelExperts(ExpertsLayer):
+    """Experts of a two-layer FFN split (CustomKernelExperts-compatible).
+
+    Parameters w1 [E,d,H], b1 [E,H], w2 [E,H,d]; ``forward(x[N,d], routing_tensor[N,E])``
+    returns sum over the experts with a non-zero routing entry of
+    act(x W1[e] + b1[e]) W2[e]  (architectures/moe/moe_layers.py:174-211).
+    """
+
+    def __init__(self, dim, num_experts, depth=2, expert_dim=None, bias=True, activation=nn.GELU,
+                 intermediate_gating=False):
+        if intermediate_gating:
+            raise NotImplementedError("intermediate_gating: use experts_class='b200_glu'")
+        super().__init__()
+        assert depth == 2, "No support for depth != 2 for now"
+        assert bias == "without_last", 'No support for bias != "without_last" for now'
+        assert activation in ACTIVATION_TO_NAME, f"{activation} not supported by the kernel"
+        self.num_experts = num_experts
+        self.depth = depth
+        self.expert_dim = dim * 2 if expert_dim is None else expert_dim
+        self.hidden_dim = dim
+        self.bias_mode = bias
+        self.w1 = _uniform_init(nn.Parameter(torch.empty(num_experts, dim, self.expert_dim)))
+        self.b1 = _uniform_init(nn.Parameter(torch.empty(num_experts, self.expert_dim)))
+        self.w2 = _uniform_init(nn.Parameter(torch.empty(num_experts, self.expert_dim, dim)))
+        self.act = activation()
+        self.activation_str = ACTIVATION_TO_NAME[activation]
+        self._forward_mode = "b200"
+        self.intermediate_activation_extraction_stub = ExpertIntermediateActivationExtractionStub()
+        self.output_activation_extraction_stub = ExpertOutputActivationExtractionStub()
+        self._wsp = _WorkspaceCache()
+        self._packed = _PackedCache()
+
+    @property
+    def forward_mode(self):
+        return self._forward_mode
+
+    @forward_mode.setter
+    def forward_mode(self, value):
+        self._forward_mode = value
+
+    # parameters in the order the kernels take them
+    def kernel_params(self):
+        return dict(w1=self.w1, b1=self.b1, w2=self.w2, w_up=None, act=self.activation_str)
+
+    def packed(self):
+        p = self.kernel_params()
+        return self._packed.get((p["w1"], p["b1"], p["w2"], p["w_up"]),
+                                lambda: ops.prepack_experts(p["w1"].detach(),
+                                                            None if p["b1"] is None else p["b1"].detach(),
+                                                            p["w2"].detach(),
+                                                            None if p["w_up"] is None else p["w_up"].detach()))
+
+    def _check_mode(self):
+        if self._forward_mode not in _KERNEL_MODES:
+            raise NotImplementedError(
+                f"Unsupported forward_mode: {self._forward_mode!r}; this class runs the CUDA "
+                f"kernels only (modes {_KERNEL_MODES})")
+
+    @torch.no_grad()
+    def forward(self, x, routing_tensor):
+        assert x.dim() == 2, f"{x.size()=}"
+        self._check_mode()
+        N, _ = x.shape
+        E = self.num_experts
+        x = x.contiguous()
+        rt = routing_tensor.contiguous().to(x.dtype)
+        wsp = self._wsp.get(N, E, x.device)
+        out = torch.empty_like(x)
+        if N == 0:
+            return out
+        p = self.kernel_params()
+        ops.pack_mask(rt, wsp)
+        ops.compact(wsp, N, E)
+        ops.experts_ffn(x, wsp, p["w1"], p["b1"], p["w2"], p["act"], out, w_up=p["w_up"],
+                        packed=self.packed(), accumulate=False)
+        return out
+
+
+class _GluLayer(nn.Module):
+    """Holder of one stacked expert weight ``w [E, in, out]``, named like
+    ExecuteAllExpertsLayer (architectures/moe/moe_layers.py:32-47) so that
+    ``layers.{i}.w`` keys of an upstream state_dict load."""
+
+    def __init__(self, in_dim, out_dim, num_experts):
+        super().__init__()
+        self.w = _uniform_init(nn.Parameter(torch.empty(num_experts, in_dim, out_dim)))
+
+
+class B200GluExperts(B200KernelExperts):
+    """Gated experts: down(act(gate(x)) * up(x)), no biases.  Parameter names follow
+    ExecuteAllExperts with intermediate gating: layers.0 = gate, layers.1 = down,
+    layers.2 = up (architectures/moe/moe_layers.py:71-78,91-96)."""
+
+    def __init__(self, dim, num_experts, depth=2, expert_dim=None, bias=False, activation=nn.GELU,
+                 intermediate_gating=True):
+        ExpertsLayer.__init__(self)
+        assert depth == 2, "Intermediate gating not supported for depth > 2"
+        if bias not in (False, None):
+            raise NotImplementedError("gated experts with biases are not supported by the kernel")
+        if not intermediate_gating:
+            raise NotImplementedError("use experts_class='b200_kernel' for ungated experts")
+        assert activation in ACTIVATION_TO_NAME, f"{activation} not supported by the kernel"
+        self.num_experts = num_experts
+        self.depth = depth
+        self.dim = dim
+        self.hidden_dim = dim
+        self.expert_dim = dim * 2 if expert_dim is None else expert_dim
+        self.bias_mode = bias
+        self.activation = activation
+        self.intermediate_gating = True
+        self.layers = nn.ModuleList([
+            _GluLayer(dim, self.expert_dim, num_experts),
+            _GluLayer(self.expert_dim, dim, num_experts),
+            _GluLayer(dim, self.expert_dim, num_experts),
+        ])
+        self.act = activation()
+        self.activation_str = ACTIVATION_TO_NAME[activation]
+        self._forward_mode = "b200"
+        self._wsp = _WorkspaceCache()
+        self._packed = _PackedCache()
+
+    def kernel_params(self):
+        return dict(w1=self.layers[0].w, b1=None, w2=self.layers[1].w, w_up=self.layers[2].w,
+                    act=self.activation_str)
+
+
+MOE_IMPL_MAP = {
+    "b200_kernel": B200KernelExperts,
+    "b200_glu": B200GluExperts,
+    # upstream keys resolve to the CUDA classes so that existing call sites
+    # (replace_with_moes(..., experts_class='custom_kernel')) pick them up
+    "custom_kernel": B200KernelExperts,
+}
+
+
+class MoELayer(nn.Module):
+    def __init__(self, name, num_experts):
+        super().__init__()
+        self.name = name
+        self.num_experts = num_experts
+
+
+class MoeficationRouter(nn.Module):
+    """Regression router MLP (architectures/moe/moefication.py:309-339): same
+    constructor, same ``layers`` ModuleList (so the state_dict keys are
+    ``layers.0.weight`` and ``layers.2.weight`` for depth 2) and the same cached
+    Bernoulli override used by the upstream micro-benchmark."""
+
+    def __init__(self, hidden_dim, num_experts, width=128, depth=2, bias=False, activation="tanh",
+                 output_activation="identity", test_override_outputs_p=None):
+        super().__init__()
+        self.layers = nn.ModuleList()
+        if depth == 1:
+            self.layers.append(nn.Linear(hidden_dim, num_experts, bias=bias))
+        else:
+            self.layers.append(nn.Linear(hidden_dim, width, bias=bias))
+            self.layers.append(ACTIVATION_NAME_MAP[activation]())
+            for _ in range(depth - 2):
+                self.layers.append(nn.Linear(width, width, bias=bias))
+                self.layers.append(ACTIVATION_NAME_MAP[activation]())
+            self.layers.append(nn.Linear(width, num_experts, bias=bias))
+        self.layers.append(ACTIVATION_NAME_MAP[output_activation]())
+        self.test_override_outputs_p = test_override_outputs_p
+        if test_override_outputs_p is not None:
+            self.response_cache = {}
+        self._fusable = (depth == 2 and not bias and activation == "relu"
+                         and output_activation == "abs" and test_override_outputs_p is None)
+        self._packed = _PackedCache()
+
+    def fusable(self) -> bool:
+        """True when the router is the D2DMoE form (depth 2, ReLU, abs, no bias) that
+        the fused router+mask kernel computes."""
+        return self._fusable
+
+    def packed(self):
+        wa, wb = self.layers[0].weight, self.layers[2].weight
+        return self._packed.get((wa, wb), lambda: ops.prepack_router(wa.detach(), wb.detach()))
+
+    def forward(self, x):
+        for layer in self.layers:
+            x = layer(x)
+        if self.test_override_outputs_p is not None:
+            key = (x.size(0), x.size(1))
+            if key in self.response_cache:
+                x = self.response_cache[key]
+            else:
+                with torch.no_grad():
+                    x.bernoulli_(self.test_override_outputs_p)
+                    self.response_cache[key] = x
+        return x
+
+
+class MoeficationMoE(MoELayer):
+    """The MoE-FFN layer (architectures/moe/moefication.py:28-101).
+
+    ``forward(x[B,S,d]) -> (out[B,S,d], {name: (routing_tensor[B,S,E],)})`` with
+    ``forward_mode`` in {'all','topk','dynk','dynk_max'}, ``tau``/``k`` read at call
+    time.  In 'dynk_max' mode with a D2DMoE router the whole layer is one library call
+    (router + rule -> bit mask -> token lists -> expert FFN with scatter-add); other
+    modes compute the routing tensor with device tensor ops and share the rest.
+    ``tau`` keeps the upstream meaning: expert e runs iff score_e >= max_e(score)*(1.0-tau).
+    """
+
+    def __init__(self, name, hidden_dim, num_experts, bias, expert_dim, activation,
+                 experts_class="b200_kernel", add_residual_connection=False,
+                 add_intermediate_gating=False):
+        super().__init__(name, num_experts)
+        self.hidden_dim = hidden_dim
+        self.expert_dim = expert_dim
+        self.num_experts = num_experts
+        self.bias = bias
+        if add_intermediate_gating and experts_class in ("execute_all", "module", "custom_kernel",
+                                                         "b200_kernel"):
+            experts_class = "b200_glu"
+        if experts_class not in MOE_IMPL_MAP:
+            raise NotImplementedError(
+                f"experts_class={experts_class!r}: this package provides {sorted(MOE_IMPL_MAP)}")
+        self.experts = MOE_IMPL_MAP[experts_class](dim=hidden_dim, num_experts=num_experts, depth=2,
+                                                   expert_dim=self.expert_dim,
+                                                   bias=False if not bias else "without_last",
+                                                   activation=activation,
+                                                   intermediate_gating=add_intermediate_gating)
+        if self.bias:
+            self.last_bias = nn.Parameter(torch.zeros(1, hidden_dim))
+        self.forward_mode = "all"
+        self.router = None
+        self.k = None
+        self.tau = None
+        self.add_residual_connection = add_residual_connection
+        self._wsp = _WorkspaceCache()
+
+    # -- routing for the modes that are not fused ---------------------------------
+    def gate(self, x):
+        """Routing tensor [B,S,E] of 0/1 in the router's dtype for the non-fused modes
+        (architectures/moe/moefication.py:54-88), on the device."""
+        if self.forward_mode == "all":
+            return torch.ones(x.size(0), x.size(1), self.num_experts, dtype=x.dtype,
+                              device=x.device)
+        if self.forward_mode == "topk":
+            s = self.router(x)
+            top = torch.topk(s, k=self.k, dim=-1)[1]
+            rt = torch.zeros_like(s)
+            rt.scatter_(2, top, 1.0)
+            return rt
+        if self.forward_mode == "dynk":
+            s = self.router(x)
+            shares = s / s.sum(dim=-1, keepdim=True)
+            srt, idx = torch.sort(shares, dim=-1, descending=True)
+            m = torch.cumsum(srt, dim=-1) < self.tau
+            m = m.roll(shifts=1, dims=-1)
+            m[..., 0] = True
+            return m.gather(dim=-1, index=idx.argsort(dim=-1)).to(x.dtype)
+        if self.forward_mode == "dynk_max":
+            s = self.router(x)
+            wsp = self._wsp.get(s.numel() // s.size(-1), self.num_experts, x.device)
+            s2 = s.reshape(-1, s.size(-1)).contiguous()
+            ops.mask_from_scores(s2, self.tau, wsp)
+            return ops.expand_mask(wsp, s2.size(0), s2.size(1), s.dtype).view(s.shape)
+        raise ValueError(f"Unsupported forward_mode: {self.forward_mode}")
+
+    @torch.no_grad()
+    def forward(self, x):
+        if not x.is_cuda:
+            raise RuntimeError("d2dmoe_b200 runs on CUDA tensors only (there is no CPU path)")
+        self.experts._check_mode()
+        orig_size = x.size()
+        E = self.num_experts
+        x2d = x.reshape(-1, x.size(-1)).contiguous()
+        N = x2d.size(0)
+        p = self.experts.kernel_params()
+        last_bias = self.last_bias.view(-1) if self.bias else None
+        out = torch.empty_like(x2d)
+        wsp = self._wsp.get(N, E, x.device)
+        fused = (self.forward_mode == "dynk_max" and self.router is not None
+                 and isinstance(self.router, MoeficationRouter) and self.router.fusable())
+        if N == 0:
+            rt = torch.zeros(*orig_size[:-1], E, dtype=x.dtype, device=x.device)
+            return out.view(orig_size), {self.name: (rt,)}
+        if fused:
+            wa, wb = self.router.layers[0].weight, self.router.layers[2].weight
+            ops.moe_forward(x2d, wa, wb, self.tau, p["w1"], p["b1"], p["w2"], p["act"], out, wsp,
+                            w_up=p["w_up"], last_bias=last_bias,
+                            add_residual=self.add_residual_connection,
+                            router_packed=self.router.packed(),
+                            experts_packed=self.experts.packed())
+            rt = ops.expand_mask(wsp, N, E, x.dtype).view(*orig_size[:-1], E)
+        elif self.forward_mode == "dynk_max":
+            # any other router: its scores come from device tensor ops, the rule and the
+            # rest of the layer from the library
+            s = self.router(x)
+            s2 = s.reshape(N, E).contiguous()
+            ops.moe_forward(x2d, None, None, self.tau, p["w1"], p["b1"], p["w2"], p["act"], out,
+                            wsp, w_up=p["w_up"], scores=s2, last_bias=last_bias,
+                            add_residual=self.add_residual_connection,
+                            experts_packed=self.experts.packed())
+            rt = ops.expand_mask(wsp, N, E, s.dtype).view(*orig_size[:-1], E)
+        else:
+            rt = self.gate(x)
+            ops.pack_mask(rt.reshape(N, E).contiguous(), wsp)
+            ops.compact(wsp, N, E)
+            ops.experts_ffn(x2d, wsp, p["w1"], p["b1"], p["w2"], p["act"], out, w_up=p["w_up"],
+                            packed=self.experts.packed(), last_bias=last_bias,
+                            add_residual=self.add_residual_connection, accumulate=False)
+        return out.view(orig_size), {self.name: (rt,)}
+
+    def last_workspace(self, n: int, device) -> ops.Workspace:
+        """The cached buffers of the last call with ``n`` tokens: bit mask, token lists,
+        offsets and the device status word (for tests and diagnostics)."""
+        return self._wsp.get(n, self.num_experts, device)
+
+
+def add_routers(model: nn.Module, router_args: dict) -> dict:
+    """Attach a MoeficationRouter to every MoeficationMoE of ``model``
+    (architectures/moe/moefication.py:342-354)."""
+    found = {}
+    for name, m in model.named_modules():
+        if isinstance(m, MoeficationMoE):
+            m.router = MoeficationRouter(m.hidden_dim, m.num_experts, **router_args)
+            found[name] = m
+    assert len(found) > 0
+    return found

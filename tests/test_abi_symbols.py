@@ -1,0 +1,42 @@
+"""The shared library loads and exports every function include/d2dmoe.h declares."""
+import ctypes
+import re
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parents[1]
+
+
+def declared_functions():
+    text = (ROOT / "include" / "d2dmoe.h").read_text()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    return sorted(set(re.findall(r"\b(d2d_[a-z0-9_]+)\s*\(", text)))
+
+
+def test_header_declares_the_expected_surface():
+    names = declared_functions()
+    for must in ("d2d_router_mask", "d2d_mask_from_scores", "d2d_compact", "d2d_experts_ffn",
+                 "d2d_moe_forward", "d2d_expand_mask", "d2d_strerror", "d2d_abi_version"):
+        assert must in names
+
+
+def test_library_exports_every_declared_symbol():
+    from d2dmoe_b200 import _capi
+    cdll = ctypes.CDLL(str(_capi.LIB_PATH))
+    for name in declared_functions():
+        assert hasattr(cdll, name), f"{name} declared in d2dmoe.h but not exported"
+        assert name in _capi.SIGNATURES, f"{name} has no ctypes signature"
+    assert set(_capi.SIGNATURES) == set(declared_functions())
+
+
+def test_host_only_entry_points():
+    from d2dmoe_b200 import _capi
+    assert _capi.lib.d2d_abi_version() == 1
+    assert _capi.lib.d2d_strerror(0) == b"ok"
+    assert b"workspace" in _capi.lib.d2d_strerror(4)
+    n = ctypes.c_size_t(0)
+    assert _capi.lib.d2d_workspace_bytes(50432, 24, ctypes.byref(n)) == 0
+    assert n.value >= 50 * 24 * 4 and n.value % 256 == 0
+    assert _capi.lib.d2d_workspace_bytes(-1, 24, ctypes.byref(n)) == 1      # BAD_ARG
+    # null pointers are rejected on the host before anything is launched
+    assert _capi.lib.d2d_compact(None, None, None, 10, 4, None, 0, None, None) == 1
+    assert _capi.lib.d2d_mask_from_scores(None, 0.5, None, 10, 4, 0, None, None) == 1

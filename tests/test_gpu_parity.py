@@ -1,0 +1,219 @@
+"""CUDA path vs the committed upstream outputs and the CPU oracle (through the C ABI)."""
+import numpy as np
+import pytest
+import torch
+
+from helpers import C, O, TOL, WINDOW, all_cases, case_ids, golden_mask, golden_scores, load_golden
+
+pytestmark = pytest.mark.gpu
+
+
+def dev(t):
+    return None if t is None else t.cuda().contiguous()
+
+
+def bits_of(wsp, N):
+    return wsp.mask_bits[:N].cpu().numpy().view(np.uint32)
+
+
+def lists_of(wsp, E):
+    off = wsp.offsets.cpu().numpy()
+    idx = wsp.token_idx[: int(off[E])].cpu().numpy()
+    return off, idx
+
+
+def load_mask(wsp, mask):
+    b = torch.from_numpy(O.pack_mask(mask).view(np.int32)).cuda()
+    wsp.mask_bits[: b.shape[0]].copy_(b)
+
+
+@pytest.mark.parametrize("c", all_cases(), ids=case_ids())
+def test_mask_from_upstream_scores_bit_exact(c):
+    from d2dmoe_b200 import ops
+    g, t = load_golden(c)
+    wsp = ops.Workspace.allocate(c.N, c.E, "cuda")
+    ops.mask_from_scores(dev(golden_scores(g, c)), c.tau, wsp)
+    assert np.array_equal(bits_of(wsp, c.N), g["mask_bits"])      # zero exclusions
+    wsp.check_status()
+
+
+@pytest.mark.parametrize("c", all_cases(), ids=case_ids())
+def test_router_mask(c):
+    from d2dmoe_b200 import ops
+    g, t = load_golden(c)
+    if c.score_override:
+        pytest.skip("scores are given, no router")
+    wsp = ops.Workspace.allocate(c.N, c.E, "cuda")
+    x2d = dev(t["x"].reshape(c.N, c.d))
+    scores = torch.empty(c.N, c.E, dtype=c.torch_dtype, device="cuda")
+    wa, wb = dev(t["wa"]), dev(t["wb"])
+    for packed in (None, ops.prepack_router(wa, wb)):
+        ops.router_mask(x2d, wa, wb, c.tau, wsp, scores_out=scores, packed=packed)
+        sg = golden_scores(g, c)
+        err = O.rel_err(scores.cpu(), sg)
+        assert err <= (1e-5 if c.dtype == "fp32" else 2.0 ** -7), err
+        m = O.unpack_mask(bits_of(wsp, c.N), c.E)
+        # our own scores -> our own mask must be exactly the rule
+        assert torch.equal(m, O.dynk_max_mask(scores.cpu(), c.tau))
+        near = O.near_threshold(sg, c.tau, WINDOW[c.dtype])
+        bad = ((m != golden_mask(g, c)) & ~near).sum().item()
+        assert bad == 0, f"{bad} mask bits differ outside the tie window ({near.sum().item()} excluded)"
+        wsp.check_status()
+
+
+@pytest.mark.parametrize("c", all_cases(), ids=case_ids())
+def test_compaction_bit_exact(c):
+    from d2dmoe_b200 import ops
+    g, t = load_golden(c)
+    mask = golden_mask(g, c)
+    wsp = ops.Workspace.allocate(c.N, c.E, "cuda")
+    load_mask(wsp, mask)
+    ops.compact(wsp, c.N, c.E)
+    off, idx = lists_of(wsp, c.E)
+    roff, ridx = O.expert_token_lists(mask)
+    assert np.array_equal(off, roff) and np.array_equal(idx, ridx)
+    ops.compact(wsp, c.N, c.E)          # run twice: same bits
+    off2, idx2 = lists_of(wsp, c.E)
+    assert np.array_equal(off, off2) and np.array_equal(idx, idx2)
+    wsp.check_status()
+
+
+def _exact(c, t, mask):
+    x2d = t["x"].reshape(c.N, c.d)
+    b1 = None if c.glu else t["b1"]
+    ex = O.experts_ffn_exact(x2d, mask, t["w1"], b1, t["w2"], c.act, t.get("w_up"))
+    if not c.glu:
+        ex = ex + t["last_bias"].double()
+    if c.residual:
+        ex = ex + x2d.double()
+    return ex
+
+
+@pytest.mark.parametrize("c", all_cases(), ids=case_ids())
+def test_experts_ffn(c):
+    from d2dmoe_b200 import ops
+    g, t = load_golden(c)
+    mask = golden_mask(g, c)
+    wsp = ops.Workspace.allocate(c.N, c.E, "cuda")
+    load_mask(wsp, mask)
+    ops.compact(wsp, c.N, c.E)
+    x2d = dev(t["x"].reshape(c.N, c.d))
+    w1, w2 = dev(t["w1"]), dev(t["w2"])
+    b1 = None if c.glu else dev(t["b1"])
+    w_up = dev(t.get("w_up"))
+    lb = None if c.glu else dev(t["last_bias"].reshape(-1))
+    rows = torch.from_numpy(g["rows"])
+    ref = torch.from_numpy(g["out_execute_all" if c.glu else "out_naive"])
+    exact = _exact(c, t, mask)
+    for packed in (None, ops.prepack_experts(w1, b1, w2, w_up)):
+        out = torch.full((c.N, c.d), float("nan"), dtype=c.torch_dtype, device="cuda")
+        ops.experts_ffn(x2d, wsp, w1, b1, w2, c.act, out, w_up=w_up, packed=packed, last_bias=lb,
+                        add_residual=c.residual, accumulate=False)
+        o = out.cpu().float()
+        assert O.rel_err(o[rows], ref) <= TOL[c.dtype]          # vs upstream output
+        assert O.rel_err(o, exact) <= TOL[c.dtype]              # vs fp64 truth, every row
+        wsp.check_status()
+
+
+@pytest.mark.parametrize("c", all_cases(), ids=case_ids())
+def test_module_forward(c):
+    import d2dmoe_b200 as D
+    g, t = load_golden(c)
+    act = {"relu": torch.nn.ReLU, "gelu": torch.nn.GELU, "tanh": torch.nn.Tanh,
+           "leaky_relu": torch.nn.LeakyReLU}[c.act]
+    if c.glu:
+        moe = D.MoeficationMoE(c.name, c.d, c.E, False, c.H, act, experts_class="execute_all",
+                               add_intermediate_gating=True)
+        sd = {"experts.layers.0.w": t["w1"], "experts.layers.1.w": t["w2"],
+              "experts.layers.2.w": t["w_up"]}
+    else:
+        moe = D.MoeficationMoE(c.name, c.d, c.E, True, c.H, act, experts_class="custom_kernel",
+                               add_residual_connection=c.residual)
+        sd = {"experts.w1": t["w1"], "experts.b1": t["b1"], "experts.w2": t["w2"],
+              "last_bias": t["last_bias"]}
+    moe.router = D.MoeficationRouter(c.d, c.E, width=c.R, depth=2, bias=False, activation="relu",
+                                     output_activation="abs")
+    sd["router.layers.0.weight"], sd["router.layers.2.weight"] = t["wa"], t["wb"]
+    moe = moe.to(c.torch_dtype)
+    moe.load_state_dict(sd, strict=True)
+    if c.score_override:
+        class Fixed(torch.nn.Module):
+            def forward(self, x):
+                return t["scores"].cuda()
+        moe.router = Fixed()
+    moe = moe.cuda().eval()
+    moe.forward_mode, moe.tau = "dynk_max", c.tau
+    x = t["x"].cuda()
+    moe(x)                                   # warm-up: caches, packed weights
+    torch.cuda.synchronize()
+    # the layer must not synchronise with the host
+    # (upstream enforces this for its GPU mode: scripts/test_moe_implementations.py:78-83)
+    torch.cuda.set_sync_debug_mode("error")
+    try:
+        out, gd = moe(x)
+    finally:
+        torch.cuda.set_sync_debug_mode("default")
+    rt = gd[c.name][0]
+    assert out.shape == x.shape and rt.shape == (c.B, c.S, c.E) and rt.dtype == x.dtype
+    m = rt.reshape(c.N, c.E).cpu() > 0
+    assert set(rt.unique().tolist()) <= {0.0, 1.0}
+    near = O.near_threshold(golden_scores(g, c), c.tau, WINDOW[c.dtype])
+    assert ((m != golden_mask(g, c)) & ~near).sum().item() == 0
+    exact = _exact(c, t, m)                  # truth for the mask the layer itself chose
+    assert O.rel_err(out.reshape(c.N, c.d).cpu().float(), exact) <= TOL[c.dtype]
+    if torch.equal(m, golden_mask(g, c)):
+        rows = torch.from_numpy(g["rows"])
+        ref = torch.from_numpy(g["out_execute_all" if c.glu else "out_naive"])
+        assert O.rel_err(out.reshape(c.N, c.d).cpu().float()[rows], ref) <= TOL[c.dtype]
+    moe.last_workspace(c.N, x.device).check_status()
+
+
+def test_other_forward_modes_match_oracle():
+    import d2dmoe_b200 as D
+    c = C.LayerCase("modes", 2, 37, 64, 32, 8, tau=0.6)
+    t = C.make_tensors(c)
+    moe = D.MoeficationMoE(c.name, c.d, c.E, True, c.H, torch.nn.ReLU)
+    moe.router = D.MoeficationRouter(c.d, c.E, width=c.R, depth=2, bias=False, activation="relu",
+                                     output_activation="abs")
+    moe.load_state_dict({"experts.w1": t["w1"], "experts.b1": t["b1"], "experts.w2": t["w2"],
+                         "last_bias": t["last_bias"], "router.layers.0.weight": t["wa"],
+                         "router.layers.2.weight": t["wb"]})
+    moe = moe.cuda()
+    x2d = t["x"].reshape(c.N, c.d)
+    s = O.router_scores(x2d, t["wa"], t["wb"])
+    for mode, mask in (("all", torch.ones(c.N, c.E, dtype=torch.bool)),
+                       ("topk", O.gate_topk(s, 3)),
+                       ("dynk", O.gate_dynk_cumulative(s, 0.6))):
+        moe.forward_mode, moe.k, moe.tau = mode, 3, 0.6
+        out, gd = moe(t["x"].cuda())
+        m = gd[c.name][0].reshape(c.N, c.E).cpu() > 0
+        assert (m != mask).sum().item() <= 2          # fp32 router ties only
+        ex = O.experts_ffn_exact(x2d, m, t["w1"], t["b1"], t["w2"]) + t["last_bias"].double()
+        assert O.rel_err(out.reshape(c.N, c.d).cpu(), ex) <= TOL["fp32"]
+
+
+def test_empty_and_error_paths():
+    from d2dmoe_b200 import ops, _capi
+    import d2dmoe_b200 as D
+    moe = D.MoeficationMoE("e", 64, 4, True, 32, torch.nn.ReLU).cuda()
+    moe.router = D.MoeficationRouter(64, 4, activation="relu", output_activation="abs").cuda()
+    moe.forward_mode, moe.tau = "dynk_max", 0.5
+    out, gd = moe(torch.empty(0, 3, 64, device="cuda"))
+    assert out.shape == (0, 3, 64) and gd["e"][0].shape == (0, 3, 4)
+    wsp = ops.Workspace.allocate(8, 4, "cuda")
+    small = ops.Workspace.allocate(8, 4, "cuda")
+    small.ws = small.ws[:0]
+    with pytest.raises(_capi.D2DError, match="WORKSPACE|BAD_ARG"):
+        ops.compact(small, 5000, 4)
+    # out-of-range token index: reported through the device status word, no fault
+    wsp.offsets.copy_(torch.tensor([0, 1, 1, 1, 1], dtype=torch.int32))
+    wsp.token_idx[:1] = 12345
+    x = torch.randn(8, 64, device="cuda")
+    w1 = torch.randn(4, 64, 32, device="cuda")
+    b1 = torch.randn(4, 32, device="cuda")
+    w2 = torch.randn(4, 32, 64, device="cuda")
+    out = torch.empty(8, 64, device="cuda")
+    ops.experts_ffn(x, wsp, w1, b1, w2, "relu", out)
+    with pytest.raises(_capi.D2DError, match="INDEX_RANGE"):
+        wsp.check_status()
+    assert torch.equal(out, torch.zeros_like(out))      # nothing was added
