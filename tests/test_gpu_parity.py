@@ -137,9 +137,11 @@ def test_module_forward(c):
     moe = moe.to(c.torch_dtype)
     moe.load_state_dict(sd, strict=True)
     if c.score_override:
+        dev_scores = t["scores"].cuda()
+
         class Fixed(torch.nn.Module):
             def forward(self, x):
-                return t["scores"].cuda()
+                return dev_scores
         moe.router = Fixed()
     moe = moe.cuda().eval()
     moe.forward_mode, moe.tau = "dynk_max", c.tau
