@@ -15,7 +15,7 @@ ACT = {"relu": 0, "gelu": 1, "tanh": 2, "leaky_relu": 3, "gelu_tanh": 4}
 
 OK = 0
 STATUS_NAMES = {0: "OK", 1: "BAD_ARG", 2: "UNSUPPORTED", 3: "LAUNCH", 4: "WORKSPACE",
-                5: "INDEX_RANGE", 6: "TIMEOUT", 7: "NO_DEVICE"}
+                5: "INDEX_RANGE", 6: "TIMEOUT", 7: "NO_DEVICE", 8: "SCRATCH_LIMIT"}
 
 _p, _i, _i64, _f, _sz = C.c_void_p, C.c_int, C.c_int64, C.c_float, C.c_size_t
 
@@ -30,6 +30,7 @@ SIGNATURES = {
     "d2d_expand_mask": (_i, [_p, _p, _i64, _i, _i, _p]),
     "d2d_pack_mask": (_i, [_p, _p, _i64, _i, _i, _p]),
     "d2d_compact": (_i, [_p, _p, _p, _i64, _i, _p, _sz, _p, _p]),
+    "d2d_compact_noalloc": (_i, [_p, _p, _p, _i64, _i, _p, _p]),
     "d2d_experts_ffn": (_i, [_p, _p, _p, _p, _p, _p, _p, _p, _p, _i, _i, _p,
                              _i64, _i, _i, _i, _i, _i, _p, _p]),
     "d2d_moe_forward": (_i, [_p, _p, _p, _p, _p, _f, _p, _p, _p, _p, _p, _p, _i, _p,
@@ -51,7 +52,7 @@ class D2DError(RuntimeError):
 def _load() -> C.CDLL:
     if not LIB_PATH.exists():
         raise ImportError(
-            f"{LIB_PATH} not found: build it with `python -m d2dmoe_b200.build` "
+            f"{LIB_PATH} not found: build it with `python d2dmoe_b200/build.py` "
             "(this package has no non-CUDA path)")
     cdll = C.CDLL(str(LIB_PATH))
     for name, (res, args) in SIGNATURES.items():

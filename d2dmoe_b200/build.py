@@ -1,6 +1,8 @@
 """Build the CUDA library in-tree with nvcc for sm_100a.
 
-    python -m d2dmoe_b200.build        # -> d2dmoe_b200/_lib/libd2dmoe_b200.so
+    python d2dmoe_b200/build.py        # -> d2dmoe_b200/_lib/libd2dmoe_b200.so
+
+Run it as a script (importing the package needs the library to exist already).
 
 nvcc cross-compiles without a GPU.  The library links the static CUDA runtime, so
 it needs nothing but the driver at load time.

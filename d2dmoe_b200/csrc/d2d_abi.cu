@@ -29,6 +29,9 @@ const char* d2d_strerror(int status) {
     case D2D_ERR_INDEX_RANGE: return "device: token index or offset out of range";
     case D2D_ERR_TIMEOUT: return "device: bounded wait ran out";
     case D2D_ERR_NO_DEVICE: return "no sm_100 CUDA device is current";
+    case D2D_ERR_SCRATCH_LIMIT:
+      return "size exceeds the built-in scratch array of the no-allocation entry point "
+             "(ceil(N/1024)*E must be <= 65536); use d2d_compact with a caller workspace";
     default: return "unknown status";
   }
 }

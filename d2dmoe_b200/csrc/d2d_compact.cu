@@ -164,3 +164,67 @@ int launch_compact(const uint32_t* mask_bits, int32_t* token_idx, int32_t* offse
 }
 
 }  // namespace d2d
+
+// ---------------------------------------------------------------------------
+// Compaction for callers that cannot allocate device memory.
+//
+// Some hosts of this library have no way to hand over a workspace: a plugin slot
+// that passes only the operator's inputs and outputs, a runtime whose memory pool
+// is frozen after start-up, or a latency-critical loop that must never enter the
+// driver's allocator.  For them the counts
+// table lives in the library itself, in a fixed device array that every GPU
+// loading the library holds until the process exits.
+//
+// Limit: D2D_NOALLOC_MAX_CELLS table cells = ceil(N/1024) * E; e.g. 262144 tokens
+// x 256 experts, or 1M tokens x 64 experts.  Larger requests are refused with
+// D2D_ERR_SCRATCH_LIMIT before anything is launched.
+//
+// The table is shared by every call in the process and keeps the previous call's
+// contents.  Nothing in it needs clearing: the count kernel writes every cell the
+// scatter kernel later reads (all E cells of each of the ceil(N/1024) chunks).
+// Two calls that run concurrently on one GPU (different streams) would overwrite
+// each other's counts: keep such calls on one stream or order them with events.
+// ---------------------------------------------------------------------------
+#define D2D_NOALLOC_MAX_CELLS (256 * 256)
+
+static __device__ __align__(256) int32_t g_noalloc_counts[D2D_NOALLOC_MAX_CELLS];
+
+namespace {
+
+constexpr int kMaxDevices = 64;
+int32_t* g_noalloc_ptr[kMaxDevices] = {nullptr};   // per device: address of the array there
+
+// Device address of g_noalloc_counts on the current device.  In host code the
+// array's name is only a handle for the runtime, not an address a kernel may use;
+// the address comes from cudaGetSymbolAddress, asked once per device while that
+// device is current.
+int noalloc_scratch(int32_t** out) {
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return D2D_ERR_NO_DEVICE;
+  int32_t* p = __atomic_load_n(&g_noalloc_ptr[dev], __ATOMIC_ACQUIRE);
+  if (!p) {
+    void* sym = nullptr;
+    if (cudaGetSymbolAddress(&sym, g_noalloc_counts) != cudaSuccess || !sym) {
+      cudaGetLastError();
+      return D2D_ERR_NO_DEVICE;
+    }
+    p = static_cast<int32_t*>(sym);
+    __atomic_store_n(&g_noalloc_ptr[dev], p, __ATOMIC_RELEASE);
+  }
+  *out = p;
+  return D2D_OK;
+}
+
+}  // namespace
+
+extern "C" int d2d_compact_noalloc(const uint32_t* mask_bits, int32_t* token_idx, int32_t* offsets,
+                                   int64_t N, int E, int* dev_status, d2d_stream_t stream) {
+  if (!mask_bits || !token_idx || !offsets || N < 0 || E < 1) return D2D_ERR_BAD_ARG;
+  const int64_t nchunks = d2d::ceil_div64(N > 0 ? N : 1, d2d::CHUNK);
+  if (nchunks * (int64_t)E > D2D_NOALLOC_MAX_CELLS) return D2D_ERR_SCRATCH_LIMIT;
+  int32_t* counts = nullptr;
+  const int rc = noalloc_scratch(&counts);   // first call on a device looks the address up
+  if (rc != D2D_OK) return rc;
+  return d2d::launch_compact(mask_bits, token_idx, offsets, N, E, counts, dev_status,
+                             (cudaStream_t)stream);
+}

@@ -57,7 +57,8 @@ enum d2d_status {
   D2D_ERR_WORKSPACE = 4,      /* workspace smaller than d2d_workspace_bytes says */
   D2D_ERR_INDEX_RANGE = 5,    /* device: a token index or offset out of range */
   D2D_ERR_TIMEOUT = 6,        /* device: a bounded wait ran out */
-  D2D_ERR_NO_DEVICE = 7       /* no sm_100 device is current */
+  D2D_ERR_NO_DEVICE = 7,      /* no sm_100 device is current */
+  D2D_ERR_SCRATCH_LIMIT = 8   /* size beyond the built-in scratch of a *_noalloc entry point */
 };
 
 /* Library identity. */
@@ -118,6 +119,21 @@ int d2d_pack_mask(const void* routing_tensor, uint32_t* mask_bits,
 int d2d_compact(const uint32_t* mask_bits, int32_t* token_idx, int32_t* offsets,
                 int64_t N, int E, void* ws, size_t ws_bytes,
                 int* dev_status, d2d_stream_t stream);
+
+/* d2d_compact for callers that cannot allocate device memory and so cannot supply
+ * `ws`: operator slots that receive only inputs and outputs, runtimes whose pool is
+ * frozen after start-up, loops that must stay out of the driver's allocator.
+ * (No counterpart upstream: the upstream path allocates its scratch inside every
+ * call.)  Same outputs as d2d_compact, bit for bit.  The counts table is a fixed
+ * array inside the library, held by every GPU that loads it until the process
+ * exits: 256 KiB, which covers ceil(N/1024) * E <= 65536 (e.g. N = 262144 with
+ * E = 256); beyond that the call returns D2D_ERR_SCRATCH_LIMIT and launches
+ * nothing.  It calls no allocating routine.  The first call on each device looks up
+ * the array's device address (with that device current); make that first call
+ * outside any stream capture.  All calls share the one array: calls that can run
+ * at the same time on one GPU (different streams, no ordering) race on it. */
+int d2d_compact_noalloc(const uint32_t* mask_bits, int32_t* token_idx, int32_t* offsets,
+                        int64_t N, int E, int* dev_status, d2d_stream_t stream);
 
 /* Grouped expert FFN with fused scatter-add:
  *   for every expert e and token t in its list:
