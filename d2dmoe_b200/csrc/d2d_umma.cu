@@ -1,11 +1,820 @@
+// bf16 tensor-core path (tcgen05 + TMEM) of the two MLP-shaped stages of the layer:
+//
+//   experts : per (expert e, 128 rows of its token list)
+//               h   = act(bf16(x[rows] W1[e]) + b1[e]) (* bf16(x[rows] W_up[e]))
+//               out[rows] += bf16(h W2[e])               red.global.add bf16x2
+//             fusing architectures/moe/moe_impls.py:93-180 (gathered first layer) and
+//             :244-301 (second layer + atomic add); h never leaves the SM.
+//   router  : per 128 consecutive tokens
+//               s = |bf16(relu(bf16(x Wa^T)) Wb^T)|, keep e iff s_e >= bf16(max s * mult)
+//             (architectures/moe/moefication.py:328-330 and :80-85), written as mask
+//             bits; the same CTA writes the layer output's initial value.
+//
+// Both are one persistent kernel: GEMM1 (K = d) into TMEM, an epilogue that turns
+// the accumulator into the bf16 A operand of GEMM2 in shared memory, GEMM2 (K = hidden
+// width) into a double-buffered TMEM accumulator, and a second epilogue.
+//
+// Warp roles (320 threads, one CTA per SM):
+//   warps 0-3  epilogues (warp w reads TMEM lanes 32w..32w+31 = tile rows)
+//   warp  4    TMEM allocation; lane 0 issues every tcgen05.mma / tcgen05.commit
+//   warp  5    lane 0 streams weight tiles with cp.async.bulk (TMA, 1-D) into ring B
+//   warps 6-9  gather token rows of x with 16-byte cp.async into ring A, writing the
+//              128-byte-swizzled K-major layout the MMA descriptors expect
+// Weights are packed once (d2d_prepack_*) into exactly the shared-memory images the
+// MMA reads, so a weight tile is one contiguous bulk copy.
+//
+// Every wait is bounded: when one runs out the kernel records D2D_ERR_TIMEOUT in the
+// status word, all roles leave their loops, TMEM is freed and the kernel returns.
 #include "d2d_umma_api.cuh"
+
 namespace d2d {
-bool umma_experts_supported(int, int, int, bool, int) { return false; }
-size_t umma_experts_packed_bytes(int, int, int, bool) { return 0; }
-int launch_prepack_experts(const void*, const void*, const void*, const void*, void*, int, int, int, cudaStream_t) { return D2D_ERR_UNSUPPORTED; }
-int launch_experts_umma(const void*, const int32_t*, const int32_t*, const void*, void*, int64_t, int, int, int, bool, int, int*, cudaStream_t) { return D2D_ERR_UNSUPPORTED; }
-bool umma_router_supported(int, int, int, int) { return false; }
-size_t umma_router_packed_bytes(int, int, int) { return 0; }
-int launch_prepack_router(const void*, const void*, void*, int, int, int, cudaStream_t) { return D2D_ERR_UNSUPPORTED; }
-int launch_router_mask_umma(const void*, const void*, float, uint32_t*, void*, const void*, int, void*, int64_t, int, int, int, int*, cudaStream_t) { return D2D_ERR_UNSUPPORTED; }
+namespace {
+
+constexpr int TILE_M = 128;
+constexpr int SLOT = TILE_M * 128;   // 16 KB: 128 rows x 64 bf16, also the weight slot size
+constexpr int NA = 4;                // ring A stages
+constexpr int LAG = 2;               // cp.async groups a producer thread keeps in flight
+constexpr int NB_MAX = 6;            // ring B stages
+constexpr int NTHREADS = 320;
+constexpr int MAX_E = 128;
+constexpr uint32_t WAIT_LIMIT = 1u << 22;
+constexpr int MODE_EXPERTS = 0, MODE_ROUTER = 1;
+
+struct Geo {
+  int kc1;       // d / 64
+  int nsub;      // weight subtiles per k-chunk of GEMM1 (gate/up, or two halves of a wide router)
+  int nsubw;     // columns per subtile (<= 128, multiple of 16)
+  int K2;        // GEMM2 reduction = hidden width held in shared memory
+  int kc2;       // ceil(K2 / 64)
+  int nd;        // GEMM2 output columns per chunk (<= 128, multiple of 16)
+  int nc;        // number of chunks
+  int nb;        // ring B stages
+  long long w1_bytes, bias_off, stride;   // packed layout per expert
+};
+
+struct Params {
+  const bf16* x;
+  long long N;
+  int d;
+  const uint8_t* packed;
+  Geo g;
+  // experts
+  const int32_t* token_idx;
+  const int32_t* offsets;
+  int E;
+  bf16* out;
+  int act, glu;
+  // router
+  float mult;
+  uint32_t* mask_bits;
+  bf16* scores;
+  const bf16* last_bias;
+  int add_residual;
+  bf16* out_init;
+  int* dev_status;
+};
+
+Geo experts_geo(int d, int H, bool glu) {
+  Geo g;
+  g.kc1 = d / 64;
+  g.nsub = glu ? 2 : 1;
+  g.nsubw = H;
+  g.K2 = H;
+  g.kc2 = (H + 63) / 64;
+  g.nd = (d % 128 == 0) ? 128 : 64;
+  g.nc = d / g.nd;
+  g.nb = NB_MAX;
+  g.w1_bytes = (long long)g.kc1 * g.nsub * g.nsubw * 128;
+  g.bias_off = g.w1_bytes + (long long)g.nc * g.kc2 * g.nd * 128;
+  g.stride = (g.bias_off + 512 + 1023) / 1024 * 1024;
+  return g;
 }
+
+Geo router_geo(int d, int R, int E) {
+  Geo g;
+  g.kc1 = d / 64;
+  g.nsub = R > 128 ? 2 : 1;
+  g.nsubw = R / g.nsub;
+  g.K2 = R;
+  g.kc2 = (R + 63) / 64;
+  g.nd = (E + 15) / 16 * 16;
+  g.nc = 1;
+  g.nb = g.kc2 > 2 ? 5 : NB_MAX;
+  g.w1_bytes = (long long)g.kc1 * g.nsub * g.nsubw * 128;
+  g.bias_off = g.w1_bytes + (long long)g.nc * g.kc2 * g.nd * 128;
+  g.stride = (g.bias_off + 512 + 1023) / 1024 * 1024;
+  return g;
+}
+
+// byte offset of element (row n, k) inside a K-major tile of 64 bf16 per row with the
+// 128-byte swizzle: 16-byte piece index XOR (row mod 8), 8-row groups 1024 bytes apart
+__host__ __device__ __forceinline__ int swz(int n, int k) {
+  return (n >> 3) * 1024 + (n & 7) * 128 + ((((k >> 3) ^ (n & 7)) & 7) << 4) + (k & 7) * 2;
+}
+
+// ---------------------------------------------------------------------------
+// PTX wrappers
+// ---------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t smem_u32(const void* p) {
+  return (uint32_t)__cvta_generic_to_shared(p);
+}
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes)
+               : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+// Bounded wait.  false = gave up (this thread's limit ran out, or another role did).
+__device__ __noinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag,
+                                       int* dev_status) {
+  for (uint32_t i = 0; i < WAIT_LIMIT; ++i) {
+    if (mbar_try_wait(bar, parity)) return true;
+    if (i > 64) {
+      __nanosleep(i > 4096 ? 256 : 32);
+      if ((i & 63) == 0 && *abort_flag) return false;
+    }
+  }
+  *abort_flag = 1;
+  report(dev_status, D2D_ERR_TIMEOUT);
+  return false;
+}
+__device__ __forceinline__ void bulk_g2s(uint32_t dst, const void* src, uint32_t bytes,
+                                         uint32_t bar) {
+  asm volatile(
+      "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::
+          "r"(dst),
+      "l"(src), "r"(bytes), "r"(bar)
+      : "memory");
+}
+__device__ __forceinline__ void cp_async16(uint32_t dst, const void* src) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() {
+  asm volatile("cp.async.commit_group;" ::: "memory");
+}
+template <int N>
+__device__ __forceinline__ void cp_async_wait() {
+  asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
+}
+__device__ __forceinline__ void fence_proxy_async() {
+  asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+}
+__device__ __forceinline__ void tc_fence_before() {
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+}
+__device__ __forceinline__ void tc_fence_after() {
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_alloc(uint32_t smem_dst, uint32_t ncols) {
+  asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_dst),
+               "r"(ncols)
+               : "memory");
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t ncols) {
+  asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols)
+               : "memory");
+}
+// D[tmem] (+)= A[smem] * B[smem], bf16 inputs, fp32 accumulate, issued by one thread
+__device__ __forceinline__ void umma_bf16(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc,
+                                          uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}" ::"r"(tmem_d),
+      "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+// mbarrier arrives once every MMA issued so far by this thread has completed
+__device__ __forceinline__ void umma_commit(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(
+                   bar)
+               : "memory");
+}
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t* v) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+      : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]),
+        "=r"(v[7]), "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]),
+        "=r"(v[14]), "=r"(v[15])
+      : "r"(taddr)
+      : "memory");
+}
+__device__ __forceinline__ void tmem_wait_ld() {
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void st_shared_v4(uint32_t addr, uint32_t a, uint32_t b, uint32_t c,
+                                             uint32_t d) {
+  asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(a), "r"(b), "r"(c),
+               "r"(d)
+               : "memory");
+}
+
+// Shared-memory matrix descriptor: K-major tile, 128-byte swizzle, 8-row groups 1024
+// bytes apart (stride byte offset), descriptor version 1 (sm_100).
+__device__ __forceinline__ uint64_t smem_desc(uint32_t addr) {
+  return (uint64_t)((addr >> 4) & 0x3FFF) | ((uint64_t)1 << 16) | ((uint64_t)(1024 >> 4) << 32) |
+         ((uint64_t)1 << 46) | ((uint64_t)2 << 61);
+}
+// Instruction descriptor, kind::f16: D fp32, A/B bf16, both K-major, M x N tile.
+__device__ __forceinline__ uint32_t instr_desc(int M, int N) {
+  return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(N >> 3) << 17) |
+         ((uint32_t)(M >> 4) << 24);
+}
+
+__device__ __forceinline__ float bfr(float v) { return __bfloat162float(__float2bfloat16_rn(v)); }
+__device__ __forceinline__ float nanmax(float a, float b) {
+  return (a != a || b != b) ? __int_as_float(0x7fc00000) : fmaxf(a, b);
+}
+
+// ---------------------------------------------------------------------------
+// shared-memory bookkeeping
+// ---------------------------------------------------------------------------
+struct Ctl {
+  unsigned long long fullA[NA], emptyA[NA], fullB[NB_MAX], emptyB[NB_MAX];
+  unsigned long long acc1_full, hs_full, hs_empty, acc2_full[2], acc2_empty[2];
+  uint32_t tmem_base;
+  int abort_flag;
+  int total_tiles;
+  int tstart[MAX_E + 1];
+};
+
+struct Tile {
+  int e, r0, nrows;
+};
+
+template <int MODE>
+__device__ __forceinline__ Tile tile_info(const Params& p, const Ctl* c, int tile) {
+  Tile t;
+  if (MODE == MODE_ROUTER) {
+    t.e = 0;
+    t.r0 = tile * TILE_M;
+    t.nrows = (int)min((long long)TILE_M, p.N - (long long)t.r0);
+  } else {
+    int lo = 0, hi = p.E;
+    while (hi - lo > 1) {
+      const int mid = (lo + hi) >> 1;
+      if (c->tstart[mid] <= tile) lo = mid; else hi = mid;
+    }
+    t.e = lo;
+    t.r0 = p.offsets[lo] + (tile - c->tstart[lo]) * TILE_M;
+    t.nrows = min(TILE_M, p.offsets[lo + 1] - t.r0);
+  }
+  return t;
+}
+
+// ---------------------------------------------------------------------------
+// roles
+// ---------------------------------------------------------------------------
+template <int MODE>
+__device__ void role_producer(const Params& p, Ctl* c, uint32_t ringA, int pt) {
+  const int lane = pt & 31, pw = pt >> 5;
+  const int j = lane & 7;
+  uint32_t dstoff[8];
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    const int row = pw * 32 + i * 4 + (lane >> 3);
+    dstoff[i] = (row >> 3) * 1024 + (row & 7) * 128 + ((j ^ (row & 7)) << 4);
+  }
+  volatile int* af = &c->abort_flag;
+  uint32_t it = 0;
+  for (int tile = blockIdx.x; tile < c->total_tiles; tile += gridDim.x) {
+    const Tile t = tile_info<MODE>(p, c, tile);
+    const bf16* src[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      int row = pw * 32 + i * 4 + (lane >> 3);
+      row = min(row, t.nrows - 1);      // rows past the tail repeat the last row; masked later
+      long long tok;
+      if (MODE == MODE_ROUTER) {
+        tok = (long long)t.r0 + row;
+      } else {
+        tok = p.token_idx[t.r0 + row];
+        if (tok < 0 || tok >= p.N) {
+          report(p.dev_status, D2D_ERR_INDEX_RANGE);
+          tok = 0;
+        }
+      }
+      src[i] = p.x + tok * p.d + j * 8;
+    }
+    for (int kc = 0; kc < p.g.kc1; ++kc) {
+      const uint32_t s = it % NA;
+      if (!mbar_wait(smem_u32(&c->emptyA[s]), ((it / NA) & 1) ^ 1, af, p.dev_status)) return;
+      const uint32_t base = ringA + s * SLOT;
+#pragma unroll
+      for (int i = 0; i < 8; ++i) cp_async16(base + dstoff[i], src[i] + kc * 64);
+      cp_async_commit();
+      if (it >= LAG) {
+        cp_async_wait<LAG>();
+        fence_proxy_async();
+        mbar_arrive(smem_u32(&c->fullA[(it - LAG) % NA]));
+      }
+      ++it;
+    }
+  }
+  cp_async_wait<0>();
+  fence_proxy_async();
+  for (uint32_t k = (it >= LAG ? it - LAG : 0); k < it; ++k) mbar_arrive(smem_u32(&c->fullA[k % NA]));
+}
+
+template <int MODE>
+__device__ void role_bulk(const Params& p, Ctl* c, uint32_t ringB) {
+  volatile int* af = &c->abort_flag;
+  const Geo& g = p.g;
+  uint32_t ib = 0;
+  for (int tile = blockIdx.x; tile < c->total_tiles; tile += gridDim.x) {
+    const Tile t = tile_info<MODE>(p, c, tile);
+    const uint8_t* pe = p.packed + (long long)t.e * g.stride;
+    const uint32_t b1 = g.nsubw * 128;
+    for (int i = 0; i < g.kc1 * g.nsub; ++i) {
+      const uint32_t s = ib % g.nb;
+      if (!mbar_wait(smem_u32(&c->emptyB[s]), ((ib / g.nb) & 1) ^ 1, af, p.dev_status)) return;
+      const uint32_t bar = smem_u32(&c->fullB[s]);
+      mbar_arrive_expect_tx(bar, b1);
+      bulk_g2s(ringB + s * SLOT, pe + (long long)i * b1, b1, bar);
+      ++ib;
+    }
+    const uint32_t b2 = g.nd * 128;
+    for (int i = 0; i < g.nc * g.kc2; ++i) {
+      const uint32_t s = ib % g.nb;
+      if (!mbar_wait(smem_u32(&c->emptyB[s]), ((ib / g.nb) & 1) ^ 1, af, p.dev_status)) return;
+      const uint32_t bar = smem_u32(&c->fullB[s]);
+      mbar_arrive_expect_tx(bar, b2);
+      bulk_g2s(ringB + s * SLOT, pe + g.w1_bytes + (long long)i * b2, b2, bar);
+      ++ib;
+    }
+  }
+}
+
+template <int MODE>
+__device__ void role_mma(const Params& p, Ctl* c, uint32_t ringA, uint32_t ringB, uint32_t hs,
+                         uint32_t tmem) {
+  volatile int* af = &c->abort_flag;
+  const Geo& g = p.g;
+  const uint32_t idesc1 = instr_desc(TILE_M, g.nsubw), idesc2 = instr_desc(TILE_M, g.nd);
+  uint32_t ia = 0, ib = 0, g2 = 0, tc = 0;
+  for (int tile = blockIdx.x; tile < c->total_tiles; tile += gridDim.x) {
+    // ---- GEMM1: acc1[sub] = A(rows, d) * W1sub(d, nsubw) ------------------------
+    for (int kc = 0; kc < g.kc1; ++kc) {
+      const uint32_t sa = ia % NA;
+      if (!mbar_wait(smem_u32(&c->fullA[sa]), (ia / NA) & 1, af, p.dev_status)) return;
+      uint32_t sb[2];
+      for (int sub = 0; sub < g.nsub; ++sub) {
+        sb[sub] = ib % g.nb;
+        if (!mbar_wait(smem_u32(&c->fullB[sb[sub]]), (ib / g.nb) & 1, af, p.dev_status)) return;
+        ++ib;
+      }
+      tc_fence_after();
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        const uint64_t ad = smem_desc(ringA + sa * SLOT + k * 32);
+        for (int sub = 0; sub < g.nsub; ++sub)
+          umma_bf16(tmem + sub * 128, ad, smem_desc(ringB + sb[sub] * SLOT + k * 32), idesc1,
+                    (kc | k) != 0);
+      }
+      umma_commit(smem_u32(&c->emptyA[sa]));
+      for (int sub = 0; sub < g.nsub; ++sub) umma_commit(smem_u32(&c->emptyB[sb[sub]]));
+      ++ia;
+    }
+    umma_commit(smem_u32(&c->acc1_full));
+    // ---- GEMM2: acc2[buf] = Hs(rows, K2) * W2chunk(K2, nd) ----------------------
+    if (!mbar_wait(smem_u32(&c->hs_full), tc & 1, af, p.dev_status)) return;
+    tc_fence_after();
+    for (int nci = 0; nci < g.nc; ++nci) {
+      const uint32_t buf = g2 & 1;
+      if (!mbar_wait(smem_u32(&c->acc2_empty[buf]), ((g2 >> 1) & 1) ^ 1, af, p.dev_status)) return;
+      tc_fence_after();
+      for (int k2 = 0; k2 < g.kc2; ++k2) {
+        const uint32_t s = ib % g.nb;
+        if (!mbar_wait(smem_u32(&c->fullB[s]), (ib / g.nb) & 1, af, p.dev_status)) return;
+        tc_fence_after();
+        const int ksteps = min(4, (g.K2 - k2 * 64) >> 4);
+        for (int k = 0; k < ksteps; ++k)
+          umma_bf16(tmem + 256 + buf * 128, smem_desc(hs + k2 * SLOT + k * 32),
+                    smem_desc(ringB + s * SLOT + k * 32), idesc2, (k2 | k) != 0);
+        umma_commit(smem_u32(&c->emptyB[s]));
+        ++ib;
+      }
+      umma_commit(smem_u32(&c->acc2_full[buf]));
+      ++g2;
+    }
+    umma_commit(smem_u32(&c->hs_empty));
+    ++tc;
+  }
+}
+
+template <int MODE>
+__device__ void role_epilogue(const Params& p, Ctl* c, uint32_t hs, uint32_t tmem, int r) {
+  volatile int* af = &c->abort_flag;
+  const Geo& g = p.g;
+  const uint32_t lane_base = (uint32_t)(r & ~31) << 16;   // this warp's TMEM lane quarter
+  const uint32_t hs_row = hs + (r >> 3) * 1024 + (r & 7) * 128;
+  uint32_t g2 = 0, tc = 0;
+  for (int tile = blockIdx.x; tile < c->total_tiles; tile += gridDim.x) {
+    const Tile t = tile_info<MODE>(p, c, tile);
+    if (MODE == MODE_ROUTER && p.out_init) {
+      // initial value of the layer output for this tile's tokens: last_bias (+ x)
+      const int v8 = p.d >> 3;
+      for (int i = r; i < t.nrows * v8; i += TILE_M) {
+        const int row = i / v8, c8 = i % v8;
+        const long long off = ((long long)t.r0 + row) * p.d + c8 * 8;
+        uint4 o = make_uint4(0u, 0u, 0u, 0u);
+        if (p.last_bias) o = *reinterpret_cast<const uint4*>(p.last_bias + c8 * 8);
+        if (p.add_residual) {
+          const uint4 xv = *reinterpret_cast<const uint4*>(p.x + off);
+          const __nv_bfloat162* a = reinterpret_cast<const __nv_bfloat162*>(&o);
+          const __nv_bfloat162* b = reinterpret_cast<const __nv_bfloat162*>(&xv);
+          uint32_t w[4];
+#pragma unroll
+          for (int q = 0; q < 4; ++q) {
+            const float2 fa = __bfloat1622float2(a[q]), fb = __bfloat1622float2(b[q]);
+            w[q] = pack_bf16x2(fa.x + fb.x, fa.y + fb.y);
+          }
+          o = make_uint4(w[0], w[1], w[2], w[3]);
+        }
+        *reinterpret_cast<uint4*>(p.out_init + off) = o;
+      }
+    }
+    // ---- epilogue 1: acc1 -> bf16 hidden tile in shared memory ------------------
+    if (!mbar_wait(smem_u32(&c->acc1_full), tc & 1, af, p.dev_status)) return;
+    if (!mbar_wait(smem_u32(&c->hs_empty), (tc & 1) ^ 1, af, p.dev_status)) return;
+    tc_fence_after();
+    const float* bias = reinterpret_cast<const float*>(p.packed + (long long)t.e * g.stride + g.bias_off);
+    const int nsub1 = (MODE == MODE_ROUTER) ? g.nsub : 1;
+    for (int sub = 0; sub < nsub1; ++sub) {
+      for (int c0 = 0; c0 < g.nsubw; c0 += 16) {
+        uint32_t v[16], u[16];
+        tmem_ld16(tmem + lane_base + sub * 128 + c0, v);
+        if (MODE == MODE_EXPERTS && p.glu) tmem_ld16(tmem + lane_base + 128 + c0, u);
+        tmem_wait_ld();
+        uint32_t w[8];
+#pragma unroll
+        for (int q = 0; q < 8; ++q) {
+          float h0 = bfr(__uint_as_float(v[2 * q])), h1 = bfr(__uint_as_float(v[2 * q + 1]));
+          if (MODE == MODE_ROUTER) {
+            h0 = fmaxf(h0, 0.f);
+            h1 = fmaxf(h1, 0.f);
+          } else {
+            h0 = bfr(activate(bfr(h0 + bias[c0 + 2 * q]), p.act));
+            h1 = bfr(activate(bfr(h1 + bias[c0 + 2 * q + 1]), p.act));
+            if (p.glu) {
+              h0 *= bfr(__uint_as_float(u[2 * q]));
+              h1 *= bfr(__uint_as_float(u[2 * q + 1]));
+            }
+          }
+          w[q] = pack_bf16x2(h0, h1);
+        }
+        const int hc = sub * g.nsubw + c0;          // hidden column of v[0]
+        const uint32_t base = hs_row + (hc >> 6) * SLOT;
+        const int j0 = (hc & 63) >> 3;
+        st_shared_v4(base + (((j0) ^ (r & 7)) << 4), w[0], w[1], w[2], w[3]);
+        st_shared_v4(base + (((j0 + 1) ^ (r & 7)) << 4), w[4], w[5], w[6], w[7]);
+      }
+    }
+    fence_proxy_async();
+    tc_fence_before();
+    mbar_arrive(smem_u32(&c->hs_full));
+    // ---- epilogue 2 -------------------------------------------------------------
+    if (MODE == MODE_EXPERTS) {
+      long long tok = -1;
+      if (r < t.nrows) {
+        tok = p.token_idx[t.r0 + r];
+        if (tok < 0 || tok >= p.N) tok = -1;     // reported by the producer
+      }
+      for (int nci = 0; nci < g.nc; ++nci) {
+        const uint32_t buf = g2 & 1;
+        if (!mbar_wait(smem_u32(&c->acc2_full[buf]), (g2 >> 1) & 1, af, p.dev_status)) return;
+        tc_fence_after();
+        bf16* orow = p.out + (tok < 0 ? 0 : tok) * p.d + nci * g.nd;
+        for (int c0 = 0; c0 < g.nd; c0 += 16) {
+          uint32_t v[16];
+          tmem_ld16(tmem + lane_base + 256 + buf * 128 + c0, v);
+          tmem_wait_ld();
+          if (tok >= 0) {
+            uint32_t w[8];
+#pragma unroll
+            for (int q = 0; q < 8; ++q)
+              w[q] = pack_bf16x2(__uint_as_float(v[2 * q]), __uint_as_float(v[2 * q + 1]));
+            red_add_bf16x8(orow + c0, w[0], w[1], w[2], w[3]);
+            red_add_bf16x8(orow + c0 + 8, w[4], w[5], w[6], w[7]);
+          }
+        }
+        tc_fence_before();
+        mbar_arrive(smem_u32(&c->acc2_empty[buf]));
+        ++g2;
+      }
+    } else {
+      const uint32_t buf = g2 & 1;
+      if (!mbar_wait(smem_u32(&c->acc2_full[buf]), (g2 >> 1) & 1, af, p.dev_status)) return;
+      tc_fence_after();
+      const int E = p.E;
+      const long long trow = (long long)t.r0 + r;
+      float m = -INFINITY;
+      for (int c0 = 0; c0 < g.nd; c0 += 16) {
+        uint32_t v[16];
+        tmem_ld16(tmem + lane_base + 256 + buf * 128 + c0, v);
+        tmem_wait_ld();
+#pragma unroll
+        for (int q = 0; q < 16; ++q)
+          if (c0 + q < E) m = nanmax(m, fabsf(bfr(__uint_as_float(v[q]))));
+      }
+      const float thr = bfr(__fmul_rn(m, p.mult));
+      const int nw = (E + 31) >> 5;
+      uint32_t word = 0;
+      for (int c0 = 0; c0 < g.nd; c0 += 16) {
+        uint32_t v[16];
+        tmem_ld16(tmem + lane_base + 256 + buf * 128 + c0, v);
+        tmem_wait_ld();
+#pragma unroll
+        for (int q = 0; q < 16; ++q) {
+          const float s = fabsf(bfr(__uint_as_float(v[q])));
+          if (c0 + q < E) {
+            if (s >= thr) word |= 1u << ((c0 + q) & 31);
+            if (p.scores && r < t.nrows) p.scores[trow * E + c0 + q] = __float2bfloat16_rn(s);
+          }
+        }
+        if (((c0 + 16) & 31) == 0 || c0 + 16 >= g.nd) {
+          const int jw = c0 >> 5;
+          if (r < t.nrows && jw < nw) p.mask_bits[trow * nw + jw] = word;
+          word = 0;
+        }
+      }
+      tc_fence_before();
+      mbar_arrive(smem_u32(&c->acc2_empty[buf]));
+      ++g2;
+    }
+    ++tc;
+  }
+}
+
+// ---------------------------------------------------------------------------
+// kernel
+// ---------------------------------------------------------------------------
+template <int MODE>
+__global__ void __launch_bounds__(NTHREADS, 1) mlp_tiles_kernel(const Params p) {
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t raw = smem_u32(smem_raw);
+  const uint32_t base = (raw + 1023u) & ~1023u;
+  uint8_t* aligned = smem_raw + (base - raw);
+  const uint32_t ringA = base;
+  const uint32_t ringB = ringA + NA * SLOT;
+  const uint32_t hs = ringB + p.g.nb * SLOT;
+  Ctl* c = reinterpret_cast<Ctl*>(aligned + (size_t)(NA + p.g.nb + p.g.kc2) * SLOT);
+  const int tid = threadIdx.x, warp = tid >> 5;
+
+  if (tid == 0) {
+    for (int i = 0; i < NA; ++i) {
+      mbar_init(smem_u32(&c->fullA[i]), 128);
+      mbar_init(smem_u32(&c->emptyA[i]), 1);
+    }
+    for (int i = 0; i < NB_MAX; ++i) {
+      mbar_init(smem_u32(&c->fullB[i]), 1);
+      mbar_init(smem_u32(&c->emptyB[i]), 1);
+    }
+    mbar_init(smem_u32(&c->acc1_full), 1);
+    mbar_init(smem_u32(&c->hs_full), 128);
+    mbar_init(smem_u32(&c->hs_empty), 1);
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(smem_u32(&c->acc2_full[i]), 1);
+      mbar_init(smem_u32(&c->acc2_empty[i]), 128);
+    }
+    c->abort_flag = 0;
+    if (MODE == MODE_ROUTER) {
+      c->total_tiles = (int)((p.N + TILE_M - 1) / TILE_M);
+    } else {
+      int run = 0;
+      for (int e = 0; e < p.E; ++e) {
+        c->tstart[e] = run;
+        const int n = p.offsets[e + 1] - p.offsets[e];
+        if (n < 0 || p.offsets[e + 1] > p.N * (long long)p.E) report(p.dev_status, D2D_ERR_INDEX_RANGE);
+        run += n > 0 ? (n + TILE_M - 1) / TILE_M : 0;
+      }
+      c->tstart[p.E] = run;
+      c->total_tiles = run;
+    }
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    fence_proxy_async();
+  }
+  if (warp == 4) tmem_alloc(smem_u32(&c->tmem_base), 512);
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = c->tmem_base;
+
+  if (warp < 4) {
+    role_epilogue<MODE>(p, c, hs, tmem, tid);
+  } else if (warp == 4) {
+    if ((tid & 31) == 0) role_mma<MODE>(p, c, ringA, ringB, hs, tmem);
+  } else if (warp == 5) {
+    if ((tid & 31) == 0) role_bulk<MODE>(p, c, ringB);
+  } else {
+    role_producer<MODE>(p, c, ringA, tid - 192);
+    cp_async_wait<0>();
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 4) {
+    tc_fence_after();
+    tmem_dealloc(tmem, 512);
+  }
+}
+
+// ---------------------------------------------------------------------------
+// weight packing
+// ---------------------------------------------------------------------------
+__global__ void prepack_experts_kernel(const bf16* __restrict__ w1, const bf16* __restrict__ b1,
+                                       const bf16* __restrict__ w_up, const bf16* __restrict__ w2,
+                                       uint8_t* __restrict__ packed, Geo g, int d, int E, int H) {
+  const int e = blockIdx.y;
+  uint8_t* pe = packed + (long long)e * g.stride;
+  const long long n1 = (long long)g.kc1 * g.nsub * g.nsubw * 64;
+  const long long n2 = (long long)g.nc * g.kc2 * g.nd * 64;
+  const bf16 zero = __float2bfloat16_rn(0.f);
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n1 + n2 + g.nsubw;
+       i += (long long)gridDim.x * blockDim.x) {
+    if (i < n1) {
+      const int k = (int)(i % 64);
+      const int n = (int)((i / 64) % g.nsubw);
+      const int sub = (int)((i / (64LL * g.nsubw)) % g.nsub);
+      const int kc = (int)(i / (64LL * g.nsubw * g.nsub));
+      const bf16* src = sub == 0 ? w1 : w_up;
+      const bf16 v = src[((long long)e * d + kc * 64 + k) * H + n];
+      *reinterpret_cast<bf16*>(pe + (long long)(kc * g.nsub + sub) * g.nsubw * 128 + swz(n, k)) = v;
+    } else if (i < n1 + n2) {
+      const long long q = i - n1;
+      const int k = (int)(q % 64);
+      const int n = (int)((q / 64) % g.nd);
+      const int k2 = (int)((q / (64LL * g.nd)) % g.kc2);
+      const int nci = (int)(q / (64LL * g.nd * g.kc2));
+      const int kk = k2 * 64 + k;
+      const bf16 v = kk < H ? w2[((long long)e * H + kk) * d + nci * g.nd + n] : zero;
+      *reinterpret_cast<bf16*>(pe + g.w1_bytes + (long long)(nci * g.kc2 + k2) * g.nd * 128 +
+                               swz(n, k)) = v;
+    } else {
+      const int h = (int)(i - n1 - n2);
+      reinterpret_cast<float*>(pe + g.bias_off)[h] =
+          b1 ? __bfloat162float(b1[(long long)e * H + h]) : 0.f;
+    }
+  }
+}
+
+__global__ void prepack_router_kernel(const bf16* __restrict__ wa, const bf16* __restrict__ wb,
+                                      uint8_t* __restrict__ packed, Geo g, int d, int R, int E) {
+  const long long n1 = (long long)g.kc1 * g.nsub * g.nsubw * 64;
+  const long long n2 = (long long)g.kc2 * g.nd * 64;
+  const bf16 zero = __float2bfloat16_rn(0.f);
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n1 + n2;
+       i += (long long)gridDim.x * blockDim.x) {
+    if (i < n1) {
+      const int k = (int)(i % 64);
+      const int n = (int)((i / 64) % g.nsubw);
+      const int sub = (int)((i / (64LL * g.nsubw)) % g.nsub);
+      const int kc = (int)(i / (64LL * g.nsubw * g.nsub));
+      const bf16 v = wa[(long long)(sub * g.nsubw + n) * d + kc * 64 + k];
+      *reinterpret_cast<bf16*>(packed + (long long)(kc * g.nsub + sub) * g.nsubw * 128 +
+                               swz(n, k)) = v;
+    } else {
+      const long long q = i - n1;
+      const int k = (int)(q % 64);
+      const int n = (int)((q / 64) % g.nd);
+      const int k2 = (int)(q / (64LL * g.nd));
+      const int kk = k2 * 64 + k;
+      const bf16 v = (n < E && kk < R) ? wb[(long long)n * R + kk] : zero;
+      *reinterpret_cast<bf16*>(packed + g.w1_bytes + (long long)k2 * g.nd * 128 + swz(n, k)) = v;
+    }
+  }
+}
+
+int sm_count() {
+  static int n = 0;
+  if (n == 0) {
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess) return 148;
+    if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0)
+      n = 148;
+  }
+  return n;
+}
+
+size_t smem_bytes(const Geo& g) {
+  return 1024 + (size_t)(NA + g.nb + g.kc2) * SLOT + sizeof(Ctl) + 64;
+}
+
+template <int MODE>
+int launch(const Params& p, long long max_tiles, cudaStream_t s) {
+  const size_t smem = smem_bytes(p.g);
+  auto k = mlp_tiles_kernel<MODE>;
+  static bool attr_set[2] = {false, false};
+  static size_t attr_val[2] = {0, 0};
+  if (!attr_set[MODE] || attr_val[MODE] < smem) {
+    if (cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) !=
+        cudaSuccess) {
+      cudaGetLastError();
+      return D2D_ERR_LAUNCH;
+    }
+    attr_set[MODE] = true;
+    attr_val[MODE] = smem;
+  }
+  long long grid = max_tiles < sm_count() ? max_tiles : sm_count();
+  if (grid < 1) grid = 1;
+  k<<<(unsigned)grid, NTHREADS, smem, s>>>(p);
+  return cudaGetLastError() == cudaSuccess ? D2D_OK : D2D_ERR_LAUNCH;
+}
+
+}  // namespace
+
+// ---------------------------------------------------------------------------
+// host interface
+// ---------------------------------------------------------------------------
+bool umma_experts_supported(int d, int E, int H, bool glu, int dtype) {
+  (void)glu;
+  return dtype == D2D_BF16 && d >= 64 && d % 64 == 0 && (d % 128 == 0 || d == 64) && H >= 16 &&
+         H <= 128 && H % 16 == 0 && E >= 1 && E <= MAX_E;
+}
+
+size_t umma_experts_packed_bytes(int d, int E, int H, bool glu) {
+  return (size_t)experts_geo(d, H, glu).stride * (size_t)E;
+}
+
+int launch_prepack_experts(const void* w1, const void* b1, const void* w_up, const void* w2,
+                           void* packed, int d, int E, int H, cudaStream_t s) {
+  const Geo g = experts_geo(d, H, w_up != nullptr);
+  dim3 grid(64, E);
+  prepack_experts_kernel<<<grid, 256, 0, s>>>((const bf16*)w1, (const bf16*)b1, (const bf16*)w_up,
+                                              (const bf16*)w2, (uint8_t*)packed, g, d, E, H);
+  return cudaGetLastError() == cudaSuccess ? D2D_OK : D2D_ERR_LAUNCH;
+}
+
+int launch_experts_umma(const void* x, const int32_t* token_idx, const int32_t* offsets,
+                        const void* packed, void* out, int64_t N, int d, int E, int H, bool glu,
+                        int act, int* dev_status, cudaStream_t s) {
+  Params p = {};
+  p.x = (const bf16*)x;
+  p.N = N;
+  p.d = d;
+  p.packed = (const uint8_t*)packed;
+  p.g = experts_geo(d, H, glu);
+  p.token_idx = token_idx;
+  p.offsets = offsets;
+  p.E = E;
+  p.out = (bf16*)out;
+  p.act = act;
+  p.glu = glu ? 1 : 0;
+  p.dev_status = dev_status;
+  const long long max_tiles = (N * (long long)E + TILE_M - 1) / TILE_M + E;
+  return launch<MODE_EXPERTS>(p, max_tiles, s);
+}
+
+bool umma_router_supported(int d, int R, int E, int dtype) {
+  return dtype == D2D_BF16 && d >= 64 && d % 64 == 0 && R >= 16 && R % 16 == 0 &&
+         (R <= 128 || R == 256) && E >= 1 && E <= MAX_E;
+}
+
+size_t umma_router_packed_bytes(int d, int R, int E) { return (size_t)router_geo(d, R, E).stride; }
+
+int launch_prepack_router(const void* wa, const void* wb, void* packed, int d, int R, int E,
+                          cudaStream_t s) {
+  const Geo g = router_geo(d, R, E);
+  prepack_router_kernel<<<64, 256, 0, s>>>((const bf16*)wa, (const bf16*)wb, (uint8_t*)packed, g, d,
+                                           R, E);
+  return cudaGetLastError() == cudaSuccess ? D2D_OK : D2D_ERR_LAUNCH;
+}
+
+int launch_router_mask_umma(const void* x, const void* packed, float mult, uint32_t* mask_bits,
+                            void* scores, const void* last_bias, int add_residual, void* out_init,
+                            int64_t N, int d, int R, int E, int* dev_status, cudaStream_t s) {
+  Params p = {};
+  p.x = (const bf16*)x;
+  p.N = N;
+  p.d = d;
+  p.packed = (const uint8_t*)packed;
+  p.g = router_geo(d, R, E);
+  p.E = E;
+  p.mult = mult;
+  p.mask_bits = mask_bits;
+  p.scores = (bf16*)scores;
+  p.last_bias = (const bf16*)last_bias;
+  p.add_residual = add_residual;
+  p.out_init = (bf16*)out_init;
+  p.dev_status = dev_status;
+  return launch<MODE_ROUTER>(p, (N + TILE_M - 1) / TILE_M, s);
+}
+
+}  // namespace d2d
