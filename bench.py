@@ -296,6 +296,14 @@ def run_ours(args):
     ms = timed(lambda: step(1.0 - HEADLINE_TAU), steps, warmup, dist)
     clocks = sampler.stop() if sampler else None
     value = world * tokens_step * steps / (ms * 1e-3)
+    if args.quick:
+        if dist is not None:
+            dist.destroy_process_group()
+        if rank == 0:
+            print(json.dumps({"metric": "moe_ffn_layer_tokens_per_s", "value": value,
+                              "unit": "tokens/s", "ms_per_step": ms / steps, "quick": True,
+                              "layers": LAYERS, "tau_cfg": HEADLINE_TAU, "clocks": clocks}))
+        return
 
     # ---- tau sweep ----------------------------------------------------------------
     sweep = []
@@ -408,13 +416,21 @@ def run_ours(args):
 
 
 def main():
+    global LAYERS, HEADLINE_TAU
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--layers", type=int, default=LAYERS,
+                    help="profiling aid: run fewer than the 12 layers (not a bench value)")
+    ap.add_argument("--tau", type=float, default=HEADLINE_TAU,
+                    help="profiling aid: tau_cfg of the headline measurement")
+    ap.add_argument("--quick", action="store_true",
+                    help="profiling aid: headline timing only (no sweep, stages, e2e, CPU leg)")
     args = ap.parse_args()
+    LAYERS, HEADLINE_TAU = args.layers, args.tau
     if args.impl == "reference":
         run_reference(args)
     else:

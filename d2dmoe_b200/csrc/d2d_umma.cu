@@ -32,9 +32,9 @@ namespace {
 
 constexpr int TILE_M = 128;
 constexpr int SLOT = TILE_M * 128;   // 16 KB: 128 rows x 64 bf16, also the weight slot size
-constexpr int NA = 4;                // ring A stages
-constexpr int LAG = 2;               // cp.async groups a producer thread keeps in flight
+constexpr int NA = 6;                // ring A stages
 constexpr int NB_MAX = 6;            // ring B stages
+constexpr int SLOTS_TOTAL = 13;      // ring A + ring B + hidden tile chunks (208 KB)
 constexpr int NTHREADS = 320;
 constexpr int MAX_E = 128;
 constexpr uint32_t WAIT_LIMIT = 1u << 22;
@@ -83,7 +83,7 @@ Geo experts_geo(int d, int H, bool glu) {
   g.kc2 = (H + 63) / 64;
   g.nd = (d % 128 == 0) ? 128 : 64;
   g.nc = d / g.nd;
-  g.nb = NB_MAX;
+  g.nb = min(NB_MAX, SLOTS_TOTAL - NA - g.kc2);
   g.w1_bytes = (long long)g.kc1 * g.nsub * g.nsubw * 128;
   g.bias_off = g.w1_bytes + (long long)g.nc * g.kc2 * g.nd * 128;
   g.stride = (g.bias_off + 512 + 1023) / 1024 * 1024;
@@ -99,7 +99,7 @@ Geo router_geo(int d, int R, int E) {
   g.kc2 = (R + 63) / 64;
   g.nd = (E + 15) / 16 * 16;
   g.nc = 1;
-  g.nb = g.kc2 > 2 ? 5 : NB_MAX;
+  g.nb = min(NB_MAX, SLOTS_TOTAL - NA - g.kc2);
   g.w1_bytes = (long long)g.kc1 * g.nsub * g.nsubw * 128;
   g.bias_off = g.w1_bytes + (long long)g.nc * g.kc2 * g.nd * 128;
   g.stride = (g.bias_off + 512 + 1023) / 1024 * 1024;
@@ -164,12 +164,13 @@ __device__ __forceinline__ void bulk_g2s(uint32_t dst, const void* src, uint32_t
 __device__ __forceinline__ void cp_async16(uint32_t dst, const void* src) {
   asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
 }
-__device__ __forceinline__ void cp_async_commit() {
-  asm volatile("cp.async.commit_group;" ::: "memory");
+// the mbarrier receives one arrival (already counted in its expected count) once every
+// cp.async this thread has issued so far has landed
+__device__ __forceinline__ void cp_async_arrive_noinc(uint32_t bar) {
+  asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(bar) : "memory");
 }
-template <int N>
-__device__ __forceinline__ void cp_async_wait() {
-  asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
+__device__ __forceinline__ void cp_async_wait_all() {
+  asm volatile("cp.async.wait_all;" ::: "memory");
 }
 __device__ __forceinline__ void fence_proxy_async() {
   asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -319,18 +320,10 @@ __device__ void role_producer(const Params& p, Ctl* c, uint32_t ringA, int pt) {
       const uint32_t base = ringA + s * SLOT;
 #pragma unroll
       for (int i = 0; i < 8; ++i) cp_async16(base + dstoff[i], src[i] + kc * 64);
-      cp_async_commit();
-      if (it >= LAG) {
-        cp_async_wait<LAG>();
-        fence_proxy_async();
-        mbar_arrive(smem_u32(&c->fullA[(it - LAG) % NA]));
-      }
+      cp_async_arrive_noinc(smem_u32(&c->fullA[s]));
       ++it;
     }
   }
-  cp_async_wait<0>();
-  fence_proxy_async();
-  for (uint32_t k = (it >= LAG ? it - LAG : 0); k < it; ++k) mbar_arrive(smem_u32(&c->fullA[k % NA]));
 }
 
 template <int MODE>
@@ -380,6 +373,7 @@ __device__ void role_mma(const Params& p, Ctl* c, uint32_t ringA, uint32_t ringB
         if (!mbar_wait(smem_u32(&c->fullB[sb[sub]]), (ib / g.nb) & 1, af, p.dev_status)) return;
         ++ib;
       }
+      fence_proxy_async();     // rows arrived through the generic proxy (cp.async)
       tc_fence_after();
 #pragma unroll
       for (int k = 0; k < 4; ++k) {
@@ -395,6 +389,7 @@ __device__ void role_mma(const Params& p, Ctl* c, uint32_t ringA, uint32_t ringB
     umma_commit(smem_u32(&c->acc1_full));
     // ---- GEMM2: acc2[buf] = Hs(rows, K2) * W2chunk(K2, nd) ----------------------
     if (!mbar_wait(smem_u32(&c->hs_full), tc & 1, af, p.dev_status)) return;
+    fence_proxy_async();       // hidden tile was written with ordinary shared stores
     tc_fence_after();
     for (int nci = 0; nci < g.nc; ++nci) {
       const uint32_t buf = g2 & 1;
@@ -487,7 +482,6 @@ __device__ void role_epilogue(const Params& p, Ctl* c, uint32_t hs, uint32_t tme
         st_shared_v4(base + (((j0 + 1) ^ (r & 7)) << 4), w[4], w[5], w[6], w[7]);
       }
     }
-    fence_proxy_async();
     tc_fence_before();
     mbar_arrive(smem_u32(&c->hs_full));
     // ---- epilogue 2 -------------------------------------------------------------
@@ -625,7 +619,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) mlp_tiles_kernel(const Params p) 
     if ((tid & 31) == 0) role_bulk<MODE>(p, c, ringB);
   } else {
     role_producer<MODE>(p, c, ringA, tid - 192);
-    cp_async_wait<0>();
+    cp_async_wait_all();
   }
 
   tc_fence_before();
