@@ -32,9 +32,9 @@ namespace {
 
 constexpr int TILE_M = 128;
 constexpr int SLOT = TILE_M * 128;   // 16 KB: 128 rows x 64 bf16, also the weight slot size
-constexpr int NA = 6;                // ring A stages
-constexpr int NB_MAX = 6;            // ring B stages
-constexpr int SLOTS_TOTAL = 13;      // ring A + ring B + hidden tile chunks (208 KB)
+constexpr int NA_MAX = 6;            // ring A stages (upper bound)
+constexpr int NB_MAX = 6;            // ring B stages (upper bound)
+constexpr int SLOTS_TOTAL = 13;      // ring A + ring B + hidden tile + staging (208 KB)
 constexpr int NTHREADS = 320;
 constexpr int MAX_E = 128;
 constexpr uint32_t WAIT_LIMIT = 1u << 22;
@@ -49,6 +49,8 @@ struct Geo {
   int nd;        // GEMM2 output columns per chunk (<= 128, multiple of 16)
   int nc;        // number of chunks
   int nb;        // ring B stages
+  int na;        // ring A stages
+  int stg;       // 16 KB slots of epilogue staging (experts: 2 = 32 rows x 256 B per warp)
   long long w1_bytes, bias_off, stride;   // packed layout per expert
 };
 
@@ -83,7 +85,9 @@ Geo experts_geo(int d, int H, bool glu) {
   g.kc2 = (H + 63) / 64;
   g.nd = (d % 128 == 0) ? 128 : 64;
   g.nc = d / g.nd;
-  g.nb = min(NB_MAX, SLOTS_TOTAL - NA - g.kc2);
+  g.stg = 2;
+  g.na = glu ? 4 : 5;
+  g.nb = min(NB_MAX, SLOTS_TOTAL - g.na - g.kc2 - g.stg);
   g.w1_bytes = (long long)g.kc1 * g.nsub * g.nsubw * 128;
   g.bias_off = g.w1_bytes + (long long)g.nc * g.kc2 * g.nd * 128;
   g.stride = (g.bias_off + 512 + 1023) / 1024 * 1024;
@@ -99,7 +103,9 @@ Geo router_geo(int d, int R, int E) {
   g.kc2 = (R + 63) / 64;
   g.nd = (E + 15) / 16 * 16;
   g.nc = 1;
-  g.nb = min(NB_MAX, SLOTS_TOTAL - NA - g.kc2);
+  g.stg = 0;
+  g.na = g.kc2 > 2 ? 5 : NA_MAX;
+  g.nb = min(NB_MAX, SLOTS_TOTAL - g.na - g.kc2);
   g.w1_bytes = (long long)g.kc1 * g.nsub * g.nsubw * 128;
   g.bias_off = g.w1_bytes + (long long)g.nc * g.kc2 * g.nd * 128;
   g.stride = (g.bias_off + 512 + 1023) / 1024 * 1024;
@@ -217,6 +223,27 @@ __device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t* v) {
       : "r"(taddr)
       : "memory");
 }
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t* v) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]),
+        "=r"(v[7]), "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]),
+        "=r"(v[14]), "=r"(v[15]), "=r"(v[16]), "=r"(v[17]), "=r"(v[18]), "=r"(v[19]),
+        "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]), "=r"(v[24]), "=r"(v[25]),
+        "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
+      : "r"(taddr)
+      : "memory");
+}
+__device__ __forceinline__ uint4 ld_shared_v4(uint32_t addr) {
+  uint4 r;
+  asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];"
+               : "=r"(r.x), "=r"(r.y), "=r"(r.z), "=r"(r.w)
+               : "r"(addr)
+               : "memory");
+  return r;
+}
 __device__ __forceinline__ void tmem_wait_ld() {
   asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 }
@@ -225,6 +252,19 @@ __device__ __forceinline__ void st_shared_v4(uint32_t addr, uint32_t a, uint32_t
   asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(a), "r"(b), "r"(c),
                "r"(d)
                : "memory");
+}
+
+// One lane of a converged warp.  Unlike a test on the lane id, elect.sync tells the
+// compiler that exactly one thread runs the guarded code, so warp-uniform operands of
+// tcgen05.mma / tcgen05.commit need no per-lane handling.
+__device__ __forceinline__ bool elect_one() {
+  uint32_t pred;
+  asm volatile(
+      "{\n\t.reg .pred P;\n\t"
+      "elect.sync _|P, 0xffffffff;\n\t"
+      "selp.u32 %0, 1, 0, P;\n\t}"
+      : "=r"(pred));
+  return pred != 0;
 }
 
 // Shared-memory matrix descriptor: K-major tile, 128-byte swizzle, 8-row groups 1024
@@ -248,7 +288,7 @@ __device__ __forceinline__ float nanmax(float a, float b) {
 // shared-memory bookkeeping
 // ---------------------------------------------------------------------------
 struct Ctl {
-  unsigned long long fullA[NA], emptyA[NA], fullB[NB_MAX], emptyB[NB_MAX];
+  unsigned long long fullA[NA_MAX], emptyA[NA_MAX], fullB[NB_MAX], emptyB[NB_MAX];
   unsigned long long acc1_full, hs_full, hs_empty, acc2_full[2], acc2_empty[2];
   uint32_t tmem_base;
   int abort_flag;
@@ -294,7 +334,7 @@ __device__ void role_producer(const Params& p, Ctl* c, uint32_t ringA, int pt) {
     dstoff[i] = (row >> 3) * 1024 + (row & 7) * 128 + ((j ^ (row & 7)) << 4);
   }
   volatile int* af = &c->abort_flag;
-  uint32_t it = 0;
+  uint32_t s = 0, ph = 0;
   for (int tile = blockIdx.x; tile < c->total_tiles; tile += gridDim.x) {
     const Tile t = tile_info<MODE>(p, c, tile);
     const bf16* src[8];
@@ -315,13 +355,15 @@ __device__ void role_producer(const Params& p, Ctl* c, uint32_t ringA, int pt) {
       src[i] = p.x + tok * p.d + j * 8;
     }
     for (int kc = 0; kc < p.g.kc1; ++kc) {
-      const uint32_t s = it % NA;
-      if (!mbar_wait(smem_u32(&c->emptyA[s]), ((it / NA) & 1) ^ 1, af, p.dev_status)) return;
+      if (!mbar_wait(smem_u32(&c->emptyA[s]), ph ^ 1, af, p.dev_status)) return;
       const uint32_t base = ringA + s * SLOT;
 #pragma unroll
       for (int i = 0; i < 8; ++i) cp_async16(base + dstoff[i], src[i] + kc * 64);
       cp_async_arrive_noinc(smem_u32(&c->fullA[s]));
-      ++it;
+      if (++s == (uint32_t)p.g.na) {
+        s = 0;
+        ph ^= 1;
+      }
     }
   }
 }
@@ -330,94 +372,131 @@ template <int MODE>
 __device__ void role_bulk(const Params& p, Ctl* c, uint32_t ringB) {
   volatile int* af = &c->abort_flag;
   const Geo& g = p.g;
-  uint32_t ib = 0;
+  // the whole warp walks the loop and waits; one elected lane issues the copies
+  uint32_t s = 0, ph = 0;
   for (int tile = blockIdx.x; tile < c->total_tiles; tile += gridDim.x) {
     const Tile t = tile_info<MODE>(p, c, tile);
     const uint8_t* pe = p.packed + (long long)t.e * g.stride;
-    const uint32_t b1 = g.nsubw * 128;
-    for (int i = 0; i < g.kc1 * g.nsub; ++i) {
-      const uint32_t s = ib % g.nb;
-      if (!mbar_wait(smem_u32(&c->emptyB[s]), ((ib / g.nb) & 1) ^ 1, af, p.dev_status)) return;
+    const uint32_t b1 = g.nsubw * 128, n1 = g.kc1 * g.nsub;
+    const uint32_t b2 = g.nd * 128, n2 = g.nc * g.kc2;
+    for (uint32_t i = 0; i < n1 + n2; ++i) {
+      if (!mbar_wait(smem_u32(&c->emptyB[s]), ph ^ 1, af, p.dev_status)) return;
       const uint32_t bar = smem_u32(&c->fullB[s]);
-      mbar_arrive_expect_tx(bar, b1);
-      bulk_g2s(ringB + s * SLOT, pe + (long long)i * b1, b1, bar);
-      ++ib;
-    }
-    const uint32_t b2 = g.nd * 128;
-    for (int i = 0; i < g.nc * g.kc2; ++i) {
-      const uint32_t s = ib % g.nb;
-      if (!mbar_wait(smem_u32(&c->emptyB[s]), ((ib / g.nb) & 1) ^ 1, af, p.dev_status)) return;
-      const uint32_t bar = smem_u32(&c->fullB[s]);
-      mbar_arrive_expect_tx(bar, b2);
-      bulk_g2s(ringB + s * SLOT, pe + g.w1_bytes + (long long)i * b2, b2, bar);
-      ++ib;
+      const uint32_t bytes = i < n1 ? b1 : b2;
+      const uint8_t* src = i < n1 ? pe + (long long)i * b1 : pe + g.w1_bytes + (long long)(i - n1) * b2;
+      if (elect_one()) {
+        mbar_arrive_expect_tx(bar, bytes);
+        bulk_g2s(ringB + s * SLOT, src, bytes, bar);
+      }
+      __syncwarp();
+      if (++s == (uint32_t)g.nb) {
+        s = 0;
+        ph ^= 1;
+      }
     }
   }
+}
+
+// Ring position kept as (stage, phase) with wrap-around instead of a running counter:
+// no integer division, and every value stays provably warp-uniform, which lets the
+// compiler form the MMA operands in uniform registers.
+struct RingPos {
+  uint32_t s, ph;
+  __device__ __forceinline__ void next(uint32_t n) {
+    if (++s == n) {
+      s = 0;
+      ph ^= 1;
+    }
+  }
+};
+
+// Whole-warp bounded wait with a warp-uniform result.
+__device__ __forceinline__ bool warp_wait(uint32_t bar, uint32_t parity, volatile int* af,
+                                          int* dev_status) {
+  return __all_sync(0xffffffffu, mbar_wait(bar, parity, af, dev_status));
 }
 
 template <int MODE>
 __device__ void role_mma(const Params& p, Ctl* c, uint32_t ringA, uint32_t ringB, uint32_t hs,
-                         uint32_t tmem) {
+                         uint32_t tmem_in) {
   volatile int* af = &c->abort_flag;
   const Geo& g = p.g;
+  const uint32_t tmem = __shfl_sync(0xffffffffu, tmem_in, 0);
   const uint32_t idesc1 = instr_desc(TILE_M, g.nsubw), idesc2 = instr_desc(TILE_M, g.nd);
-  uint32_t ia = 0, ib = 0, g2 = 0, tc = 0;
+  const uint64_t descA0 = smem_desc(ringA), descB0 = smem_desc(ringB), descH0 = smem_desc(hs);
+  RingPos pa = {0, 0}, pb = {0, 0};
+  uint32_t buf = 0, ph_acc2 = 0, ph_tile = 0;
   for (int tile = blockIdx.x; tile < c->total_tiles; tile += gridDim.x) {
     // ---- GEMM1: acc1[sub] = A(rows, d) * W1sub(d, nsubw) ------------------------
     for (int kc = 0; kc < g.kc1; ++kc) {
-      const uint32_t sa = ia % NA;
-      if (!mbar_wait(smem_u32(&c->fullA[sa]), (ia / NA) & 1, af, p.dev_status)) return;
-      uint32_t sb[2];
-      for (int sub = 0; sub < g.nsub; ++sub) {
-        sb[sub] = ib % g.nb;
-        if (!mbar_wait(smem_u32(&c->fullB[sb[sub]]), (ib / g.nb) & 1, af, p.dev_status)) return;
-        ++ib;
+      if (!warp_wait(smem_u32(&c->fullA[pa.s]), pa.ph, af, p.dev_status)) return;
+      const uint32_t sb0 = pb.s;
+      if (!warp_wait(smem_u32(&c->fullB[pb.s]), pb.ph, af, p.dev_status)) return;
+      pb.next(g.nb);
+      const uint32_t sb1 = pb.s;
+      if (g.nsub == 2) {
+        if (!warp_wait(smem_u32(&c->fullB[pb.s]), pb.ph, af, p.dev_status)) return;
+        pb.next(g.nb);
       }
-      fence_proxy_async();     // rows arrived through the generic proxy (cp.async)
       tc_fence_after();
+      // descriptors advance in 16-byte units: one slot = 1024 units, one k-step = 2
+      const uint64_t ad = descA0 + (uint64_t)(pa.s * (SLOT >> 4));
+      const uint64_t bd0 = descB0 + (uint64_t)(sb0 * (SLOT >> 4));
+      const uint64_t bd1 = descB0 + (uint64_t)(sb1 * (SLOT >> 4));
+      if (elect_one()) {
 #pragma unroll
-      for (int k = 0; k < 4; ++k) {
-        const uint64_t ad = smem_desc(ringA + sa * SLOT + k * 32);
-        for (int sub = 0; sub < g.nsub; ++sub)
-          umma_bf16(tmem + sub * 128, ad, smem_desc(ringB + sb[sub] * SLOT + k * 32), idesc1,
-                    (kc | k) != 0);
+        for (int k = 0; k < 4; ++k) {
+          umma_bf16(tmem, ad + 2 * k, bd0 + 2 * k, idesc1, (kc | k) != 0);
+          if (g.nsub == 2) umma_bf16(tmem + 128, ad + 2 * k, bd1 + 2 * k, idesc1, (kc | k) != 0);
+        }
+        umma_commit(smem_u32(&c->emptyA[pa.s]));
+        umma_commit(smem_u32(&c->emptyB[sb0]));
+        if (g.nsub == 2) umma_commit(smem_u32(&c->emptyB[sb1]));
+        if (kc == g.kc1 - 1) umma_commit(smem_u32(&c->acc1_full));
       }
-      umma_commit(smem_u32(&c->emptyA[sa]));
-      for (int sub = 0; sub < g.nsub; ++sub) umma_commit(smem_u32(&c->emptyB[sb[sub]]));
-      ++ia;
+      __syncwarp();
+      pa.next(g.na);
     }
-    umma_commit(smem_u32(&c->acc1_full));
     // ---- GEMM2: acc2[buf] = Hs(rows, K2) * W2chunk(K2, nd) ----------------------
-    if (!mbar_wait(smem_u32(&c->hs_full), tc & 1, af, p.dev_status)) return;
-    fence_proxy_async();       // hidden tile was written with ordinary shared stores
+    if (!warp_wait(smem_u32(&c->hs_full), ph_tile, af, p.dev_status)) return;
     tc_fence_after();
     for (int nci = 0; nci < g.nc; ++nci) {
-      const uint32_t buf = g2 & 1;
-      if (!mbar_wait(smem_u32(&c->acc2_empty[buf]), ((g2 >> 1) & 1) ^ 1, af, p.dev_status)) return;
+      if (!warp_wait(smem_u32(&c->acc2_empty[buf]), ph_acc2 ^ 1, af, p.dev_status)) return;
       tc_fence_after();
       for (int k2 = 0; k2 < g.kc2; ++k2) {
-        const uint32_t s = ib % g.nb;
-        if (!mbar_wait(smem_u32(&c->fullB[s]), (ib / g.nb) & 1, af, p.dev_status)) return;
+        if (!warp_wait(smem_u32(&c->fullB[pb.s]), pb.ph, af, p.dev_status)) return;
         tc_fence_after();
+        const uint64_t hd = descH0 + (uint64_t)(k2 * (SLOT >> 4));
+        const uint64_t bd = descB0 + (uint64_t)(pb.s * (SLOT >> 4));
         const int ksteps = min(4, (g.K2 - k2 * 64) >> 4);
-        for (int k = 0; k < ksteps; ++k)
-          umma_bf16(tmem + 256 + buf * 128, smem_desc(hs + k2 * SLOT + k * 32),
-                    smem_desc(ringB + s * SLOT + k * 32), idesc2, (k2 | k) != 0);
-        umma_commit(smem_u32(&c->emptyB[s]));
-        ++ib;
+        if (elect_one()) {
+#pragma unroll
+          for (int k = 0; k < 4; ++k)
+            if (k < ksteps)
+              umma_bf16(tmem + 256 + buf * 128, hd + 2 * k, bd + 2 * k, idesc2, (k2 | k) != 0);
+          umma_commit(smem_u32(&c->emptyB[pb.s]));
+          if (k2 == g.kc2 - 1) {
+            umma_commit(smem_u32(&c->acc2_full[buf]));
+            if (nci == g.nc - 1) umma_commit(smem_u32(&c->hs_empty));
+          }
+        }
+        __syncwarp();
+        pb.next(g.nb);
       }
-      umma_commit(smem_u32(&c->acc2_full[buf]));
-      ++g2;
+      buf ^= 1;
+      if (buf == 0) ph_acc2 ^= 1;
     }
-    umma_commit(smem_u32(&c->hs_empty));
-    ++tc;
+    ph_tile ^= 1;
   }
 }
 
 template <int MODE>
-__device__ void role_epilogue(const Params& p, Ctl* c, uint32_t hs, uint32_t tmem, int r) {
+__device__ void role_epilogue(const Params& p, Ctl* c, uint32_t hs, uint32_t stg, uint32_t tmem,
+                              int r) {
   volatile int* af = &c->abort_flag;
   const Geo& g = p.g;
+  const int lane = r & 31;
+  const uint32_t stg_w = stg + (r >> 5) * 8192;   // this warp's 32 rows x 256 B of staging
   const uint32_t lane_base = (uint32_t)(r & ~31) << 16;   // this warp's TMEM lane quarter
   const uint32_t hs_row = hs + (r >> 3) * 1024 + (r & 7) * 128;
   uint32_t g2 = 0, tc = 0;
@@ -455,8 +534,15 @@ __device__ void role_epilogue(const Params& p, Ctl* c, uint32_t hs, uint32_t tme
     for (int sub = 0; sub < nsub1; ++sub) {
       for (int c0 = 0; c0 < g.nsubw; c0 += 16) {
         uint32_t v[16], u[16];
+        float bv[16];
         tmem_ld16(tmem + lane_base + sub * 128 + c0, v);
         if (MODE == MODE_EXPERTS && p.glu) tmem_ld16(tmem + lane_base + 128 + c0, u);
+        if (MODE == MODE_EXPERTS) {
+#pragma unroll
+          for (int q = 0; q < 4; ++q)
+            *reinterpret_cast<float4*>(&bv[4 * q]) =
+                __ldg(reinterpret_cast<const float4*>(bias + c0) + q);
+        }
         tmem_wait_ld();
         uint32_t w[8];
 #pragma unroll
@@ -466,8 +552,8 @@ __device__ void role_epilogue(const Params& p, Ctl* c, uint32_t hs, uint32_t tme
             h0 = fmaxf(h0, 0.f);
             h1 = fmaxf(h1, 0.f);
           } else {
-            h0 = bfr(activate(bfr(h0 + bias[c0 + 2 * q]), p.act));
-            h1 = bfr(activate(bfr(h1 + bias[c0 + 2 * q + 1]), p.act));
+            h0 = bfr(activate(bfr(h0 + bv[2 * q]), p.act));
+            h1 = bfr(activate(bfr(h1 + bv[2 * q + 1]), p.act));
             if (p.glu) {
               h0 *= bfr(__uint_as_float(u[2 * q]));
               h1 *= bfr(__uint_as_float(u[2 * q + 1]));
@@ -482,6 +568,7 @@ __device__ void role_epilogue(const Params& p, Ctl* c, uint32_t hs, uint32_t tme
         st_shared_v4(base + (((j0 + 1) ^ (r & 7)) << 4), w[4], w[5], w[6], w[7]);
       }
     }
+    fence_proxy_async();     // ordinary shared stores -> visible to the MMA's async reads
     tc_fence_before();
     mbar_arrive(smem_u32(&c->hs_full));
     // ---- epilogue 2 -------------------------------------------------------------
@@ -495,22 +582,39 @@ __device__ void role_epilogue(const Params& p, Ctl* c, uint32_t hs, uint32_t tme
         const uint32_t buf = g2 & 1;
         if (!mbar_wait(smem_u32(&c->acc2_full[buf]), (g2 >> 1) & 1, af, p.dev_status)) return;
         tc_fence_after();
-        bf16* orow = p.out + (tok < 0 ? 0 : tok) * p.d + nci * g.nd;
-        for (int c0 = 0; c0 < g.nd; c0 += 16) {
-          uint32_t v[16];
-          tmem_ld16(tmem + lane_base + 256 + buf * 128 + c0, v);
+        // TMEM -> bf16 -> this warp's staging rows (piece index XOR row keeps the 16-byte
+        // stores of 8 consecutive rows on distinct banks)
+        for (int c0 = 0; c0 < g.nd; c0 += 32) {
+          uint32_t v[32];
+          tmem_ld32(tmem + lane_base + 256 + buf * 128 + c0, v);
           tmem_wait_ld();
-          if (tok >= 0) {
-            uint32_t w[8];
 #pragma unroll
-            for (int q = 0; q < 8; ++q)
-              w[q] = pack_bf16x2(__uint_as_float(v[2 * q]), __uint_as_float(v[2 * q + 1]));
-            red_add_bf16x8(orow + c0, w[0], w[1], w[2], w[3]);
-            red_add_bf16x8(orow + c0 + 8, w[4], w[5], w[6], w[7]);
+          for (int q4 = 0; q4 < 4; ++q4) {
+            uint32_t w[4];
+#pragma unroll
+            for (int q = 0; q < 4; ++q)
+              w[q] = pack_bf16x2(__uint_as_float(v[8 * q4 + 2 * q]),
+                                 __uint_as_float(v[8 * q4 + 2 * q + 1]));
+            const int piece = (c0 >> 3) + q4;
+            st_shared_v4(stg_w + lane * 256 + ((piece ^ (lane & 15)) << 4), w[0], w[1], w[2], w[3]);
           }
         }
+        // the accumulator buffer is free as soon as it has been read
         tc_fence_before();
         mbar_arrive(smem_u32(&c->acc2_empty[buf]));
+        __syncwarp();
+        // read back row-contiguous: `pieces` lanes cover one row's chunk, so one red
+        // instruction touches 2 (nd = 128) or 4 (nd = 64) rows instead of 32
+        const int pieces = g.nd >> 3, rpi = 32 / pieces;
+        const int pl = lane % pieces, rl = lane / pieces;
+        for (int i = 0; i < pieces; ++i) {
+          const int rr = i * rpi + rl;
+          const uint4 val = ld_shared_v4(stg_w + rr * 256 + ((pl ^ (rr & 15)) << 4));
+          const long long tk = __shfl_sync(0xffffffffu, tok, rr);
+          if (tk >= 0)
+            red_add_bf16x8(p.out + tk * p.d + nci * g.nd + pl * 8, val.x, val.y, val.z, val.w);
+        }
+        __syncwarp();
         ++g2;
       }
     } else {
@@ -567,13 +671,15 @@ __global__ void __launch_bounds__(NTHREADS, 1) mlp_tiles_kernel(const Params p) 
   const uint32_t base = (raw + 1023u) & ~1023u;
   uint8_t* aligned = smem_raw + (base - raw);
   const uint32_t ringA = base;
-  const uint32_t ringB = ringA + NA * SLOT;
+  const uint32_t ringB = ringA + p.g.na * SLOT;
   const uint32_t hs = ringB + p.g.nb * SLOT;
-  Ctl* c = reinterpret_cast<Ctl*>(aligned + (size_t)(NA + p.g.nb + p.g.kc2) * SLOT);
+  const uint32_t stg = hs + p.g.kc2 * SLOT;
+  Ctl* c = reinterpret_cast<Ctl*>(aligned +
+                                  (size_t)(p.g.na + p.g.nb + p.g.kc2 + p.g.stg) * SLOT);
   const int tid = threadIdx.x, warp = tid >> 5;
 
   if (tid == 0) {
-    for (int i = 0; i < NA; ++i) {
+    for (int i = 0; i < NA_MAX; ++i) {
       mbar_init(smem_u32(&c->fullA[i]), 128);
       mbar_init(smem_u32(&c->emptyA[i]), 1);
     }
@@ -612,11 +718,11 @@ __global__ void __launch_bounds__(NTHREADS, 1) mlp_tiles_kernel(const Params p) 
   const uint32_t tmem = c->tmem_base;
 
   if (warp < 4) {
-    role_epilogue<MODE>(p, c, hs, tmem, tid);
+    role_epilogue<MODE>(p, c, hs, stg, tmem, tid);
   } else if (warp == 4) {
-    if ((tid & 31) == 0) role_mma<MODE>(p, c, ringA, ringB, hs, tmem);
+    role_mma<MODE>(p, c, ringA, ringB, hs, tmem);
   } else if (warp == 5) {
-    if ((tid & 31) == 0) role_bulk<MODE>(p, c, ringB);
+    role_bulk<MODE>(p, c, ringB);
   } else {
     role_producer<MODE>(p, c, ringA, tid - 192);
     cp_async_wait_all();
@@ -708,7 +814,7 @@ int sm_count() {
 }
 
 size_t smem_bytes(const Geo& g) {
-  return 1024 + (size_t)(NA + g.nb + g.kc2) * SLOT + sizeof(Ctl) + 64;
+  return 1024 + (size_t)(g.na + g.nb + g.kc2 + g.stg) * SLOT + sizeof(Ctl) + 64;
 }
 
 template <int MODE>
