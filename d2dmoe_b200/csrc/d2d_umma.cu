@@ -34,8 +34,9 @@ constexpr int TILE_M = 128;
 constexpr int SLOT = TILE_M * 128;   // 16 KB: 128 rows x 64 bf16, also the weight slot size
 constexpr int NA_MAX = 6;            // ring A stages (upper bound)
 constexpr int NB_MAX = 6;            // ring B stages (upper bound)
-constexpr int SLOTS_TOTAL = 13;      // ring A + ring B + hidden tile + staging (208 KB)
-constexpr int NTHREADS = 320;
+constexpr int SLOTS_TOTAL = 14;      // ring A + ring B + hidden tile + staging (224 KB)
+constexpr int NTHREADS = 448;
+constexpr int WARP_MMA = 8, WARP_BULK = 9, WARP_PROD0 = 10;
 constexpr int MAX_E = 128;
 constexpr uint32_t WAIT_LIMIT = 1u << 22;
 constexpr int MODE_EXPERTS = 0, MODE_ROUTER = 1;
@@ -50,7 +51,7 @@ struct Geo {
   int nc;        // number of chunks
   int nb;        // ring B stages
   int na;        // ring A stages
-  int stg;       // 16 KB slots of epilogue staging (experts: 2 = 32 rows x 256 B per warp)
+  int stg;       // 16 KB slots of epilogue staging (experts: 2 = 32 rows x 128 B per warp)
   long long w1_bytes, bias_off, stride;   // packed layout per expert
 };
 
@@ -85,7 +86,7 @@ Geo experts_geo(int d, int H, bool glu) {
   g.kc2 = (H + 63) / 64;
   g.nd = (d % 128 == 0) ? 128 : 64;
   g.nc = d / g.nd;
-  g.stg = 2;
+  g.stg = 2;                       // 8 epilogue warps x 4 KB
   g.na = glu ? 4 : 5;
   g.nb = min(NB_MAX, SLOTS_TOTAL - g.na - g.kc2 - g.stg);
   g.w1_bytes = (long long)g.kc1 * g.nsub * g.nsubw * 128;
@@ -289,7 +290,7 @@ __device__ __forceinline__ float nanmax(float a, float b) {
 // ---------------------------------------------------------------------------
 struct Ctl {
   unsigned long long fullA[NA_MAX], emptyA[NA_MAX], fullB[NB_MAX], emptyB[NB_MAX];
-  unsigned long long acc1_full, hs_full, hs_empty, acc2_full[2], acc2_empty[2];
+  unsigned long long acc1_full[2], hs_full, hs_empty, acc2_full[2], acc2_empty[2];
   uint32_t tmem_base;
   int abort_flag;
   int total_tiles;
@@ -319,6 +320,30 @@ __device__ __forceinline__ Tile tile_info(const Params& p, const Ctl* c, int til
   }
   return t;
 }
+
+// Ring position kept as (stage, phase) with wrap-around instead of a running counter:
+// no integer division, and every value stays provably warp-uniform, which lets the
+// compiler form the MMA operands in uniform registers.
+struct RingPos {
+  uint32_t s, ph;
+  __device__ __forceinline__ void next(uint32_t n) {
+    if (++s == n) {
+      s = 0;
+      ph ^= 1;
+    }
+  }
+};
+
+// Whole-warp bounded wait with a warp-uniform result.
+__device__ __forceinline__ bool warp_wait(uint32_t bar, uint32_t parity, volatile int* af,
+                                          int* dev_status) {
+  return __all_sync(0xffffffffu, mbar_wait(bar, parity, af, dev_status));
+}
+
+// With one weight subtile per k-chunk (nsub == 1) the first accumulator is double
+// buffered and GEMM1 of the next tile is issued before GEMM2 of the current one, so the
+// tensor pipe works while the epilogue warps turn acc1 into the hidden tile.
+__device__ __forceinline__ bool lookahead(const Geo& g) { return g.nsub == 1; }
 
 // ---------------------------------------------------------------------------
 // roles
@@ -368,25 +393,23 @@ __device__ void role_producer(const Params& p, Ctl* c, uint32_t ringA, int pt) {
   }
 }
 
+// Weight tiles in the order the MMA warp consumes them: W1 chunks of a tile, W2 pieces of
+// a tile; with lookahead the W1 chunks of tile i+1 come before the W2 pieces of tile i.
 template <int MODE>
 __device__ void role_bulk(const Params& p, Ctl* c, uint32_t ringB) {
   volatile int* af = &c->abort_flag;
   const Geo& g = p.g;
-  // the whole warp walks the loop and waits; one elected lane issues the copies
+  const uint32_t b1 = g.nsubw * 128, n1 = g.kc1 * g.nsub;
+  const uint32_t b2 = g.nd * 128, n2 = g.nc * g.kc2;
+  const bool la = lookahead(g);
   uint32_t s = 0, ph = 0;
-  for (int tile = blockIdx.x; tile < c->total_tiles; tile += gridDim.x) {
-    const Tile t = tile_info<MODE>(p, c, tile);
-    const uint8_t* pe = p.packed + (long long)t.e * g.stride;
-    const uint32_t b1 = g.nsubw * 128, n1 = g.kc1 * g.nsub;
-    const uint32_t b2 = g.nd * 128, n2 = g.nc * g.kc2;
-    for (uint32_t i = 0; i < n1 + n2; ++i) {
-      if (!mbar_wait(smem_u32(&c->emptyB[s]), ph ^ 1, af, p.dev_status)) return;
+  auto stream = [&](const uint8_t* src, uint32_t bytes, uint32_t n) -> bool {
+    for (uint32_t i = 0; i < n; ++i) {
+      if (!mbar_wait(smem_u32(&c->emptyB[s]), ph ^ 1, af, p.dev_status)) return false;
       const uint32_t bar = smem_u32(&c->fullB[s]);
-      const uint32_t bytes = i < n1 ? b1 : b2;
-      const uint8_t* src = i < n1 ? pe + (long long)i * b1 : pe + g.w1_bytes + (long long)(i - n1) * b2;
       if (elect_one()) {
         mbar_arrive_expect_tx(bar, bytes);
-        bulk_g2s(ringB + s * SLOT, src, bytes, bar);
+        bulk_g2s(ringB + s * SLOT, src + (long long)i * bytes, bytes, bar);
       }
       __syncwarp();
       if (++s == (uint32_t)g.nb) {
@@ -394,26 +417,28 @@ __device__ void role_bulk(const Params& p, Ctl* c, uint32_t ringB) {
         ph ^= 1;
       }
     }
-  }
-}
-
-// Ring position kept as (stage, phase) with wrap-around instead of a running counter:
-// no integer division, and every value stays provably warp-uniform, which lets the
-// compiler form the MMA operands in uniform registers.
-struct RingPos {
-  uint32_t s, ph;
-  __device__ __forceinline__ void next(uint32_t n) {
-    if (++s == n) {
-      s = 0;
-      ph ^= 1;
+    return true;
+  };
+  const int first = blockIdx.x, step = gridDim.x, total = c->total_tiles;
+  if (first >= total) return;
+  const uint8_t* pe = p.packed + (long long)tile_info<MODE>(p, c, first).e * g.stride;
+  if (la && !stream(pe, b1, n1)) return;
+  for (int tile = first; tile < total; tile += step) {
+    if (la) {
+      if (tile + step < total) {
+        const uint8_t* pn = p.packed + (long long)tile_info<MODE>(p, c, tile + step).e * g.stride;
+        if (!stream(pn, b1, n1)) return;
+        if (!stream(pe + g.w1_bytes, b2, n2)) return;
+        pe = pn;
+      } else if (!stream(pe + g.w1_bytes, b2, n2)) {
+        return;
+      }
+    } else {
+      pe = p.packed + (long long)tile_info<MODE>(p, c, tile).e * g.stride;
+      if (!stream(pe, b1, n1)) return;
+      if (!stream(pe + g.w1_bytes, b2, n2)) return;
     }
   }
-};
-
-// Whole-warp bounded wait with a warp-uniform result.
-__device__ __forceinline__ bool warp_wait(uint32_t bar, uint32_t parity, volatile int* af,
-                                          int* dev_status) {
-  return __all_sync(0xffffffffu, mbar_wait(bar, parity, af, dev_status));
 }
 
 template <int MODE>
@@ -424,18 +449,21 @@ __device__ void role_mma(const Params& p, Ctl* c, uint32_t ringA, uint32_t ringB
   const uint32_t tmem = __shfl_sync(0xffffffffu, tmem_in, 0);
   const uint32_t idesc1 = instr_desc(TILE_M, g.nsubw), idesc2 = instr_desc(TILE_M, g.nd);
   const uint64_t descA0 = smem_desc(ringA), descB0 = smem_desc(ringB), descH0 = smem_desc(hs);
+  const bool la = lookahead(g);
   RingPos pa = {0, 0}, pb = {0, 0};
-  uint32_t buf = 0, ph_acc2 = 0, ph_tile = 0;
-  for (int tile = blockIdx.x; tile < c->total_tiles; tile += gridDim.x) {
-    // ---- GEMM1: acc1[sub] = A(rows, d) * W1sub(d, nsubw) ------------------------
+  uint32_t ph_acc2[2] = {0, 0};
+
+  // GEMM1 of one tile into acc1 buffer b: acc1[sub] = A(rows, d) * W1sub(d, nsubw)
+  auto gemm1 = [&](uint32_t b) -> bool {
+    const uint32_t acc = tmem + (la ? b * 128 : 0);
     for (int kc = 0; kc < g.kc1; ++kc) {
-      if (!warp_wait(smem_u32(&c->fullA[pa.s]), pa.ph, af, p.dev_status)) return;
+      if (!warp_wait(smem_u32(&c->fullA[pa.s]), pa.ph, af, p.dev_status)) return false;
       const uint32_t sb0 = pb.s;
-      if (!warp_wait(smem_u32(&c->fullB[pb.s]), pb.ph, af, p.dev_status)) return;
+      if (!warp_wait(smem_u32(&c->fullB[pb.s]), pb.ph, af, p.dev_status)) return false;
       pb.next(g.nb);
       const uint32_t sb1 = pb.s;
       if (g.nsub == 2) {
-        if (!warp_wait(smem_u32(&c->fullB[pb.s]), pb.ph, af, p.dev_status)) return;
+        if (!warp_wait(smem_u32(&c->fullB[pb.s]), pb.ph, af, p.dev_status)) return false;
         pb.next(g.nb);
       }
       tc_fence_after();
@@ -446,25 +474,31 @@ __device__ void role_mma(const Params& p, Ctl* c, uint32_t ringA, uint32_t ringB
       if (elect_one()) {
 #pragma unroll
         for (int k = 0; k < 4; ++k) {
-          umma_bf16(tmem, ad + 2 * k, bd0 + 2 * k, idesc1, (kc | k) != 0);
-          if (g.nsub == 2) umma_bf16(tmem + 128, ad + 2 * k, bd1 + 2 * k, idesc1, (kc | k) != 0);
+          umma_bf16(acc, ad + 2 * k, bd0 + 2 * k, idesc1, (kc | k) != 0);
+          if (g.nsub == 2) umma_bf16(acc + 128, ad + 2 * k, bd1 + 2 * k, idesc1, (kc | k) != 0);
         }
         umma_commit(smem_u32(&c->emptyA[pa.s]));
         umma_commit(smem_u32(&c->emptyB[sb0]));
         if (g.nsub == 2) umma_commit(smem_u32(&c->emptyB[sb1]));
-        if (kc == g.kc1 - 1) umma_commit(smem_u32(&c->acc1_full));
+        if (kc == g.kc1 - 1) umma_commit(smem_u32(&c->acc1_full[b]));
       }
       __syncwarp();
       pa.next(g.na);
     }
-    // ---- GEMM2: acc2[buf] = Hs(rows, K2) * W2chunk(K2, nd) ----------------------
-    if (!warp_wait(smem_u32(&c->hs_full), ph_tile, af, p.dev_status)) return;
+    return true;
+  };
+  // GEMM2 of one tile: acc2[chunk & 1] = Hs(rows, K2) * W2chunk(K2, nd)
+  auto gemm2 = [&](uint32_t ph_tile) -> bool {
+    if (!warp_wait(smem_u32(&c->hs_full), ph_tile, af, p.dev_status)) return false;
     tc_fence_after();
     for (int nci = 0; nci < g.nc; ++nci) {
-      if (!warp_wait(smem_u32(&c->acc2_empty[buf]), ph_acc2 ^ 1, af, p.dev_status)) return;
+      const uint32_t buf = nci & 1;
+      if (!warp_wait(smem_u32(&c->acc2_empty[buf]), ph_acc2[buf] ^ 1, af, p.dev_status))
+        return false;
+      ph_acc2[buf] ^= 1;
       tc_fence_after();
       for (int k2 = 0; k2 < g.kc2; ++k2) {
-        if (!warp_wait(smem_u32(&c->fullB[pb.s]), pb.ph, af, p.dev_status)) return;
+        if (!warp_wait(smem_u32(&c->fullB[pb.s]), pb.ph, af, p.dev_status)) return false;
         tc_fence_after();
         const uint64_t hd = descH0 + (uint64_t)(k2 * (SLOT >> 4));
         const uint64_t bd = descB0 + (uint64_t)(pb.s * (SLOT >> 4));
@@ -483,90 +517,129 @@ __device__ void role_mma(const Params& p, Ctl* c, uint32_t ringA, uint32_t ringB
         __syncwarp();
         pb.next(g.nb);
       }
-      buf ^= 1;
-      if (buf == 0) ph_acc2 ^= 1;
     }
-    ph_tile ^= 1;
+    return true;
+  };
+
+  const int first = blockIdx.x, step = gridDim.x, total = c->total_tiles;
+  if (first >= total) return;
+  uint32_t i = 0;
+  if (la && !gemm1(0)) return;
+  for (int tile = first; tile < total; tile += step, ++i) {
+    if (la) {
+      if (tile + step < total && !gemm1((i + 1) & 1)) return;
+    } else if (!gemm1(0)) {
+      return;
+    }
+    if (!gemm2(i & 1)) return;
   }
 }
 
+// 16 hidden columns of epilogue 1: accumulator -> bias/activation (x up-projection) with
+// the upstream rounding points -> bf16 -> two 16-byte pieces of the swizzled hidden tile
+template <int MODE, int ACT>
+__device__ __forceinline__ void ep1_block(const Params& p, const uint32_t* v, const uint32_t* u,
+                                          const float* bv, uint32_t* w) {
+#pragma unroll
+  for (int q = 0; q < 8; ++q) {
+    float h0 = bfr(__uint_as_float(v[2 * q])), h1 = bfr(__uint_as_float(v[2 * q + 1]));
+    if (MODE == MODE_ROUTER) {
+      h0 = fmaxf(h0, 0.f);
+      h1 = fmaxf(h1, 0.f);
+    } else {
+      h0 = bfr(activate(bfr(h0 + bv[2 * q]), ACT));
+      h1 = bfr(activate(bfr(h1 + bv[2 * q + 1]), ACT));
+      if (p.glu) {
+        h0 = bfr(h0 * bfr(__uint_as_float(u[2 * q])));
+        h1 = bfr(h1 * bfr(__uint_as_float(u[2 * q + 1])));
+      }
+    }
+    w[q] = pack_bf16x2(h0, h1);
+  }
+}
+
+// Epilogue warps: 8 warps in two groups.  Warp w reads TMEM lanes 32*(w%4)..+31 (= tile
+// rows); group w/4 takes every other 16-column block of epilogue 1 and every other
+// chunk of epilogue 2 (chunk c lives in accumulator buffer c & 1 = its group).
 template <int MODE>
 __device__ void role_epilogue(const Params& p, Ctl* c, uint32_t hs, uint32_t stg, uint32_t tmem,
-                              int r) {
+                              int et) {
   volatile int* af = &c->abort_flag;
   const Geo& g = p.g;
-  const int lane = r & 31;
-  const uint32_t stg_w = stg + (r >> 5) * 8192;   // this warp's 32 rows x 256 B of staging
-  const uint32_t lane_base = (uint32_t)(r & ~31) << 16;   // this warp's TMEM lane quarter
+  const int lane = et & 31, w8 = et >> 5, grp = w8 >> 2;
+  const int r = et & 127;                                   // tile row = TMEM lane
+  const uint32_t stg_w = stg + w8 * 4096;                   // 32 rows x 128 B of staging
+  const uint32_t lane_base = (uint32_t)(r & ~31) << 16;
   const uint32_t hs_row = hs + (r >> 3) * 1024 + (r & 7) * 128;
-  uint32_t g2 = 0, tc = 0;
-  for (int tile = blockIdx.x; tile < c->total_tiles; tile += gridDim.x) {
+  const bool la = lookahead(g);
+  uint32_t i = 0, ph_mine = 0;
+  for (int tile = blockIdx.x; tile < c->total_tiles; tile += gridDim.x, ++i) {
     const Tile t = tile_info<MODE>(p, c, tile);
     if (MODE == MODE_ROUTER && p.out_init) {
-      // initial value of the layer output for this tile's tokens: last_bias (+ x)
+      // initial value of the layer output for this tile's tokens: last_bias (+ x);
+      // one warp per row, 16 bytes per lane
       const int v8 = p.d >> 3;
-      for (int i = r; i < t.nrows * v8; i += TILE_M) {
-        const int row = i / v8, c8 = i % v8;
-        const long long off = ((long long)t.r0 + row) * p.d + c8 * 8;
-        uint4 o = make_uint4(0u, 0u, 0u, 0u);
-        if (p.last_bias) o = *reinterpret_cast<const uint4*>(p.last_bias + c8 * 8);
-        if (p.add_residual) {
-          const uint4 xv = *reinterpret_cast<const uint4*>(p.x + off);
-          const __nv_bfloat162* a = reinterpret_cast<const __nv_bfloat162*>(&o);
-          const __nv_bfloat162* b = reinterpret_cast<const __nv_bfloat162*>(&xv);
-          uint32_t w[4];
+      for (int row = w8; row < t.nrows; row += 8) {
+        const long long rowoff = ((long long)t.r0 + row) * p.d;
+        for (int c8 = lane; c8 < v8; c8 += 32) {
+          uint4 o = make_uint4(0u, 0u, 0u, 0u);
+          if (p.last_bias) o = __ldg(reinterpret_cast<const uint4*>(p.last_bias) + c8);
+          if (p.add_residual) {
+            const uint4 xv = *(reinterpret_cast<const uint4*>(p.x + rowoff) + c8);
+            const __nv_bfloat162* a = reinterpret_cast<const __nv_bfloat162*>(&o);
+            const __nv_bfloat162* b = reinterpret_cast<const __nv_bfloat162*>(&xv);
+            uint32_t ww[4];
 #pragma unroll
-          for (int q = 0; q < 4; ++q) {
-            const float2 fa = __bfloat1622float2(a[q]), fb = __bfloat1622float2(b[q]);
-            w[q] = pack_bf16x2(fa.x + fb.x, fa.y + fb.y);
+            for (int q = 0; q < 4; ++q) {
+              const float2 fa = __bfloat1622float2(a[q]), fb = __bfloat1622float2(b[q]);
+              ww[q] = pack_bf16x2(fa.x + fb.x, fa.y + fb.y);
+            }
+            o = make_uint4(ww[0], ww[1], ww[2], ww[3]);
           }
-          o = make_uint4(w[0], w[1], w[2], w[3]);
+          *(reinterpret_cast<uint4*>(p.out_init + rowoff) + c8) = o;
         }
-        *reinterpret_cast<uint4*>(p.out_init + off) = o;
       }
     }
     // ---- epilogue 1: acc1 -> bf16 hidden tile in shared memory ------------------
-    if (!mbar_wait(smem_u32(&c->acc1_full), tc & 1, af, p.dev_status)) return;
-    if (!mbar_wait(smem_u32(&c->hs_empty), (tc & 1) ^ 1, af, p.dev_status)) return;
+    const uint32_t b1 = la ? (i & 1) : 0;
+    const uint32_t acc1 = tmem + lane_base + (la ? b1 * 128 : 0);
+    if (!mbar_wait(smem_u32(&c->acc1_full[b1]), la ? ((i >> 1) & 1) : (i & 1), af, p.dev_status))
+      return;
+    if (!mbar_wait(smem_u32(&c->hs_empty), (i & 1) ^ 1, af, p.dev_status)) return;
     tc_fence_after();
-    const float* bias = reinterpret_cast<const float*>(p.packed + (long long)t.e * g.stride + g.bias_off);
+    const float* bias =
+        reinterpret_cast<const float*>(p.packed + (long long)t.e * g.stride + g.bias_off);
+    const int nblk = g.nsubw >> 4;
     const int nsub1 = (MODE == MODE_ROUTER) ? g.nsub : 1;
-    for (int sub = 0; sub < nsub1; ++sub) {
-      for (int c0 = 0; c0 < g.nsubw; c0 += 16) {
-        uint32_t v[16], u[16];
-        float bv[16];
-        tmem_ld16(tmem + lane_base + sub * 128 + c0, v);
-        if (MODE == MODE_EXPERTS && p.glu) tmem_ld16(tmem + lane_base + 128 + c0, u);
-        if (MODE == MODE_EXPERTS) {
+    for (int bi = grp; bi < nsub1 * nblk; bi += 2) {
+      const int sub = bi / nblk, c0 = (bi - sub * nblk) << 4;
+      uint32_t v[16], u[16], w[8];
+      float bv[16];
+      tmem_ld16(acc1 + sub * 128 + c0, v);
+      if (MODE == MODE_EXPERTS && p.glu) tmem_ld16(acc1 + 128 + c0, u);
+      if (MODE == MODE_EXPERTS) {
 #pragma unroll
-          for (int q = 0; q < 4; ++q)
-            *reinterpret_cast<float4*>(&bv[4 * q]) =
-                __ldg(reinterpret_cast<const float4*>(bias + c0) + q);
-        }
-        tmem_wait_ld();
-        uint32_t w[8];
-#pragma unroll
-        for (int q = 0; q < 8; ++q) {
-          float h0 = bfr(__uint_as_float(v[2 * q])), h1 = bfr(__uint_as_float(v[2 * q + 1]));
-          if (MODE == MODE_ROUTER) {
-            h0 = fmaxf(h0, 0.f);
-            h1 = fmaxf(h1, 0.f);
-          } else {
-            h0 = bfr(activate(bfr(h0 + bv[2 * q]), p.act));
-            h1 = bfr(activate(bfr(h1 + bv[2 * q + 1]), p.act));
-            if (p.glu) {
-              h0 *= bfr(__uint_as_float(u[2 * q]));
-              h1 *= bfr(__uint_as_float(u[2 * q + 1]));
-            }
-          }
-          w[q] = pack_bf16x2(h0, h1);
-        }
-        const int hc = sub * g.nsubw + c0;          // hidden column of v[0]
-        const uint32_t base = hs_row + (hc >> 6) * SLOT;
-        const int j0 = (hc & 63) >> 3;
-        st_shared_v4(base + (((j0) ^ (r & 7)) << 4), w[0], w[1], w[2], w[3]);
-        st_shared_v4(base + (((j0 + 1) ^ (r & 7)) << 4), w[4], w[5], w[6], w[7]);
+        for (int q = 0; q < 4; ++q)
+          *reinterpret_cast<float4*>(&bv[4 * q]) =
+              __ldg(reinterpret_cast<const float4*>(bias + c0) + q);
       }
+      tmem_wait_ld();
+      if (MODE == MODE_ROUTER) {
+        ep1_block<MODE, D2D_RELU>(p, v, u, bv, w);
+      } else {
+        switch (p.act) {      // uniform branch around the element loop
+          case D2D_RELU: ep1_block<MODE, D2D_RELU>(p, v, u, bv, w); break;
+          case D2D_GELU: ep1_block<MODE, D2D_GELU>(p, v, u, bv, w); break;
+          case D2D_TANH: ep1_block<MODE, D2D_TANH>(p, v, u, bv, w); break;
+          case D2D_LEAKY_RELU: ep1_block<MODE, D2D_LEAKY_RELU>(p, v, u, bv, w); break;
+          default: ep1_block<MODE, D2D_GELU_TANH>(p, v, u, bv, w); break;
+        }
+      }
+      const int hc = sub * g.nsubw + c0;          // hidden column of v[0]
+      const uint32_t base = hs_row + (hc >> 6) * SLOT;
+      const int j0 = (hc & 63) >> 3;
+      st_shared_v4(base + (((j0) ^ (r & 7)) << 4), w[0], w[1], w[2], w[3]);
+      st_shared_v4(base + (((j0 + 1) ^ (r & 7)) << 4), w[4], w[5], w[6], w[7]);
     }
     fence_proxy_async();     // ordinary shared stores -> visible to the MMA's async reads
     tc_fence_before();
@@ -578,55 +651,55 @@ __device__ void role_epilogue(const Params& p, Ctl* c, uint32_t hs, uint32_t stg
         tok = p.token_idx[t.r0 + r];
         if (tok < 0 || tok >= p.N) tok = -1;     // reported by the producer
       }
-      for (int nci = 0; nci < g.nc; ++nci) {
-        const uint32_t buf = g2 & 1;
-        if (!mbar_wait(smem_u32(&c->acc2_full[buf]), (g2 >> 1) & 1, af, p.dev_status)) return;
+      const int rl = lane >> 3, pl = lane & 7;
+      for (int nci = grp; nci < g.nc; nci += 2) {
+        if (!mbar_wait(smem_u32(&c->acc2_full[grp]), ph_mine, af, p.dev_status)) return;
+        ph_mine ^= 1;
         tc_fence_after();
-        // TMEM -> bf16 -> this warp's staging rows (piece index XOR row keeps the 16-byte
-        // stores of 8 consecutive rows on distinct banks)
-        for (int c0 = 0; c0 < g.nd; c0 += 32) {
-          uint32_t v[32];
-          tmem_ld32(tmem + lane_base + 256 + buf * 128 + c0, v);
+        const int halves = g.nd >> 6;
+        for (int hf = 0; hf < halves; ++hf) {
+          uint32_t v[64];
+          tmem_ld32(tmem + lane_base + 256 + grp * 128 + hf * 64, v);
+          tmem_ld32(tmem + lane_base + 256 + grp * 128 + hf * 64 + 32, v + 32);
           tmem_wait_ld();
+          if (hf == halves - 1) {     // accumulator buffer read completely: hand it back
+            tc_fence_before();
+            mbar_arrive(smem_u32(&c->acc2_empty[grp]));
+          }
+          // bf16 -> this warp's staging rows (piece XOR row: conflict-free 16-byte stores)
 #pragma unroll
-          for (int q4 = 0; q4 < 4; ++q4) {
-            uint32_t w[4];
+          for (int pc = 0; pc < 8; ++pc) {
+            uint32_t ww[4];
 #pragma unroll
             for (int q = 0; q < 4; ++q)
-              w[q] = pack_bf16x2(__uint_as_float(v[8 * q4 + 2 * q]),
-                                 __uint_as_float(v[8 * q4 + 2 * q + 1]));
-            const int piece = (c0 >> 3) + q4;
-            st_shared_v4(stg_w + lane * 256 + ((piece ^ (lane & 15)) << 4), w[0], w[1], w[2], w[3]);
+              ww[q] = pack_bf16x2(__uint_as_float(v[8 * pc + 2 * q]),
+                                  __uint_as_float(v[8 * pc + 2 * q + 1]));
+            st_shared_v4(stg_w + lane * 128 + ((pc ^ (lane & 7)) << 4), ww[0], ww[1], ww[2], ww[3]);
           }
+          __syncwarp();
+          // read back row-contiguous: 8 lanes cover one row's 128 bytes, so one red
+          // instruction touches 4 rows (4 cache lines) instead of 32
+          bf16* ocol = p.out + nci * g.nd + hf * 64 + pl * 8;
+#pragma unroll
+          for (int it = 0; it < 8; ++it) {
+            const int rr = it * 4 + rl;
+            const uint4 val = ld_shared_v4(stg_w + rr * 128 + ((pl ^ (rr & 7)) << 4));
+            const long long tk = __shfl_sync(0xffffffffu, tok, rr);
+            if (tk >= 0) red_add_bf16x8(ocol + tk * p.d, val.x, val.y, val.z, val.w);
+          }
+          __syncwarp();
         }
-        // the accumulator buffer is free as soon as it has been read
-        tc_fence_before();
-        mbar_arrive(smem_u32(&c->acc2_empty[buf]));
-        __syncwarp();
-        // read back row-contiguous: `pieces` lanes cover one row's chunk, so one red
-        // instruction touches 2 (nd = 128) or 4 (nd = 64) rows instead of 32
-        const int pieces = g.nd >> 3, rpi = 32 / pieces;
-        const int pl = lane % pieces, rl = lane / pieces;
-        for (int i = 0; i < pieces; ++i) {
-          const int rr = i * rpi + rl;
-          const uint4 val = ld_shared_v4(stg_w + rr * 256 + ((pl ^ (rr & 15)) << 4));
-          const long long tk = __shfl_sync(0xffffffffu, tok, rr);
-          if (tk >= 0)
-            red_add_bf16x8(p.out + tk * p.d + nci * g.nd + pl * 8, val.x, val.y, val.z, val.w);
-        }
-        __syncwarp();
-        ++g2;
       }
-    } else {
-      const uint32_t buf = g2 & 1;
-      if (!mbar_wait(smem_u32(&c->acc2_full[buf]), (g2 >> 1) & 1, af, p.dev_status)) return;
+    } else if (grp == 0) {
+      if (!mbar_wait(smem_u32(&c->acc2_full[0]), ph_mine, af, p.dev_status)) return;
+      ph_mine ^= 1;
       tc_fence_after();
       const int E = p.E;
       const long long trow = (long long)t.r0 + r;
       float m = -INFINITY;
       for (int c0 = 0; c0 < g.nd; c0 += 16) {
         uint32_t v[16];
-        tmem_ld16(tmem + lane_base + 256 + buf * 128 + c0, v);
+        tmem_ld16(tmem + lane_base + 256 + c0, v);
         tmem_wait_ld();
 #pragma unroll
         for (int q = 0; q < 16; ++q)
@@ -637,14 +710,14 @@ __device__ void role_epilogue(const Params& p, Ctl* c, uint32_t hs, uint32_t stg
       uint32_t word = 0;
       for (int c0 = 0; c0 < g.nd; c0 += 16) {
         uint32_t v[16];
-        tmem_ld16(tmem + lane_base + 256 + buf * 128 + c0, v);
+        tmem_ld16(tmem + lane_base + 256 + c0, v);
         tmem_wait_ld();
 #pragma unroll
         for (int q = 0; q < 16; ++q) {
-          const float s = fabsf(bfr(__uint_as_float(v[q])));
+          const float sc = fabsf(bfr(__uint_as_float(v[q])));
           if (c0 + q < E) {
-            if (s >= thr) word |= 1u << ((c0 + q) & 31);
-            if (p.scores && r < t.nrows) p.scores[trow * E + c0 + q] = __float2bfloat16_rn(s);
+            if (sc >= thr) word |= 1u << ((c0 + q) & 31);
+            if (p.scores && r < t.nrows) p.scores[trow * E + c0 + q] = __float2bfloat16_rn(sc);
           }
         }
         if (((c0 + 16) & 31) == 0 || c0 + 16 >= g.nd) {
@@ -654,10 +727,8 @@ __device__ void role_epilogue(const Params& p, Ctl* c, uint32_t hs, uint32_t stg
         }
       }
       tc_fence_before();
-      mbar_arrive(smem_u32(&c->acc2_empty[buf]));
-      ++g2;
+      mbar_arrive(smem_u32(&c->acc2_empty[0]));
     }
-    ++tc;
   }
 }
 
@@ -687,10 +758,10 @@ __global__ void __launch_bounds__(NTHREADS, 1) mlp_tiles_kernel(const Params p) 
       mbar_init(smem_u32(&c->fullB[i]), 1);
       mbar_init(smem_u32(&c->emptyB[i]), 1);
     }
-    mbar_init(smem_u32(&c->acc1_full), 1);
-    mbar_init(smem_u32(&c->hs_full), 128);
+    mbar_init(smem_u32(&c->hs_full), 256);
     mbar_init(smem_u32(&c->hs_empty), 1);
     for (int i = 0; i < 2; ++i) {
+      mbar_init(smem_u32(&c->acc1_full[i]), 1);
       mbar_init(smem_u32(&c->acc2_full[i]), 1);
       mbar_init(smem_u32(&c->acc2_empty[i]), 128);
     }
@@ -711,26 +782,26 @@ __global__ void __launch_bounds__(NTHREADS, 1) mlp_tiles_kernel(const Params p) 
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     fence_proxy_async();
   }
-  if (warp == 4) tmem_alloc(smem_u32(&c->tmem_base), 512);
+  if (warp == WARP_MMA) tmem_alloc(smem_u32(&c->tmem_base), 512);
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem = c->tmem_base;
 
-  if (warp < 4) {
+  if (warp < 8) {
     role_epilogue<MODE>(p, c, hs, stg, tmem, tid);
-  } else if (warp == 4) {
+  } else if (warp == WARP_MMA) {
     role_mma<MODE>(p, c, ringA, ringB, hs, tmem);
-  } else if (warp == 5) {
+  } else if (warp == WARP_BULK) {
     role_bulk<MODE>(p, c, ringB);
   } else {
-    role_producer<MODE>(p, c, ringA, tid - 192);
+    role_producer<MODE>(p, c, ringA, tid - WARP_PROD0 * 32);
     cp_async_wait_all();
   }
 
   tc_fence_before();
   __syncthreads();
-  if (warp == 4) {
+  if (warp == WARP_MMA) {
     tc_fence_after();
     tmem_dealloc(tmem, 512);
   }
