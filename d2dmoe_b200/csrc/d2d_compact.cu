@@ -59,14 +59,18 @@ compact_scatter_kernel(const uint32_t* __restrict__ mask_bits, const int32_t* __
 
   for (int i = tid; i < ROWS * E; i += NT) cnt[i] = 0;
   for (int e = tid; e < E; e += NT) {
-    int a = 0, b = 0;
-    for (int c = 0; c < nchunks; ++c) {
-      const int v = counts[(int64_t)c * E + e];
-      if (c < chunk) b += v;
-      a += v;
+    tot[e] = 0;
+    pre[e] = 0;
+  }
+  __syncthreads();
+  // column sums of the counts table, all threads loading in parallel (coalesced over e)
+  for (int i = tid; i < nchunks * E; i += NT) {
+    const int v = counts[i];
+    if (v) {
+      const int cc = i / E, e = i - cc * E;
+      atomicAdd(&tot[e], v);
+      if (cc < chunk) atomicAdd(&pre[e], v);
     }
-    tot[e] = a;
-    pre[e] = b;
   }
   __syncthreads();
   // per-row popcounts of this chunk

@@ -160,6 +160,13 @@ __device__ __noinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile i
   report(dev_status, D2D_ERR_TIMEOUT);
   return false;
 }
+// Fast path inline (the barrier is usually complete already); the bounded polling loop
+// stays out of line.
+__device__ __forceinline__ bool mbar_wait_fast(uint32_t bar, uint32_t parity,
+                                               volatile int* abort_flag, int* dev_status) {
+  if (mbar_try_wait(bar, parity)) return true;
+  return mbar_wait(bar, parity, abort_flag, dev_status);
+}
 __device__ __forceinline__ void bulk_g2s(uint32_t dst, const void* src, uint32_t bytes,
                                          uint32_t bar) {
   asm volatile(
@@ -334,10 +341,28 @@ struct RingPos {
   }
 };
 
-// Whole-warp bounded wait with a warp-uniform result.
-__device__ __forceinline__ bool warp_wait(uint32_t bar, uint32_t parity, volatile int* af,
-                                          int* dev_status) {
-  return __all_sync(0xffffffffu, mbar_wait(bar, parity, af, dev_status));
+// Whole-warp bounded wait on up to three barriers at once: lane j polls barrier j, so
+// the warp pays one shared-memory round trip instead of one per barrier.  The result is
+// warp-uniform.
+__device__ __forceinline__ bool warp_wait(uint32_t bar0, uint32_t par0, volatile int* af,
+                                          int* dev_status, uint32_t bar1 = 0, uint32_t par1 = 0,
+                                          uint32_t bar2 = 0, uint32_t par2 = 0) {
+  const uint32_t lane = threadIdx.x & 31;
+  const uint32_t bar = lane == 0 ? bar0 : lane == 1 ? bar1 : lane == 2 ? bar2 : 0u;
+  const uint32_t par = lane == 0 ? par0 : lane == 1 ? par1 : par2;
+  for (uint32_t i = 0; i < WAIT_LIMIT; ++i) {
+    const bool ok = bar == 0u || mbar_try_wait(bar, par);
+    if (__all_sync(0xffffffffu, ok)) return true;
+    if (i > 64) {
+      __nanosleep(i > 4096 ? 256 : 32);
+      if ((i & 63) == 0 && __any_sync(0xffffffffu, *af != 0)) return false;
+    }
+  }
+  if (lane == 0) {
+    *af = 1;
+    report(dev_status, D2D_ERR_TIMEOUT);
+  }
+  return false;
 }
 
 // With one weight subtile per k-chunk (nsub == 1) the first accumulator is double
@@ -380,7 +405,7 @@ __device__ void role_producer(const Params& p, Ctl* c, uint32_t ringA, int pt) {
       src[i] = p.x + tok * p.d + j * 8;
     }
     for (int kc = 0; kc < p.g.kc1; ++kc) {
-      if (!mbar_wait(smem_u32(&c->emptyA[s]), ph ^ 1, af, p.dev_status)) return;
+      if (!mbar_wait_fast(smem_u32(&c->emptyA[s]), ph ^ 1, af, p.dev_status)) return;
       const uint32_t base = ringA + s * SLOT;
 #pragma unroll
       for (int i = 0; i < 8; ++i) cp_async16(base + dstoff[i], src[i] + kc * 64);
@@ -405,7 +430,7 @@ __device__ void role_bulk(const Params& p, Ctl* c, uint32_t ringB) {
   uint32_t s = 0, ph = 0;
   auto stream = [&](const uint8_t* src, uint32_t bytes, uint32_t n) -> bool {
     for (uint32_t i = 0; i < n; ++i) {
-      if (!mbar_wait(smem_u32(&c->emptyB[s]), ph ^ 1, af, p.dev_status)) return false;
+      if (!mbar_wait_fast(smem_u32(&c->emptyB[s]), ph ^ 1, af, p.dev_status)) return false;
       const uint32_t bar = smem_u32(&c->fullB[s]);
       if (elect_one()) {
         mbar_arrive_expect_tx(bar, bytes);
@@ -457,15 +482,14 @@ __device__ void role_mma(const Params& p, Ctl* c, uint32_t ringA, uint32_t ringB
   auto gemm1 = [&](uint32_t b) -> bool {
     const uint32_t acc = tmem + (la ? b * 128 : 0);
     for (int kc = 0; kc < g.kc1; ++kc) {
-      if (!warp_wait(smem_u32(&c->fullA[pa.s]), pa.ph, af, p.dev_status)) return false;
-      const uint32_t sb0 = pb.s;
-      if (!warp_wait(smem_u32(&c->fullB[pb.s]), pb.ph, af, p.dev_status)) return false;
+      const uint32_t sb0 = pb.s, ph0 = pb.ph;
       pb.next(g.nb);
-      const uint32_t sb1 = pb.s;
-      if (g.nsub == 2) {
-        if (!warp_wait(smem_u32(&c->fullB[pb.s]), pb.ph, af, p.dev_status)) return false;
-        pb.next(g.nb);
-      }
+      const uint32_t sb1 = pb.s, ph1 = pb.ph;
+      if (g.nsub == 2) pb.next(g.nb);
+      if (!warp_wait(smem_u32(&c->fullA[pa.s]), pa.ph, af, p.dev_status,
+                     smem_u32(&c->fullB[sb0]), ph0,
+                     g.nsub == 2 ? smem_u32(&c->fullB[sb1]) : 0u, ph1))
+        return false;
       tc_fence_after();
       // descriptors advance in 16-byte units: one slot = 1024 units, one k-step = 2
       const uint64_t ad = descA0 + (uint64_t)(pa.s * (SLOT >> 4));
@@ -493,12 +517,11 @@ __device__ void role_mma(const Params& p, Ctl* c, uint32_t ringA, uint32_t ringB
     tc_fence_after();
     for (int nci = 0; nci < g.nc; ++nci) {
       const uint32_t buf = nci & 1;
-      if (!warp_wait(smem_u32(&c->acc2_empty[buf]), ph_acc2[buf] ^ 1, af, p.dev_status))
-        return false;
-      ph_acc2[buf] ^= 1;
-      tc_fence_after();
       for (int k2 = 0; k2 < g.kc2; ++k2) {
-        if (!warp_wait(smem_u32(&c->fullB[pb.s]), pb.ph, af, p.dev_status)) return false;
+        if (!warp_wait(smem_u32(&c->fullB[pb.s]), pb.ph, af, p.dev_status,
+                       k2 == 0 ? smem_u32(&c->acc2_empty[buf]) : 0u, ph_acc2[buf] ^ 1))
+          return false;
+        if (k2 == 0) ph_acc2[buf] ^= 1;
         tc_fence_after();
         const uint64_t hd = descH0 + (uint64_t)(k2 * (SLOT >> 4));
         const uint64_t bd = descB0 + (uint64_t)(pb.s * (SLOT >> 4));
@@ -605,7 +628,7 @@ __device__ void role_epilogue(const Params& p, Ctl* c, uint32_t hs, uint32_t stg
     const uint32_t acc1 = tmem + lane_base + (la ? b1 * 128 : 0);
     if (!mbar_wait(smem_u32(&c->acc1_full[b1]), la ? ((i >> 1) & 1) : (i & 1), af, p.dev_status))
       return;
-    if (!mbar_wait(smem_u32(&c->hs_empty), (i & 1) ^ 1, af, p.dev_status)) return;
+    if (!mbar_wait_fast(smem_u32(&c->hs_empty), (i & 1) ^ 1, af, p.dev_status)) return;
     tc_fence_after();
     const float* bias =
         reinterpret_cast<const float*>(p.packed + (long long)t.e * g.stride + g.bias_off);
@@ -653,7 +676,7 @@ __device__ void role_epilogue(const Params& p, Ctl* c, uint32_t hs, uint32_t stg
       }
       const int rl = lane >> 3, pl = lane & 7;
       for (int nci = grp; nci < g.nc; nci += 2) {
-        if (!mbar_wait(smem_u32(&c->acc2_full[grp]), ph_mine, af, p.dev_status)) return;
+        if (!mbar_wait_fast(smem_u32(&c->acc2_full[grp]), ph_mine, af, p.dev_status)) return;
         ph_mine ^= 1;
         tc_fence_after();
         const int halves = g.nd >> 6;
