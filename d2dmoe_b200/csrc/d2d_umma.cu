@@ -35,8 +35,8 @@ constexpr int SLOT = TILE_M * 128;   // 16 KB: 128 rows x 64 bf16, also the weig
 constexpr int NA_MAX = 6;            // ring A stages (upper bound)
 constexpr int NB_MAX = 6;            // ring B stages (upper bound)
 constexpr int SLOTS_TOTAL = 14;      // ring A + ring B + hidden tile + staging (224 KB)
-constexpr int NTHREADS = 448;
-constexpr int WARP_MMA = 8, WARP_BULK = 9, WARP_PROD0 = 10;
+constexpr int NTHREADS = 480;
+constexpr int WARP_MMA1 = 8, WARP_MMA2 = 9, WARP_BULK = 10, WARP_PROD0 = 11;
 constexpr int MAX_E = 128;
 constexpr uint32_t WAIT_LIMIT = 1u << 22;
 constexpr int MODE_EXPERTS = 0, MODE_ROUTER = 1;
@@ -49,7 +49,8 @@ struct Geo {
   int kc2;       // ceil(K2 / 64)
   int nd;        // GEMM2 output columns per chunk (<= 128, multiple of 16)
   int nc;        // number of chunks
-  int nb;        // ring B stages
+  int nb;        // ring B1 stages (W1 tiles, consumed by the GEMM1 warp)
+  int nb2;       // ring B2 stages (W2 pieces, consumed by the GEMM2 warp)
   int na;        // ring A stages
   int stg;       // 16 KB slots of epilogue staging (experts: 2 = 32 rows x 128 B per warp)
   long long w1_bytes, bias_off, stride;   // packed layout per expert
@@ -87,8 +88,9 @@ Geo experts_geo(int d, int H, bool glu) {
   g.nd = (d % 128 == 0) ? 128 : 64;
   g.nc = d / g.nd;
   g.stg = 2;                       // 8 epilogue warps x 4 KB
-  g.na = glu ? 4 : 5;
-  g.nb = min(NB_MAX, SLOTS_TOTAL - g.na - g.kc2 - g.stg);
+  g.na = 4;
+  g.nb = glu ? 4 : 3;
+  g.nb2 = min(NB_MAX, SLOTS_TOTAL - g.na - g.nb - g.kc2 - g.stg);
   g.w1_bytes = (long long)g.kc1 * g.nsub * g.nsubw * 128;
   g.bias_off = g.w1_bytes + (long long)g.nc * g.kc2 * g.nd * 128;
   g.stride = (g.bias_off + 512 + 1023) / 1024 * 1024;
@@ -105,8 +107,9 @@ Geo router_geo(int d, int R, int E) {
   g.nd = (E + 15) / 16 * 16;
   g.nc = 1;
   g.stg = 0;
-  g.na = g.kc2 > 2 ? 5 : NA_MAX;
-  g.nb = min(NB_MAX, SLOTS_TOTAL - g.na - g.kc2);
+  g.na = g.kc2 > 2 ? 4 : NA_MAX;
+  g.nb = 4;
+  g.nb2 = min(NB_MAX, SLOTS_TOTAL - g.na - g.nb - g.kc2);
   g.w1_bytes = (long long)g.kc1 * g.nsub * g.nsubw * 128;
   g.bias_off = g.w1_bytes + (long long)g.nc * g.kc2 * g.nd * 128;
   g.stride = (g.bias_off + 512 + 1023) / 1024 * 1024;
@@ -140,6 +143,19 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
   asm volatile(
       "{\n\t.reg .pred p;\n\t"
       "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+// Non-blocking test (try_wait may suspend the thread for a while when the phase is not
+// complete; a loop that serves two rings must not sit in one of them).
+__device__ __forceinline__ bool mbar_test_wait(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
       "selp.u32 %0, 1, 0, p;\n\t}"
       : "=r"(ok)
       : "r"(bar), "r"(parity)
@@ -297,7 +313,8 @@ __device__ __forceinline__ float nanmax(float a, float b) {
 // ---------------------------------------------------------------------------
 struct Ctl {
   unsigned long long fullA[NA_MAX], emptyA[NA_MAX], fullB[NB_MAX], emptyB[NB_MAX];
-  unsigned long long acc1_full[2], hs_full, hs_empty, acc2_full[2], acc2_empty[2];
+  unsigned long long fullB2[NB_MAX], emptyB2[NB_MAX];
+  unsigned long long acc1_full[2], acc1_empty[2], hs_full, hs_empty, acc2_full[2], acc2_empty[2];
   uint32_t tmem_base;
   int abort_flag;
   int total_tiles;
@@ -418,69 +435,91 @@ __device__ void role_producer(const Params& p, Ctl* c, uint32_t ringA, int pt) {
   }
 }
 
-// Weight tiles in the order the MMA warp consumes them: W1 chunks of a tile, W2 pieces of
-// a tile; with lookahead the W1 chunks of tile i+1 come before the W2 pieces of tile i.
+// Weight tiles for both rings.  The two streams (W1 tiles for the GEMM1 warp, W2 pieces
+// for the GEMM2 warp) advance independently: whichever ring has a free stage gets its
+// next tile, so neither GEMM waits for the other's weights.
 template <int MODE>
-__device__ void role_bulk(const Params& p, Ctl* c, uint32_t ringB) {
+__device__ void role_bulk(const Params& p, Ctl* c, uint32_t ringB, uint32_t ringB2) {
   volatile int* af = &c->abort_flag;
   const Geo& g = p.g;
-  const uint32_t b1 = g.nsubw * 128, n1 = g.kc1 * g.nsub;
-  const uint32_t b2 = g.nd * 128, n2 = g.nc * g.kc2;
-  const bool la = lookahead(g);
-  uint32_t s = 0, ph = 0;
-  auto stream = [&](const uint8_t* src, uint32_t bytes, uint32_t n) -> bool {
-    for (uint32_t i = 0; i < n; ++i) {
-      if (!mbar_wait_fast(smem_u32(&c->emptyB[s]), ph ^ 1, af, p.dev_status)) return false;
-      const uint32_t bar = smem_u32(&c->fullB[s]);
+  const uint32_t b1 = g.nsubw * 128, b2 = g.nd * 128;
+  const int n1 = g.kc1 * g.nsub, n2 = g.nc * g.kc2;
+  const int step = gridDim.x, total = c->total_tiles;
+  RingPos r1 = {0, 0}, r2 = {0, 0};
+  int t1 = blockIdx.x, t2 = blockIdx.x, j1 = 0, j2 = 0;
+  const uint8_t *pe1 = nullptr, *pe2 = nullptr;
+  if (t1 < total) pe1 = pe2 = p.packed + (long long)tile_info<MODE>(p, c, t1).e * g.stride;
+  uint32_t idle = 0;
+  while (t1 < total || t2 < total) {
+    bool progress = false;
+    // every decision below is warp-uniform (votes), so elect.sync sees the whole warp
+    if (t1 < total &&
+        __all_sync(0xffffffffu, mbar_test_wait(smem_u32(&c->emptyB[r1.s]), r1.ph ^ 1))) {
+      const uint32_t bar = smem_u32(&c->fullB[r1.s]);
       if (elect_one()) {
-        mbar_arrive_expect_tx(bar, bytes);
-        bulk_g2s(ringB + s * SLOT, src + (long long)i * bytes, bytes, bar);
+        mbar_arrive_expect_tx(bar, b1);
+        bulk_g2s(ringB + r1.s * SLOT, pe1 + (long long)j1 * b1, b1, bar);
       }
       __syncwarp();
-      if (++s == (uint32_t)g.nb) {
-        s = 0;
-        ph ^= 1;
+      r1.next(g.nb);
+      if (++j1 == n1) {
+        j1 = 0;
+        t1 += step;
+        if (t1 < total) pe1 = p.packed + (long long)tile_info<MODE>(p, c, t1).e * g.stride;
       }
+      progress = true;
     }
-    return true;
-  };
-  const int first = blockIdx.x, step = gridDim.x, total = c->total_tiles;
-  if (first >= total) return;
-  const uint8_t* pe = p.packed + (long long)tile_info<MODE>(p, c, first).e * g.stride;
-  if (la && !stream(pe, b1, n1)) return;
-  for (int tile = first; tile < total; tile += step) {
-    if (la) {
-      if (tile + step < total) {
-        const uint8_t* pn = p.packed + (long long)tile_info<MODE>(p, c, tile + step).e * g.stride;
-        if (!stream(pn, b1, n1)) return;
-        if (!stream(pe + g.w1_bytes, b2, n2)) return;
-        pe = pn;
-      } else if (!stream(pe + g.w1_bytes, b2, n2)) {
+    if (t2 < total &&
+        __all_sync(0xffffffffu, mbar_test_wait(smem_u32(&c->emptyB2[r2.s]), r2.ph ^ 1))) {
+      const uint32_t bar = smem_u32(&c->fullB2[r2.s]);
+      if (elect_one()) {
+        mbar_arrive_expect_tx(bar, b2);
+        bulk_g2s(ringB2 + r2.s * SLOT, pe2 + g.w1_bytes + (long long)j2 * b2, b2, bar);
+      }
+      __syncwarp();
+      r2.next(g.nb2);
+      if (++j2 == n2) {
+        j2 = 0;
+        t2 += step;
+        if (t2 < total) pe2 = p.packed + (long long)tile_info<MODE>(p, c, t2).e * g.stride;
+      }
+      progress = true;
+    }
+    if (progress) {
+      idle = 0;
+    } else {
+      if (++idle > 64) __nanosleep(idle > 4096 ? 256 : 32);
+      if ((idle & 63) == 0 && __any_sync(0xffffffffu, *af != 0)) return;
+      if (idle >= WAIT_LIMIT) {
+        if ((threadIdx.x & 31) == 0) {
+          *af = 1;
+          report(p.dev_status, D2D_ERR_TIMEOUT);
+        }
         return;
       }
-    } else {
-      pe = p.packed + (long long)tile_info<MODE>(p, c, tile).e * g.stride;
-      if (!stream(pe, b1, n1)) return;
-      if (!stream(pe + g.w1_bytes, b2, n2)) return;
     }
   }
 }
 
+// GEMM1 stream: acc1[buffer][sub] = A(rows, d) * W1sub(d, nsubw), one tile after another.
 template <int MODE>
-__device__ void role_mma(const Params& p, Ctl* c, uint32_t ringA, uint32_t ringB, uint32_t hs,
-                         uint32_t tmem_in) {
+__device__ void role_mma1(const Params& p, Ctl* c, uint32_t ringA, uint32_t ringB,
+                          uint32_t tmem_in) {
   volatile int* af = &c->abort_flag;
   const Geo& g = p.g;
   const uint32_t tmem = __shfl_sync(0xffffffffu, tmem_in, 0);
-  const uint32_t idesc1 = instr_desc(TILE_M, g.nsubw), idesc2 = instr_desc(TILE_M, g.nd);
-  const uint64_t descA0 = smem_desc(ringA), descB0 = smem_desc(ringB), descH0 = smem_desc(hs);
+  const uint32_t idesc1 = instr_desc(TILE_M, g.nsubw);
+  const uint64_t descA0 = smem_desc(ringA), descB0 = smem_desc(ringB);
   const bool la = lookahead(g);
   RingPos pa = {0, 0}, pb = {0, 0};
-  uint32_t ph_acc2[2] = {0, 0};
-
-  // GEMM1 of one tile into acc1 buffer b: acc1[sub] = A(rows, d) * W1sub(d, nsubw)
-  auto gemm1 = [&](uint32_t b) -> bool {
+  uint32_t i = 0;
+  for (int tile = blockIdx.x; tile < c->total_tiles; tile += gridDim.x, ++i) {
+    const uint32_t b = la ? (i & 1) : 0;
+    const uint32_t use = la ? (i >> 1) : i;              // how often this buffer was used
     const uint32_t acc = tmem + (la ? b * 128 : 0);
+    // the epilogue warps must have read the previous contents of this buffer
+    if (!warp_wait(smem_u32(&c->acc1_empty[b]), (use & 1) ^ 1, af, p.dev_status)) return;
+    tc_fence_after();
     for (int kc = 0; kc < g.kc1; ++kc) {
       const uint32_t sb0 = pb.s, ph0 = pb.ph;
       pb.next(g.nb);
@@ -489,7 +528,7 @@ __device__ void role_mma(const Params& p, Ctl* c, uint32_t ringA, uint32_t ringB
       if (!warp_wait(smem_u32(&c->fullA[pa.s]), pa.ph, af, p.dev_status,
                      smem_u32(&c->fullB[sb0]), ph0,
                      g.nsub == 2 ? smem_u32(&c->fullB[sb1]) : 0u, ph1))
-        return false;
+        return;
       tc_fence_after();
       // descriptors advance in 16-byte units: one slot = 1024 units, one k-step = 2
       const uint64_t ad = descA0 + (uint64_t)(pa.s * (SLOT >> 4));
@@ -509,18 +548,30 @@ __device__ void role_mma(const Params& p, Ctl* c, uint32_t ringA, uint32_t ringB
       __syncwarp();
       pa.next(g.na);
     }
-    return true;
-  };
-  // GEMM2 of one tile: acc2[chunk & 1] = Hs(rows, K2) * W2chunk(K2, nd)
-  auto gemm2 = [&](uint32_t ph_tile) -> bool {
-    if (!warp_wait(smem_u32(&c->hs_full), ph_tile, af, p.dev_status)) return false;
+  }
+}
+
+// GEMM2 stream: acc2[chunk & 1] = Hs(rows, K2) * W2chunk(K2, nd) for every chunk of a tile.
+template <int MODE>
+__device__ void role_mma2(const Params& p, Ctl* c, uint32_t ringB2, uint32_t hs,
+                          uint32_t tmem_in) {
+  volatile int* af = &c->abort_flag;
+  const Geo& g = p.g;
+  const uint32_t tmem = __shfl_sync(0xffffffffu, tmem_in, 0);
+  const uint32_t idesc2 = instr_desc(TILE_M, g.nd);
+  const uint64_t descB0 = smem_desc(ringB2), descH0 = smem_desc(hs);
+  RingPos pb = {0, 0};
+  uint32_t ph_acc2[2] = {0, 0};
+  uint32_t i = 0;
+  for (int tile = blockIdx.x; tile < c->total_tiles; tile += gridDim.x, ++i) {
+    if (!warp_wait(smem_u32(&c->hs_full), i & 1, af, p.dev_status)) return;
     tc_fence_after();
     for (int nci = 0; nci < g.nc; ++nci) {
       const uint32_t buf = nci & 1;
       for (int k2 = 0; k2 < g.kc2; ++k2) {
-        if (!warp_wait(smem_u32(&c->fullB[pb.s]), pb.ph, af, p.dev_status,
+        if (!warp_wait(smem_u32(&c->fullB2[pb.s]), pb.ph, af, p.dev_status,
                        k2 == 0 ? smem_u32(&c->acc2_empty[buf]) : 0u, ph_acc2[buf] ^ 1))
-          return false;
+          return;
         if (k2 == 0) ph_acc2[buf] ^= 1;
         tc_fence_after();
         const uint64_t hd = descH0 + (uint64_t)(k2 * (SLOT >> 4));
@@ -531,30 +582,16 @@ __device__ void role_mma(const Params& p, Ctl* c, uint32_t ringA, uint32_t ringB
           for (int k = 0; k < 4; ++k)
             if (k < ksteps)
               umma_bf16(tmem + 256 + buf * 128, hd + 2 * k, bd + 2 * k, idesc2, (k2 | k) != 0);
-          umma_commit(smem_u32(&c->emptyB[pb.s]));
+          umma_commit(smem_u32(&c->emptyB2[pb.s]));
           if (k2 == g.kc2 - 1) {
             umma_commit(smem_u32(&c->acc2_full[buf]));
             if (nci == g.nc - 1) umma_commit(smem_u32(&c->hs_empty));
           }
         }
         __syncwarp();
-        pb.next(g.nb);
+        pb.next(g.nb2);
       }
     }
-    return true;
-  };
-
-  const int first = blockIdx.x, step = gridDim.x, total = c->total_tiles;
-  if (first >= total) return;
-  uint32_t i = 0;
-  if (la && !gemm1(0)) return;
-  for (int tile = first; tile < total; tile += step, ++i) {
-    if (la) {
-      if (tile + step < total && !gemm1((i + 1) & 1)) return;
-    } else if (!gemm1(0)) {
-      return;
-    }
-    if (!gemm2(i & 1)) return;
   }
 }
 
@@ -599,17 +636,19 @@ __device__ void role_epilogue(const Params& p, Ctl* c, uint32_t hs, uint32_t stg
   for (int tile = blockIdx.x; tile < c->total_tiles; tile += gridDim.x, ++i) {
     const Tile t = tile_info<MODE>(p, c, tile);
     if (MODE == MODE_ROUTER && p.out_init) {
-      // initial value of the layer output for this tile's tokens: last_bias (+ x);
-      // one warp per row, 16 bytes per lane
+      // initial value of the layer output for this tile's tokens: last_bias (+ x).
+      // Lane = one 16-byte column piece (kept in a register), rows of this warp inside.
       const int v8 = p.d >> 3;
-      for (int row = w8; row < t.nrows; row += 8) {
-        const long long rowoff = ((long long)t.r0 + row) * p.d;
-        for (int c8 = lane; c8 < v8; c8 += 32) {
-          uint4 o = make_uint4(0u, 0u, 0u, 0u);
-          if (p.last_bias) o = __ldg(reinterpret_cast<const uint4*>(p.last_bias) + c8);
+      for (int c8 = lane; c8 < v8; c8 += 32) {
+        uint4 bz = make_uint4(0u, 0u, 0u, 0u);
+        if (p.last_bias) bz = __ldg(reinterpret_cast<const uint4*>(p.last_bias) + c8);
+#pragma unroll 4
+        for (int row = w8; row < t.nrows; row += 8) {
+          const long long rowoff = ((long long)t.r0 + row) * p.d;
+          uint4 o = bz;
           if (p.add_residual) {
             const uint4 xv = *(reinterpret_cast<const uint4*>(p.x + rowoff) + c8);
-            const __nv_bfloat162* a = reinterpret_cast<const __nv_bfloat162*>(&o);
+            const __nv_bfloat162* a = reinterpret_cast<const __nv_bfloat162*>(&bz);
             const __nv_bfloat162* b = reinterpret_cast<const __nv_bfloat162*>(&xv);
             uint32_t ww[4];
 #pragma unroll
@@ -664,8 +703,9 @@ __device__ void role_epilogue(const Params& p, Ctl* c, uint32_t hs, uint32_t stg
       st_shared_v4(base + (((j0) ^ (r & 7)) << 4), w[0], w[1], w[2], w[3]);
       st_shared_v4(base + (((j0 + 1) ^ (r & 7)) << 4), w[4], w[5], w[6], w[7]);
     }
-    fence_proxy_async();     // ordinary shared stores -> visible to the MMA's async reads
     tc_fence_before();
+    mbar_arrive(smem_u32(&c->acc1_empty[b1]));     // acc1 buffer read completely
+    fence_proxy_async();     // ordinary shared stores -> visible to the MMA's async reads
     mbar_arrive(smem_u32(&c->hs_full));
     // ---- epilogue 2 -------------------------------------------------------------
     if (MODE == MODE_EXPERTS) {
@@ -766,10 +806,11 @@ __global__ void __launch_bounds__(NTHREADS, 1) mlp_tiles_kernel(const Params p) 
   uint8_t* aligned = smem_raw + (base - raw);
   const uint32_t ringA = base;
   const uint32_t ringB = ringA + p.g.na * SLOT;
-  const uint32_t hs = ringB + p.g.nb * SLOT;
+  const uint32_t ringB2 = ringB + p.g.nb * SLOT;
+  const uint32_t hs = ringB2 + p.g.nb2 * SLOT;
   const uint32_t stg = hs + p.g.kc2 * SLOT;
-  Ctl* c = reinterpret_cast<Ctl*>(aligned +
-                                  (size_t)(p.g.na + p.g.nb + p.g.kc2 + p.g.stg) * SLOT);
+  Ctl* c = reinterpret_cast<Ctl*>(
+      aligned + (size_t)(p.g.na + p.g.nb + p.g.nb2 + p.g.kc2 + p.g.stg) * SLOT);
   const int tid = threadIdx.x, warp = tid >> 5;
 
   if (tid == 0) {
@@ -780,11 +821,14 @@ __global__ void __launch_bounds__(NTHREADS, 1) mlp_tiles_kernel(const Params p) 
     for (int i = 0; i < NB_MAX; ++i) {
       mbar_init(smem_u32(&c->fullB[i]), 1);
       mbar_init(smem_u32(&c->emptyB[i]), 1);
+      mbar_init(smem_u32(&c->fullB2[i]), 1);
+      mbar_init(smem_u32(&c->emptyB2[i]), 1);
     }
     mbar_init(smem_u32(&c->hs_full), 256);
     mbar_init(smem_u32(&c->hs_empty), 1);
     for (int i = 0; i < 2; ++i) {
       mbar_init(smem_u32(&c->acc1_full[i]), 1);
+      mbar_init(smem_u32(&c->acc1_empty[i]), 256);
       mbar_init(smem_u32(&c->acc2_full[i]), 1);
       mbar_init(smem_u32(&c->acc2_empty[i]), 128);
     }
@@ -805,7 +849,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) mlp_tiles_kernel(const Params p) 
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     fence_proxy_async();
   }
-  if (warp == WARP_MMA) tmem_alloc(smem_u32(&c->tmem_base), 512);
+  if (warp == WARP_MMA1) tmem_alloc(smem_u32(&c->tmem_base), 512);
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
@@ -813,10 +857,12 @@ __global__ void __launch_bounds__(NTHREADS, 1) mlp_tiles_kernel(const Params p) 
 
   if (warp < 8) {
     role_epilogue<MODE>(p, c, hs, stg, tmem, tid);
-  } else if (warp == WARP_MMA) {
-    role_mma<MODE>(p, c, ringA, ringB, hs, tmem);
+  } else if (warp == WARP_MMA1) {
+    role_mma1<MODE>(p, c, ringA, ringB, tmem);
+  } else if (warp == WARP_MMA2) {
+    role_mma2<MODE>(p, c, ringB2, hs, tmem);
   } else if (warp == WARP_BULK) {
-    role_bulk<MODE>(p, c, ringB);
+    role_bulk<MODE>(p, c, ringB, ringB2);
   } else {
     role_producer<MODE>(p, c, ringA, tid - WARP_PROD0 * 32);
     cp_async_wait_all();
@@ -824,7 +870,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) mlp_tiles_kernel(const Params p) 
 
   tc_fence_before();
   __syncthreads();
-  if (warp == WARP_MMA) {
+  if (warp == WARP_MMA1) {
     tc_fence_after();
     tmem_dealloc(tmem, 512);
   }
@@ -908,7 +954,7 @@ int sm_count() {
 }
 
 size_t smem_bytes(const Geo& g) {
-  return 1024 + (size_t)(g.na + g.nb + g.kc2 + g.stg) * SLOT + sizeof(Ctl) + 64;
+  return 1024 + (size_t)(g.na + g.nb + g.nb2 + g.kc2 + g.stg) * SLOT + sizeof(Ctl) + 64;
 }
 
 template <int MODE>
