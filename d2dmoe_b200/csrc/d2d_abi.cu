@@ -31,7 +31,7 @@ const char* d2d_strerror(int status) {
     case D2D_ERR_NO_DEVICE: return "no sm_100 CUDA device is current";
     case D2D_ERR_SCRATCH_LIMIT:
       return "size exceeds the built-in scratch array of the no-allocation entry point "
-             "(ceil(N/1024)*E must be <= 65536); use d2d_compact with a caller workspace";
+             "(ceil(N/128)*E must be <= 262144); use d2d_compact with a caller workspace";
     default: return "unknown status";
   }
 }
@@ -52,7 +52,7 @@ int d2d_router_mask(const void* x, const void* wa, const void* wb, const void* r
   cudaStream_t s = (cudaStream_t)stream;
   if (router_packed_opt && umma_router_supported(d, R, E, dtype))
     return launch_router_mask_umma(x, router_packed_opt, thresh_mult, mask_bits, scores_opt,
-                                   last_bias_opt, add_residual, out_init_opt, N, d, R, E,
+                                   last_bias_opt, add_residual, out_init_opt, nullptr, N, d, R, E,
                                    dev_status, s);
   return launch_router_mask_simt(x, wa, wb, thresh_mult, mask_bits, scores_opt, last_bias_opt,
                                  add_residual, out_init_opt, N, d, R, E, dtype, dev_status, s);
@@ -97,7 +97,7 @@ int d2d_compact(const uint32_t* mask_bits, int32_t* token_idx, int32_t* offsets,
   if (!aligned(ws, 16)) return D2D_ERR_BAD_ARG;
   if (ws_bytes < compact_workspace_bytes(N, E)) return D2D_ERR_WORKSPACE;
   return launch_compact(mask_bits, token_idx, offsets, N, E, (int32_t*)ws, dev_status,
-                        (cudaStream_t)stream);
+                        (cudaStream_t)stream, false);
 }
 
 int d2d_experts_ffn(const void* x, const int32_t* token_idx, const int32_t* offsets,
@@ -130,19 +130,30 @@ int d2d_moe_forward(const void* x, const void* wa, const void* wb, const void* r
                     int64_t N, int d, int R, int E, int H, int act, int dtype, void* ws,
                     size_t ws_bytes, int* dev_status, d2d_stream_t stream) {
   int rc;
+  bool counts_ready = false;
   if (!wa && !scores_in_opt) return D2D_ERR_BAD_ARG;
+  if (!mask_bits || !token_idx || !offsets || !ws || !aligned(ws, 16)) return D2D_ERR_BAD_ARG;
+  if (ws_bytes < compact_workspace_bytes(N, E)) return D2D_ERR_WORKSPACE;
   if (N == 0) return D2D_OK;
   if (scores_in_opt) {
     rc = d2d_mask_from_scores(scores_in_opt, thresh_mult, mask_bits, N, E, dtype, dev_status,
                               stream);
     if (rc != D2D_OK) return rc;
     rc = d2d_init_out(x, last_bias_opt, add_residual, out, N, d, dtype, stream);
+  } else if (router_packed_opt && x && wb && dtype_ok(dtype) && d >= 1 && R >= 1 && E >= 1 &&
+             umma_router_supported(d, R, E, dtype)) {
+    // the tensor-core router also fills the compaction's counts table
+    rc = launch_router_mask_umma(x, router_packed_opt, thresh_mult, mask_bits, nullptr,
+                                 last_bias_opt, add_residual, out, (int32_t*)ws, N, d, R, E,
+                                 dev_status, (cudaStream_t)stream);
+    counts_ready = true;
   } else {
     rc = d2d_router_mask(x, wa, wb, router_packed_opt, thresh_mult, mask_bits, nullptr,
                          last_bias_opt, add_residual, out, N, d, R, E, dtype, dev_status, stream);
   }
   if (rc != D2D_OK) return rc;
-  rc = d2d_compact(mask_bits, token_idx, offsets, N, E, ws, ws_bytes, dev_status, stream);
+  rc = launch_compact(mask_bits, token_idx, offsets, N, E, (int32_t*)ws, dev_status,
+                      (cudaStream_t)stream, counts_ready);
   if (rc != D2D_OK) return rc;
   return d2d_experts_ffn(x, token_idx, offsets, w1, b1_opt, w_up_opt, w2, experts_packed_opt,
                          nullptr, 0, /*accumulate=*/1, out, N, d, E, H, act, dtype, dev_status,

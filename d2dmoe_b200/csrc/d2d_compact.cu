@@ -5,10 +5,11 @@
 // The sort only serves to bring each expert's tokens to the front of its column;
 // a compaction gives the same set per expert, here in ascending token order.
 //
-// Two launches over chunks of 1024 tokens:
-//   count   : counts[chunk][e] = tokens of the chunk that keep expert e
-//   scatter : every CTA rebuilds its base from the counts table (sum over earlier
-//             chunks + exclusive scan over experts) and writes its token indices.
+// Two launches:
+//   count   : counts[tile][e] = tokens of the 128-token tile that keep expert e
+//             (skipped when the router kernel already wrote the table)
+//   scatter : one CTA per 1024 tokens rebuilds its base from the counts table (sum over
+//             earlier tiles + exclusive scan over experts) and writes its token indices.
 // Integer work, bit-exact by construction; HBM traffic is the mask (read twice)
 // plus 4 bytes per kept token-expert pair.
 #include "d2d_common.cuh"
@@ -17,38 +18,43 @@ namespace d2d {
 namespace {
 
 constexpr int NT = 256;
-constexpr int ROWS = 32;                 // 32 rows of 32 tokens per CTA
+constexpr int ROWS = 32;                 // 32 rows of 32 tokens per scatter CTA
 constexpr int CHUNK = ROWS * 32;
+constexpr int CTILE = 128;               // granularity of the counts table
+constexpr int TILES_PER_CHUNK = CHUNK / CTILE;
 constexpr int MAX_E = 256;
 
+// one warp = one 128-token tile; lane b ends up with the count of expert 32j+b
 __global__ void __launch_bounds__(NT)
 compact_count_kernel(const uint32_t* __restrict__ mask_bits, int32_t* __restrict__ counts,
                      int64_t N, int E) {
-  __shared__ int cnt[MAX_E];
-  const int tid = threadIdx.x, lane = tid & 31, w = tid >> 5;
+  const int lane = threadIdx.x & 31;
+  const int64_t tile = (int64_t)blockIdx.x * (NT / 32) + (threadIdx.x >> 5);
+  if (tile * CTILE >= N) return;
   const int nw = (E + 31) / 32;
-  for (int e = tid; e < E; e += NT) cnt[e] = 0;
-  __syncthreads();
-  for (int r = 0; r < 4; ++r) {
-    const int64_t t = (int64_t)blockIdx.x * CHUNK + (4 * w + r) * 32 + lane;
-    for (int j = 0; j < nw; ++j) {
-      const uint32_t word = t < N ? mask_bits[t * nw + j] : 0u;
-      if (__ballot_sync(0xffffffffu, word != 0u) == 0u) continue;
-      const int nb = min(32, E - 32 * j);
-      for (int b = 0; b < nb; ++b) {
-        const uint32_t v = __ballot_sync(0xffffffffu, (word >> b) & 1u);
-        if (lane == 0 && v) atomicAdd(&cnt[32 * j + b], __popc(v));
-      }
+  for (int j = 0; j < nw; ++j) {
+    uint32_t w[4];
+#pragma unroll
+    for (int r = 0; r < 4; ++r) {
+      const int64_t t = tile * CTILE + r * 32 + lane;
+      w[r] = t < N ? mask_bits[t * nw + j] : 0u;
     }
+    int mine = 0;
+    const int nb = min(32, E - 32 * j);
+    for (int b = 0; b < nb; ++b) {
+      int cb = 0;
+#pragma unroll
+      for (int r = 0; r < 4; ++r) cb += __popc(__ballot_sync(0xffffffffu, (w[r] >> b) & 1u));
+      if (lane == b) mine = cb;
+    }
+    if (lane < nb) counts[tile * E + 32 * j + lane] = mine;
   }
-  __syncthreads();
-  for (int e = tid; e < E; e += NT) counts[(int64_t)blockIdx.x * E + e] = cnt[e];
 }
 
 __global__ void __launch_bounds__(NT)
 compact_scatter_kernel(const uint32_t* __restrict__ mask_bits, const int32_t* __restrict__ counts,
                        int32_t* __restrict__ token_idx, int32_t* __restrict__ offsets, int64_t N,
-                       int E, int nchunks, int* dev_status) {
+                       int E, int ntiles, int* dev_status) {
   extern __shared__ int sm[];
   int* cnt = sm;                 // [ROWS][E] -> becomes each row's write base
   int* tot = cnt + ROWS * E;     // [E]   total per expert, then exclusive offsets
@@ -63,16 +69,23 @@ compact_scatter_kernel(const uint32_t* __restrict__ mask_bits, const int32_t* __
     pre[e] = 0;
   }
   __syncthreads();
-  // column sums of the counts table, all threads loading in parallel (coalesced over e)
-  for (int i = tid; i < nchunks * E; i += NT) {
-    const int v = counts[i];
-    if (v) {
-      const int cc = i / E, e = i - cc * E;
-      atomicAdd(&tot[e], v);
-      if (cc < chunk) atomicAdd(&pre[e], v);
+  // column sums of the counts table: thread (grp, e) adds up tiles grp, grp+groups, ...
+  // in registers (coalesced over e), then one shared atomic per thread
+  {
+    const int groups = max(1, NT / E);
+    const int first_tile = chunk * TILES_PER_CHUNK;
+    const int e = tid % E, grp = tid / E;
+    if (grp < groups) {
+      int a = 0, b = 0;
+      for (int t = grp; t < ntiles; t += groups) {
+        const int v = counts[(int64_t)t * E + e];
+        a += v;
+        if (t < first_tile) b += v;
+      }
+      atomicAdd(&tot[e], a);
+      atomicAdd(&pre[e], b);
     }
   }
-  __syncthreads();
   // per-row popcounts of this chunk
   for (int r = 0; r < 4; ++r) {
     const int row = 4 * w + r;
@@ -87,6 +100,7 @@ compact_scatter_kernel(const uint32_t* __restrict__ mask_bits, const int32_t* __
       }
     }
   }
+  __syncthreads();
   // exclusive scan of the expert totals (E <= 256: one warp, 8 values per lane)
   if (w == 0) {
     int v[8], s = 0;
@@ -144,17 +158,22 @@ compact_scatter_kernel(const uint32_t* __restrict__ mask_bits, const int32_t* __
 }  // namespace
 
 size_t compact_workspace_bytes(int64_t n_max, int E) {
-  const int64_t nchunks = ceil_div64(n_max > 0 ? n_max : 1, CHUNK);
-  return (size_t)nchunks * (size_t)E * sizeof(int32_t);
+  const int64_t ntiles = ceil_div64(n_max > 0 ? n_max : 1, CTILE);
+  return (size_t)ntiles * (size_t)E * sizeof(int32_t);
 }
 
 int launch_compact(const uint32_t* mask_bits, int32_t* token_idx, int32_t* offsets, int64_t N,
-                   int E, int32_t* counts_ws, int* dev_status, cudaStream_t s) {
+                   int E, int32_t* counts_ws, int* dev_status, cudaStream_t s,
+                   bool counts_ready) {
   if (E > MAX_E || E < 1) return D2D_ERR_UNSUPPORTED;
   if (N * (int64_t)E > 0x7fffffffLL) return D2D_ERR_UNSUPPORTED;   // int32 offsets
+  const int64_t ntiles = ceil_div64(N > 0 ? N : 1, CTILE);
   const int64_t nchunks = ceil_div64(N > 0 ? N : 1, CHUNK);
-  compact_count_kernel<<<(unsigned)nchunks, NT, 0, s>>>(mask_bits, counts_ws, N, E);
-  if (cudaGetLastError() != cudaSuccess) return D2D_ERR_LAUNCH;
+  if (!counts_ready) {
+    compact_count_kernel<<<(unsigned)ceil_div64(ntiles, NT / 32), NT, 0, s>>>(mask_bits, counts_ws,
+                                                                             N, E);
+    if (cudaGetLastError() != cudaSuccess) return D2D_ERR_LAUNCH;
+  }
   const size_t smem = sizeof(int) * ((size_t)ROWS * E + 2 * (size_t)E);
   if (smem > 48 * 1024) {
     if (cudaFuncSetAttribute(compact_scatter_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
@@ -162,7 +181,7 @@ int launch_compact(const uint32_t* mask_bits, int32_t* token_idx, int32_t* offse
       return D2D_ERR_LAUNCH;
   }
   compact_scatter_kernel<<<(unsigned)nchunks, NT, smem, s>>>(mask_bits, counts_ws, token_idx,
-                                                             offsets, N, E, (int)nchunks,
+                                                             offsets, N, E, (int)ntiles,
                                                              dev_status);
   return cudaGetLastError() == cudaSuccess ? D2D_OK : D2D_ERR_LAUNCH;
 }
@@ -179,17 +198,17 @@ int launch_compact(const uint32_t* mask_bits, int32_t* token_idx, int32_t* offse
 // table lives in the library itself, in a fixed device array that every GPU
 // loading the library holds until the process exits.
 //
-// Limit: D2D_NOALLOC_MAX_CELLS table cells = ceil(N/1024) * E; e.g. 262144 tokens
-// x 256 experts, or 1M tokens x 64 experts.  Larger requests are refused with
+// Limit: D2D_NOALLOC_MAX_CELLS table cells = ceil(N/128) * E (1 MiB); e.g. 262144
+// tokens x 128 experts, or 1M tokens x 32 experts.  Larger requests are refused with
 // D2D_ERR_SCRATCH_LIMIT before anything is launched.
 //
 // The table is shared by every call in the process and keeps the previous call's
 // contents.  Nothing in it needs clearing: the count kernel writes every cell the
-// scatter kernel later reads (all E cells of each of the ceil(N/1024) chunks).
+// scatter kernel later reads (all E cells of each of the ceil(N/128) tiles).
 // Two calls that run concurrently on one GPU (different streams) would overwrite
 // each other's counts: keep such calls on one stream or order them with events.
 // ---------------------------------------------------------------------------
-#define D2D_NOALLOC_MAX_CELLS (256 * 256)
+#define D2D_NOALLOC_MAX_CELLS (2048 * 128)
 
 static __device__ __align__(256) int32_t g_noalloc_counts[D2D_NOALLOC_MAX_CELLS];
 
@@ -224,11 +243,11 @@ int noalloc_scratch(int32_t** out) {
 extern "C" int d2d_compact_noalloc(const uint32_t* mask_bits, int32_t* token_idx, int32_t* offsets,
                                    int64_t N, int E, int* dev_status, d2d_stream_t stream) {
   if (!mask_bits || !token_idx || !offsets || N < 0 || E < 1) return D2D_ERR_BAD_ARG;
-  const int64_t nchunks = d2d::ceil_div64(N > 0 ? N : 1, d2d::CHUNK);
-  if (nchunks * (int64_t)E > D2D_NOALLOC_MAX_CELLS) return D2D_ERR_SCRATCH_LIMIT;
+  const int64_t ntiles = d2d::ceil_div64(N > 0 ? N : 1, d2d::CTILE);
+  if (ntiles * (int64_t)E > D2D_NOALLOC_MAX_CELLS) return D2D_ERR_SCRATCH_LIMIT;
   int32_t* counts = nullptr;
   const int rc = noalloc_scratch(&counts);   // first call on a device looks the address up
   if (rc != D2D_OK) return rc;
   return d2d::launch_compact(mask_bits, token_idx, offsets, N, E, counts, dev_status,
-                             (cudaStream_t)stream);
+                             (cudaStream_t)stream, false);
 }

@@ -75,6 +75,7 @@ struct Params {
   const bf16* last_bias;
   int add_residual;
   bf16* out_init;
+  int32_t* tile_counts;     // [tiles][E]: per-expert kept-token counts of each 128-token tile
   int* dev_status;
 };
 
@@ -318,6 +319,7 @@ struct Ctl {
   uint32_t tmem_base;
   int abort_flag;
   int total_tiles;
+  int tile_cnt[MAX_E];
   int tstart[MAX_E + 1];
 };
 
@@ -770,7 +772,7 @@ __device__ void role_epilogue(const Params& p, Ctl* c, uint32_t hs, uint32_t stg
       }
       const float thr = bfr(__fmul_rn(m, p.mult));
       const int nw = (E + 31) >> 5;
-      uint32_t word = 0;
+      uint32_t word = 0, mw[4] = {0u, 0u, 0u, 0u};
       for (int c0 = 0; c0 < g.nd; c0 += 16) {
         uint32_t v[16];
         tmem_ld16(tmem + lane_base + 256 + c0, v);
@@ -785,12 +787,32 @@ __device__ void role_epilogue(const Params& p, Ctl* c, uint32_t hs, uint32_t stg
         }
         if (((c0 + 16) & 31) == 0 || c0 + 16 >= g.nd) {
           const int jw = c0 >> 5;
-          if (r < t.nrows && jw < nw) p.mask_bits[trow * nw + jw] = word;
+          if (r < t.nrows && jw < nw) {
+            p.mask_bits[trow * nw + jw] = word;
+            mw[jw & 3] = word;
+          }
           word = 0;
         }
       }
       tc_fence_before();
       mbar_arrive(smem_u32(&c->acc2_empty[0]));
+      if (p.tile_counts) {
+        // per-expert counts of this tile for the compaction: ballots per warp, summed
+        // over the group's four warps in shared memory
+        if (r < E) c->tile_cnt[r] = 0;
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        for (int jw = 0; jw < nw; ++jw) {
+          const int nb = min(32, E - 32 * jw);
+          int mine = 0;
+          for (int b = 0; b < nb; ++b) {
+            const int cb = __popc(__ballot_sync(0xffffffffu, (mw[jw] >> b) & 1u));
+            if (lane == b) mine = cb;
+          }
+          if (lane < nb && mine) atomicAdd(&c->tile_cnt[32 * jw + lane], mine);
+        }
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        if (r < E) p.tile_counts[(long long)tile * E + r] = c->tile_cnt[r];
+      }
     }
   }
 }
@@ -1039,7 +1061,8 @@ int launch_prepack_router(const void* wa, const void* wb, void* packed, int d, i
 
 int launch_router_mask_umma(const void* x, const void* packed, float mult, uint32_t* mask_bits,
                             void* scores, const void* last_bias, int add_residual, void* out_init,
-                            int64_t N, int d, int R, int E, int* dev_status, cudaStream_t s) {
+                            int32_t* tile_counts, int64_t N, int d, int R, int E, int* dev_status,
+                            cudaStream_t s) {
   Params p = {};
   p.x = (const bf16*)x;
   p.N = N;
@@ -1053,6 +1076,7 @@ int launch_router_mask_umma(const void* x, const void* packed, float mult, uint3
   p.last_bias = (const bf16*)last_bias;
   p.add_residual = add_residual;
   p.out_init = (bf16*)out_init;
+  p.tile_counts = tile_counts;
   p.dev_status = dev_status;
   return launch<MODE_ROUTER>(p, (N + TILE_M - 1) / TILE_M, s);
 }

@@ -18,6 +18,7 @@ int launch_prepack_router(const void* wa, const void* wb, void* packed, int d, i
                           cudaStream_t s);
 int launch_router_mask_umma(const void* x, const void* packed, float mult, uint32_t* mask_bits,
                             void* scores, const void* last_bias, int add_residual, void* out_init,
-                            int64_t N, int d, int R, int E, int* dev_status, cudaStream_t s);
+                            int32_t* tile_counts, int64_t N, int d, int R, int E, int* dev_status,
+                            cudaStream_t s);
 
 }  // namespace d2d

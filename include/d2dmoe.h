@@ -126,8 +126,8 @@ int d2d_compact(const uint32_t* mask_bits, int32_t* token_idx, int32_t* offsets,
  * (No counterpart upstream: the upstream path allocates its scratch inside every
  * call.)  Same outputs as d2d_compact, bit for bit.  The counts table is a fixed
  * array inside the library, held by every GPU that loads it until the process
- * exits: 256 KiB, which covers ceil(N/1024) * E <= 65536 (e.g. N = 262144 with
- * E = 256); beyond that the call returns D2D_ERR_SCRATCH_LIMIT and launches
+ * exits: 1 MiB, which covers ceil(N/128) * E <= 262144 (e.g. N = 262144 with
+ * E = 128); beyond that the call returns D2D_ERR_SCRATCH_LIMIT and launches
  * nothing.  It calls no allocating routine.  The first call on each device looks up
  * the array's device address (with that device current); make that first call
  * outside any stream capture.  All calls share the one array: calls that can run

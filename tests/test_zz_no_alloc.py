@@ -61,7 +61,7 @@ def test_noalloc_rejects_sizes_beyond_its_table():
     from d2dmoe_b200 import _capi
     lib = _capi.lib
     one = C.c_void_p(16)      # never dereferenced: the size check comes first
-    # ceil(N/1024) * E = 1025 * 64 > 65536
+    # ceil(N/128) * E = 8200 * 64 > 262144
     assert lib.d2d_compact_noalloc(one, one, one, 1025 * 1024, 64, None, None) == 8
     assert b"scratch" in lib.d2d_strerror(8)
     assert lib.d2d_compact_noalloc(None, one, one, 10, 4, None, None) == 1
