@@ -407,6 +407,59 @@ class MoeficationMoE(MoELayer):
                             add_residual=self.add_residual_connection, accumulate=False)
         return out.view(orig_size), {self.name: (rt,)}
 
+    @torch.no_grad()
+    def forward_host(self, x_host: torch.Tensor, out_host: torch.Tensor | None = None,
+                     chunks: int = 4) -> torch.Tensor:
+        """``forward`` for host-resident activations: x_host [B,S,d] (pinned) -> out_host
+        (pinned), pipelined over ``chunks`` slices of the batch so that the host-to-device
+        copy of slice i+1, the kernels of slice i and the device-to-host copy of slice i-1
+        overlap (three streams, ordered by events).  Tokens are independent, so slicing the
+        batch does not change any result.  Returns out_host; synchronises before returning.
+        """
+        if x_host.is_cuda:
+            raise ValueError("forward_host takes a host tensor; use forward() for device tensors")
+        dev = self.experts.kernel_params()["w1"].device
+        B = x_host.shape[0]
+        if out_host is None:
+            out_host = torch.empty_like(x_host).pin_memory()
+        chunks = max(1, min(chunks, B))
+        st = getattr(self, "_host_streams", None)
+        if st is None or st[0].device != dev:
+            st = tuple(torch.cuda.Stream(device=dev) for _ in range(3))
+            self._host_streams = st
+        s_in, s_run, s_out = st
+        cur = torch.cuda.current_stream(dev)
+        for s_ in st:
+            s_.wait_stream(cur)
+        bounds = [(B * i // chunks, B * (i + 1) // chunks) for i in range(chunks)]
+        bufs = getattr(self, "_host_bufs", None)
+        rows = max(hi - lo for lo, hi in bounds)
+        shape = (rows,) + tuple(x_host.shape[1:])
+        if bufs is None or bufs[0].shape != shape or bufs[0].dtype != x_host.dtype:
+            bufs = [torch.empty(shape, dtype=x_host.dtype, device=dev) for _ in range(2)]
+            self._host_bufs = bufs
+        done_run = [None, None]
+        for i, (lo, hi) in enumerate(bounds):
+            xb = bufs[i & 1][: hi - lo]
+            with torch.cuda.stream(s_in):
+                if done_run[i & 1] is not None:
+                    s_in.wait_event(done_run[i & 1])       # buffer still read by slice i-2
+                xb.copy_(x_host[lo:hi], non_blocking=True)
+                ev_in = s_in.record_event()
+            with torch.cuda.stream(s_run):
+                s_run.wait_event(ev_in)
+                out, _ = self.forward(xb)
+                ev_run = s_run.record_event()
+                done_run[i & 1] = ev_run
+            with torch.cuda.stream(s_out):
+                s_out.wait_event(ev_run)
+                out_host[lo:hi].copy_(out, non_blocking=True)
+                out.record_stream(s_out)
+        for s_ in st:
+            cur.wait_stream(s_)
+        cur.synchronize()
+        return out_host
+
     def last_workspace(self, n: int, device) -> ops.Workspace:
         """The cached buffers of the last call with ``n`` tokens: bit mask, token lists,
         offsets and the device status word (for tests and diagnostics)."""
