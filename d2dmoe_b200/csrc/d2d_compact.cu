@@ -8,7 +8,7 @@
 // Two launches:
 //   count   : counts[tile][e] = tokens of the 128-token tile that keep expert e
 //             (skipped when the router kernel already wrote the table)
-//   scatter : one CTA per 1024 tokens rebuilds its base from the counts table (sum over
+//   scatter : one CTA per 256 tokens rebuilds its base from the counts table (sum over
 //             earlier tiles + exclusive scan over experts) and writes its token indices.
 // Integer work, bit-exact by construction; HBM traffic is the mask (read twice)
 // plus 4 bytes per kept token-expert pair.
@@ -18,7 +18,7 @@ namespace d2d {
 namespace {
 
 constexpr int NT = 256;
-constexpr int ROWS = 32;                 // 32 rows of 32 tokens per scatter CTA
+constexpr int ROWS = 8;                  // rows of 32 tokens per scatter CTA (one per warp)
 constexpr int CHUNK = ROWS * 32;
 constexpr int CTILE = 128;               // granularity of the counts table
 constexpr int TILES_PER_CHUNK = CHUNK / CTILE;
@@ -87,8 +87,8 @@ compact_scatter_kernel(const uint32_t* __restrict__ mask_bits, const int32_t* __
     }
   }
   // per-row popcounts of this chunk
-  for (int r = 0; r < 4; ++r) {
-    const int row = 4 * w + r;
+  for (int r = 0; r < ROWS / 8; ++r) {
+    const int row = (ROWS / 8) * w + r;
     const int64_t t = (int64_t)chunk * CHUNK + row * 32 + lane;
     for (int j = 0; j < nw; ++j) {
       const uint32_t word = t < N ? mask_bits[t * nw + j] : 0u;
@@ -136,8 +136,8 @@ compact_scatter_kernel(const uint32_t* __restrict__ mask_bits, const int32_t* __
     }
   }
   __syncthreads();
-  for (int r = 0; r < 4; ++r) {
-    const int row = 4 * w + r;
+  for (int r = 0; r < ROWS / 8; ++r) {
+    const int row = (ROWS / 8) * w + r;
     const int64_t t = (int64_t)chunk * CHUNK + row * 32 + lane;
     for (int j = 0; j < nw; ++j) {
       const uint32_t word = t < N ? mask_bits[t * nw + j] : 0u;

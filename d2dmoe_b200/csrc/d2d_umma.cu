@@ -10,18 +10,29 @@
 //             (architectures/moe/moefication.py:328-330 and :80-85), written as mask
 //             bits; the same CTA writes the layer output's initial value.
 //
-// Both are one persistent kernel: GEMM1 (K = d) into TMEM, an epilogue that turns
-// the accumulator into the bf16 A operand of GEMM2 in shared memory, GEMM2 (K = hidden
-// width) into a double-buffered TMEM accumulator, and a second epilogue.
+// Both are one persistent kernel (one CTA of 480 threads per SM, tile = 128 rows):
+// GEMM1 (K = d) into a double-buffered TMEM accumulator, an epilogue that turns it into
+// the bf16 A operand of GEMM2 in shared memory, GEMM2 (K = hidden width) per 128-column
+// chunk into a second double-buffered TMEM accumulator, and a second epilogue.
 //
-// Warp roles (320 threads, one CTA per SM):
-//   warps 0-3  epilogues (warp w reads TMEM lanes 32w..32w+31 = tile rows)
-//   warp  4    TMEM allocation; lane 0 issues every tcgen05.mma / tcgen05.commit
-//   warp  5    lane 0 streams weight tiles with cp.async.bulk (TMA, 1-D) into ring B
-//   warps 6-9  gather token rows of x with 16-byte cp.async into ring A, writing the
-//              128-byte-swizzled K-major layout the MMA descriptors expect
+// Warp roles:
+//   warps 0-7   epilogues, two groups of four (warp w reads TMEM lanes 32*(w%4)..+31 =
+//               tile rows).  Group g takes every other 16-column block of epilogue 1 and
+//               the GEMM2 chunks that land in accumulator buffer g.  Experts: bf16 rows
+//               are staged per warp in shared memory and added to out[token] with
+//               row-contiguous red.global.add.noftz.v4.bf16x2 (4 cache lines per
+//               instruction).  Router: |.|, row max, threshold, mask word, per-tile
+//               expert counts for the compaction, and the layer output's initial value.
+//   warp  8     TMEM allocation; GEMM1 stream: waits (lanes poll the A and W1 stage
+//               barriers in parallel), one elected lane issues tcgen05.mma / commit
+//   warp  9     GEMM2 stream, same scheme, on its own weight ring
+//   warp 10     streams packed weight tiles with cp.async.bulk (TMA, 1-D) into the two
+//               weight rings, whichever has a free stage
+//   warps 11-14 gather token rows of x with 16-byte cp.async into ring A in the
+//               128-byte-swizzled K-major layout the MMA descriptors expect; stage
+//               barriers are signalled by cp.async.mbarrier.arrive
 // Weights are packed once (d2d_prepack_*) into exactly the shared-memory images the
-// MMA reads, so a weight tile is one contiguous bulk copy.
+// MMA reads, so a weight tile is one contiguous bulk copy.  No multicast loads.
 //
 // Every wait is bounded: when one runs out the kernel records D2D_ERR_TIMEOUT in the
 // status word, all roles leave their loops, TMEM is freed and the kernel returns.
@@ -319,8 +330,11 @@ struct Ctl {
   uint32_t tmem_base;
   int abort_flag;
   int total_tiles;
-  int tile_cnt[MAX_E];
-  int tstart[MAX_E + 1];
+  alignas(16) float bias_s[2][128];   // (read as float4) b1 of the current tile's expert, one copy per epilogue group
+  union {
+    int tstart[MAX_E + 1];  // experts: first tile of each expert
+    int tile_cnt[MAX_E];    // router: per-expert counts of the current tile
+  };
 };
 
 struct Tile {
@@ -665,14 +679,20 @@ __device__ void role_epilogue(const Params& p, Ctl* c, uint32_t hs, uint32_t stg
       }
     }
     // ---- epilogue 1: acc1 -> bf16 hidden tile in shared memory ------------------
+    if (MODE == MODE_EXPERTS) {
+      // stage this expert's bias in shared memory while GEMM1 is still running
+      const float* bias =
+          reinterpret_cast<const float*>(p.packed + (long long)t.e * g.stride + g.bias_off);
+      if (r < g.nsubw) c->bias_s[grp][r] = __ldg(bias + r);
+      if (grp == 0) asm volatile("bar.sync 2, 128;" ::: "memory");
+      else asm volatile("bar.sync 3, 128;" ::: "memory");
+    }
     const uint32_t b1 = la ? (i & 1) : 0;
     const uint32_t acc1 = tmem + lane_base + (la ? b1 * 128 : 0);
     if (!mbar_wait(smem_u32(&c->acc1_full[b1]), la ? ((i >> 1) & 1) : (i & 1), af, p.dev_status))
       return;
     if (!mbar_wait_fast(smem_u32(&c->hs_empty), (i & 1) ^ 1, af, p.dev_status)) return;
     tc_fence_after();
-    const float* bias =
-        reinterpret_cast<const float*>(p.packed + (long long)t.e * g.stride + g.bias_off);
     const int nblk = g.nsubw >> 4;
     const int nsub1 = (MODE == MODE_ROUTER) ? g.nsub : 1;
     for (int bi = grp; bi < nsub1 * nblk; bi += 2) {
@@ -685,7 +705,7 @@ __device__ void role_epilogue(const Params& p, Ctl* c, uint32_t hs, uint32_t stg
 #pragma unroll
         for (int q = 0; q < 4; ++q)
           *reinterpret_cast<float4*>(&bv[4 * q]) =
-              __ldg(reinterpret_cast<const float4*>(bias + c0) + q);
+              *(reinterpret_cast<const float4*>(&c->bias_s[grp][c0]) + q);
       }
       tmem_wait_ld();
       if (MODE == MODE_ROUTER) {
@@ -974,6 +994,9 @@ int sm_count() {
   }
   return n;
 }
+
+static_assert(1024 + (size_t)SLOTS_TOTAL * SLOT + sizeof(Ctl) + 64 <= 232448,
+              "shared-memory plan exceeds the 227 KB a CTA may use");
 
 size_t smem_bytes(const Geo& g) {
   return 1024 + (size_t)(g.na + g.nb + g.nb2 + g.kc2 + g.stg) * SLOT + sizeof(Ctl) + 64;
