@@ -118,10 +118,10 @@ Geo router_geo(int d, int R, int E) {
   g.kc2 = (R + 63) / 64;
   g.nd = (E + 15) / 16 * 16;
   g.nc = 1;
-  g.stg = 0;
-  g.na = g.kc2 > 2 ? 4 : NA_MAX;
+  g.stg = 1;                       // one slot holds the last_bias row for the TMA row stores
+  g.na = g.kc2 > 2 ? 4 : 5;
   g.nb = 4;
-  g.nb2 = min(NB_MAX, SLOTS_TOTAL - g.na - g.nb - g.kc2);
+  g.nb2 = min(NB_MAX, SLOTS_TOTAL - g.na - g.nb - g.kc2 - g.stg);
   g.w1_bytes = (long long)g.kc1 * g.nsub * g.nsubw * 128;
   g.bias_off = g.w1_bytes + (long long)g.nc * g.kc2 * g.nd * 128;
   g.stride = (g.bias_off + 512 + 1023) / 1024 * 1024;
@@ -279,6 +279,18 @@ __device__ __forceinline__ uint4 ld_shared_v4(uint32_t addr) {
                : "r"(addr)
                : "memory");
   return r;
+}
+// TMA store of one contiguous run from shared to global memory (bulk group completion)
+__device__ __forceinline__ void bulk_s2g(void* gdst, uint32_t ssrc, uint32_t bytes) {
+  asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;" ::"l"(gdst),
+               "r"(ssrc), "r"(bytes)
+               : "memory");
+}
+__device__ __forceinline__ void bulk_commit() {
+  asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+}
+__device__ __forceinline__ void bulk_wait_all() {
+  asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
 }
 __device__ __forceinline__ void tmem_wait_ld() {
   asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
@@ -649,9 +661,29 @@ __device__ void role_epilogue(const Params& p, Ctl* c, uint32_t hs, uint32_t stg
   const uint32_t hs_row = hs + (r >> 3) * 1024 + (r & 7) * 128;
   const bool la = lookahead(g);
   uint32_t i = 0, ph_mine = 0;
+  // Router without residual: every token's initial output is the same row (last_bias or
+  // zeros).  Keep that row in shared memory and let the TMA engine write it once per
+  // token, instead of spending the epilogue warps' store bandwidth on it.
+  const bool tma_init = MODE == MODE_ROUTER && p.out_init && !p.add_residual &&
+                        p.d * 2 <= SLOT;
+  if (tma_init) {
+    for (int c8 = et; c8 < (p.d >> 3); c8 += 256) {
+      uint4 bz = make_uint4(0u, 0u, 0u, 0u);
+      if (p.last_bias) bz = __ldg(reinterpret_cast<const uint4*>(p.last_bias) + c8);
+      st_shared_v4(stg + c8 * 16, bz.x, bz.y, bz.z, bz.w);
+    }
+    fence_proxy_async();
+    asm volatile("bar.sync 4, 256;" ::: "memory");
+  }
   for (int tile = blockIdx.x; tile < c->total_tiles; tile += gridDim.x, ++i) {
     const Tile t = tile_info<MODE>(p, c, tile);
-    if (MODE == MODE_ROUTER && p.out_init) {
+    if (tma_init) {
+      if (w8 == 7) {
+        for (int row = lane; row < t.nrows; row += 32)
+          bulk_s2g(p.out_init + ((long long)t.r0 + row) * p.d, stg, (uint32_t)p.d * 2);
+        bulk_commit();
+      }
+    } else if (MODE == MODE_ROUTER && p.out_init) {
       // initial value of the layer output for this tile's tokens: last_bias (+ x).
       // Lane = one 16-byte column piece (kept in a register), rows of this warp inside.
       const int v8 = p.d >> 3;
@@ -899,6 +931,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) mlp_tiles_kernel(const Params p) 
 
   if (warp < 8) {
     role_epilogue<MODE>(p, c, hs, stg, tmem, tid);
+    bulk_wait_all();       // TMA row stores read shared memory: finish before the CTA ends
   } else if (warp == WARP_MMA1) {
     role_mma1<MODE>(p, c, ringA, ringB, tmem);
   } else if (warp == WARP_MMA2) {
