@@ -179,6 +179,30 @@ init_out_kernel(const T* __restrict__ x, const T* __restrict__ last_bias, int ad
   }
 }
 
+// 16 bytes per thread: V = 16 / sizeof(T) columns of one row (d % V == 0, 16-byte aligned)
+template <typename T>
+__global__ void __launch_bounds__(NT)
+init_out_vec_kernel(const T* __restrict__ x, const T* __restrict__ last_bias, int add_residual,
+                    T* __restrict__ out, int64_t total_vec, int dv) {
+  constexpr int V = 16 / sizeof(T);
+  for (int64_t i = (int64_t)blockIdx.x * NT + threadIdx.x; i < total_vec;
+       i += (int64_t)gridDim.x * NT) {
+    const int cv = (int)(i % dv);
+    uint4 o = make_uint4(0u, 0u, 0u, 0u);
+    if (last_bias) o = __ldg(reinterpret_cast<const uint4*>(last_bias) + cv);
+    if (add_residual) {
+      const uint4 xv = __ldg(reinterpret_cast<const uint4*>(x) + i);
+      const T* a = reinterpret_cast<const T*>(&o);
+      const T* b = reinterpret_cast<const T*>(&xv);
+      T r[V];
+#pragma unroll
+      for (int q = 0; q < V; ++q) r[q] = DT<T>::from_f(DT<T>::to_f(a[q]) + DT<T>::to_f(b[q]));
+      o = *reinterpret_cast<const uint4*>(r);
+    }
+    *(reinterpret_cast<uint4*>(out) + i) = o;
+  }
+}
+
 template <typename T>
 __global__ void __launch_bounds__(NT)
 expand_mask_kernel(const uint32_t* __restrict__ mask_bits, T* __restrict__ rt, int64_t total, int E) {
@@ -260,6 +284,18 @@ int launch_mask_from_scores(const void* scores, float mult, uint32_t* mask_bits,
 int launch_init_out(const void* x, const void* last_bias, int add_residual, void* out, int64_t N,
                     int d, int dtype, cudaStream_t s) {
   const int64_t total = N * d;
+  const int V = dtype == D2D_F32 ? 4 : 8;
+  auto al16 = [](const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; };
+  if (d % V == 0 && al16(out) && al16(x) && al16(last_bias)) {
+    const int grid = grid_for(total / V, NT * 4, 148 * 16);
+    if (dtype == D2D_F32)
+      init_out_vec_kernel<float><<<grid, NT, 0, s>>>((const float*)x, (const float*)last_bias,
+                                                     add_residual, (float*)out, total / V, d / V);
+    else
+      init_out_vec_kernel<bf16><<<grid, NT, 0, s>>>((const bf16*)x, (const bf16*)last_bias,
+                                                    add_residual, (bf16*)out, total / V, d / V);
+    return cudaGetLastError() == cudaSuccess ? D2D_OK : D2D_ERR_LAUNCH;
+  }
   const int grid = grid_for(total, NT * 8, 148 * 8);
   if (dtype == D2D_F32)
     init_out_kernel<float><<<grid, NT, 0, s>>>((const float*)x, (const float*)last_bias,

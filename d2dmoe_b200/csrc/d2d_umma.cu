@@ -769,6 +769,14 @@ __device__ void role_epilogue(const Params& p, Ctl* c, uint32_t hs, uint32_t stg
         if (tok < 0 || tok >= p.N) tok = -1;     // reported by the producer
       }
       const int rl = lane >> 3, pl = lane & 7;
+      // In the read-back, this lane serves rows it*4 + rl (it = 0..7) of the warp: fetch
+      // their output row pointers once per tile (null = row past the tail).
+      bf16* orow[8];
+#pragma unroll
+      for (int it = 0; it < 8; ++it) {
+        const long long tk = __shfl_sync(0xffffffffu, tok, it * 4 + rl);
+        orow[it] = tk < 0 ? nullptr : p.out + tk * p.d + pl * 8;
+      }
       for (int nci = grp; nci < g.nc; nci += 2) {
         if (!mbar_wait_fast(smem_u32(&c->acc2_full[grp]), ph_mine, af, p.dev_status)) return;
         ph_mine ^= 1;
@@ -796,15 +804,18 @@ __device__ void role_epilogue(const Params& p, Ctl* c, uint32_t hs, uint32_t stg
           __syncwarp();
           // read back row-contiguous: 8 lanes cover one row's 128 bytes, so one red
           // instruction touches 4 rows (4 cache lines) instead of 32
-          bf16* ocol = p.out + nci * g.nd + hf * 64 + pl * 8;
+          const int col = nci * g.nd + hf * 64;
+          uint4 val[8];
 #pragma unroll
-          for (int it = 0; it < 8; ++it) {
+          for (int it = 0; it < 8; ++it) {      // all shared loads first, then all reds
             const int rr = it * 4 + rl;
-            const uint4 val = ld_shared_v4(stg_w + rr * 128 + ((pl ^ (rr & 7)) << 4));
-            const long long tk = __shfl_sync(0xffffffffu, tok, rr);
-            if (tk >= 0) red_add_bf16x8(ocol + tk * p.d, val.x, val.y, val.z, val.w);
+            val[it] = ld_shared_v4(stg_w + rr * 128 + ((pl ^ (rr & 7)) << 4));
           }
-          __syncwarp();
+          __syncwarp();                         // staging may be overwritten from here on
+#pragma unroll
+          for (int it = 0; it < 8; ++it)
+            if (orow[it])
+              red_add_bf16x8(orow[it] + col, val[it].x, val[it].y, val[it].z, val[it].w);
         }
       }
     } else if (grp == 0) {
