@@ -37,6 +37,10 @@ sys.path.insert(0, str(ROOT))
 TAUS = [0.5, 0.7, 0.8, 0.9, 0.95, 1.0]
 HEADLINE_TAU = 0.9
 LAYERS, BATCH, SEQ, D, H, E, R = 12, 256, 197, 768, 128, 24, 128
+# dram__bytes_read.sum + dram__bytes_write.sum of one expert-kernel launch of this workload at
+# tau_cfg 0.9 (173.0 + 31.6 MB), from the ncu capture summarised in
+# profiles/mlp_tiles_kernels_vit_b16_tau0.9.md
+NCU_EXPERTS_TRAFFIC_BYTES = 204.65e6
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
 
 
@@ -351,7 +355,9 @@ def run_ours(args):
         roof = {"bound": "hbm", "achieved": ffn_bytes / ffn_s / 1e9, "peak": pk["hbm_gbs"],
                 "unit": "GB/s"}
     roof["frac"] = roof["achieved"] / roof["peak"]
-    roof.update({"kernel": "experts_ffn", "traffic": None, "peak_source": pk["source"],
+    roof.update({"kernel": "experts_ffn (mlp_tiles_kernel<EXPERTS>)",
+                 "traffic": NCU_EXPERTS_TRAFFIC_BYTES
+                 if (LAYERS == 12 and HEADLINE_TAU == 0.9 and BATCH == 256) else None, "peak_source": pk["source"],
                  "avg_launch_us": ffn_s * 1e6, "launches_timed": launches,
                  "algorithmic_bytes_per_launch": ffn_bytes, "algorithmic_flops_per_launch": fl,
                  "stage_us_per_layer": {"router_mask": stage_ms[0] * 1e3 / launches,

@@ -77,8 +77,20 @@ compact_scatter_kernel(const uint32_t* __restrict__ mask_bits, const int32_t* __
     const int e = tid % E, grp = tid / E;
     if (grp < groups) {
       int a = 0, b = 0;
-      for (int t = grp; t < ntiles; t += groups) {
-        const int v = counts[(int64_t)t * E + e];
+      int t = grp;
+      // eight independent loads in flight per thread (the loop is latency-bound otherwise)
+      for (; t + 7 * groups < ntiles; t += 8 * groups) {
+        int v[8];
+#pragma unroll
+        for (int u = 0; u < 8; ++u) v[u] = __ldg(counts + (int64_t)(t + u * groups) * E + e);
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
+          a += v[u];
+          if (t + u * groups < first_tile) b += v[u];
+        }
+      }
+      for (; t < ntiles; t += groups) {
+        const int v = __ldg(counts + (int64_t)t * E + e);
         a += v;
         if (t < first_tile) b += v;
       }
