@@ -18,6 +18,7 @@ namespace d2d {
 namespace {
 
 constexpr int NT = 256;
+constexpr int NTS = 1024;                // scatter CTA: 8 warps do the rows, all 32 sweep the table
 constexpr int ROWS = 8;                  // rows of 32 tokens per scatter CTA (one per warp)
 constexpr int CHUNK = ROWS * 32;
 constexpr int CTILE = 128;               // granularity of the counts table
@@ -51,7 +52,7 @@ compact_count_kernel(const uint32_t* __restrict__ mask_bits, int32_t* __restrict
   }
 }
 
-__global__ void __launch_bounds__(NT)
+__global__ void __launch_bounds__(NTS)
 compact_scatter_kernel(const uint32_t* __restrict__ mask_bits, const int32_t* __restrict__ counts,
                        int32_t* __restrict__ token_idx, int32_t* __restrict__ offsets, int64_t N,
                        int E, int ntiles, int* dev_status) {
@@ -63,8 +64,8 @@ compact_scatter_kernel(const uint32_t* __restrict__ mask_bits, const int32_t* __
   const int nw = (E + 31) / 32;
   const int chunk = blockIdx.x;
 
-  for (int i = tid; i < ROWS * E; i += NT) cnt[i] = 0;
-  for (int e = tid; e < E; e += NT) {
+  for (int i = tid; i < ROWS * E; i += NTS) cnt[i] = 0;
+  for (int e = tid; e < E; e += NTS) {
     tot[e] = 0;
     pre[e] = 0;
   }
@@ -72,7 +73,7 @@ compact_scatter_kernel(const uint32_t* __restrict__ mask_bits, const int32_t* __
   // column sums of the counts table: thread (grp, e) adds up tiles grp, grp+groups, ...
   // in registers (coalesced over e), then one shared atomic per thread
   {
-    const int groups = max(1, NT / E);
+    const int groups = max(1, NTS / E);
     const int first_tile = chunk * TILES_PER_CHUNK;
     const int e = tid % E, grp = tid / E;
     if (grp < groups) {
@@ -99,8 +100,8 @@ compact_scatter_kernel(const uint32_t* __restrict__ mask_bits, const int32_t* __
     }
   }
   // per-row popcounts of this chunk
-  for (int r = 0; r < ROWS / 8; ++r) {
-    const int row = (ROWS / 8) * w + r;
+  if (w < ROWS) {                    // warps 0..ROWS-1 own one row of 32 tokens each
+    const int row = w;
     const int64_t t = (int64_t)chunk * CHUNK + row * 32 + lane;
     for (int j = 0; j < nw; ++j) {
       const uint32_t word = t < N ? mask_bits[t * nw + j] : 0u;
@@ -138,7 +139,7 @@ compact_scatter_kernel(const uint32_t* __restrict__ mask_bits, const int32_t* __
     }
   }
   __syncthreads();
-  for (int e = tid; e < E; e += NT) {
+  for (int e = tid; e < E; e += NTS) {
     if (chunk == 0) offsets[e] = tot[e];
     int run = tot[e] + pre[e];
     for (int row = 0; row < ROWS; ++row) {
@@ -148,8 +149,8 @@ compact_scatter_kernel(const uint32_t* __restrict__ mask_bits, const int32_t* __
     }
   }
   __syncthreads();
-  for (int r = 0; r < ROWS / 8; ++r) {
-    const int row = (ROWS / 8) * w + r;
+  if (w < ROWS) {                    // warps 0..ROWS-1 own one row of 32 tokens each
+    const int row = w;
     const int64_t t = (int64_t)chunk * CHUNK + row * 32 + lane;
     for (int j = 0; j < nw; ++j) {
       const uint32_t word = t < N ? mask_bits[t * nw + j] : 0u;
@@ -192,7 +193,7 @@ int launch_compact(const uint32_t* mask_bits, int32_t* token_idx, int32_t* offse
                              (int)smem) != cudaSuccess)
       return D2D_ERR_LAUNCH;
   }
-  compact_scatter_kernel<<<(unsigned)nchunks, NT, smem, s>>>(mask_bits, counts_ws, token_idx,
+  compact_scatter_kernel<<<(unsigned)nchunks, NTS, smem, s>>>(mask_bits, counts_ws, token_idx,
                                                              offsets, N, E, (int)ntiles,
                                                              dev_status);
   return cudaGetLastError() == cudaSuccess ? D2D_OK : D2D_ERR_LAUNCH;

@@ -918,21 +918,42 @@ __global__ void __launch_bounds__(NTHREADS, 1) mlp_tiles_kernel(const Params p) 
       mbar_init(smem_u32(&c->acc2_empty[i]), 128);
     }
     c->abort_flag = 0;
-    if (MODE == MODE_ROUTER) {
-      c->total_tiles = (int)((p.N + TILE_M - 1) / TILE_M);
-    } else {
-      int run = 0;
-      for (int e = 0; e < p.E; ++e) {
-        c->tstart[e] = run;
-        const int n = p.offsets[e + 1] - p.offsets[e];
-        if (n < 0 || p.offsets[e + 1] > p.N * (long long)p.E) report(p.dev_status, D2D_ERR_INDEX_RANGE);
-        run += n > 0 ? (n + TILE_M - 1) / TILE_M : 0;
-      }
-      c->tstart[p.E] = run;
-      c->total_tiles = run;
-    }
+    if (MODE == MODE_ROUTER) c->total_tiles = (int)((p.N + TILE_M - 1) / TILE_M);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     fence_proxy_async();
+  }
+  if (MODE == MODE_EXPERTS && warp == 1) {
+    // first tile of every expert: all offsets loaded in parallel (lane l owns experts
+    // 4l..4l+3), exclusive scan of the per-expert tile counts across the warp
+    const int lane = tid & 31;
+    int off[5], nt[4], sum = 0;
+#pragma unroll
+    for (int q = 0; q < 5; ++q) {
+      const int e = 4 * lane + q;
+      off[q] = e <= p.E ? p.offsets[e] : 0;
+    }
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+      const int e = 4 * lane + q;
+      const int n = e < p.E ? off[q + 1] - off[q] : 0;
+      if (e < p.E && (n < 0 || off[q + 1] > p.N * (long long)p.E))
+        report(p.dev_status, D2D_ERR_INDEX_RANGE);
+      nt[q] = n > 0 ? (n + TILE_M - 1) / TILE_M : 0;
+      sum += nt[q];
+    }
+    int incl = sum;
+    for (int o = 1; o < 32; o <<= 1) {
+      const int v = __shfl_up_sync(0xffffffffu, incl, o);
+      if (lane >= o) incl += v;
+    }
+    int run = incl - sum;
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+      const int e = 4 * lane + q;
+      if (e <= p.E) c->tstart[e] = run;
+      run += nt[q];
+    }
+    if (lane == 31) c->total_tiles = incl;
   }
   if (warp == WARP_MMA1) tmem_alloc(smem_u32(&c->tmem_base), 512);
   tc_fence_before();
