@@ -237,6 +237,10 @@ MOE_IMPL_MAP = {
 }
 
 
+# per device: (host-to-device, compute, device-to-host) streams shared by all layers
+_HOST_STREAMS: dict = {}
+
+
 class MoELayer(nn.Module):
     def __init__(self, name, num_experts):
         super().__init__()
@@ -409,12 +413,17 @@ class MoeficationMoE(MoELayer):
 
     @torch.no_grad()
     def forward_host(self, x_host: torch.Tensor, out_host: torch.Tensor | None = None,
-                     chunks: int = 4) -> torch.Tensor:
+                     chunks: int = 4, sync: bool = True) -> torch.Tensor:
         """``forward`` for host-resident activations: x_host [B,S,d] (pinned) -> out_host
         (pinned), pipelined over ``chunks`` slices of the batch so that the host-to-device
         copy of slice i+1, the kernels of slice i and the device-to-host copy of slice i-1
         overlap (three streams, ordered by events).  Tokens are independent, so slicing the
-        batch does not change any result.  Returns out_host; synchronises before returning.
+        batch does not change any result.  Returns out_host.
+
+        All layers of a device share the three streams, so with ``sync=False`` consecutive
+        calls (other layers, the next batch) queue behind each other without draining the
+        pipeline; ``out_host`` is then complete only after ``MoeficationMoE.host_synchronize``.
+        With ``sync=True`` (default) the call returns when ``out_host`` is complete.
         """
         if x_host.is_cuda:
             raise ValueError("forward_host takes a host tensor; use forward() for device tensors")
@@ -423,14 +432,15 @@ class MoeficationMoE(MoELayer):
         if out_host is None:
             out_host = torch.empty_like(x_host).pin_memory()
         chunks = max(1, min(chunks, B))
-        st = getattr(self, "_host_streams", None)
-        if st is None or st[0].device != dev:
+        st = _HOST_STREAMS.get(dev)
+        if st is None:
             st = tuple(torch.cuda.Stream(device=dev) for _ in range(3))
-            self._host_streams = st
+            _HOST_STREAMS[dev] = st
         s_in, s_run, s_out = st
         cur = torch.cuda.current_stream(dev)
-        for s_ in st:
-            s_.wait_stream(cur)
+        if sync:
+            for s_ in st:
+                s_.wait_stream(cur)
         bounds = [(B * i // chunks, B * (i + 1) // chunks) for i in range(chunks)]
         bufs = getattr(self, "_host_bufs", None)
         rows = max(hi - lo for lo, hi in bounds)
@@ -438,7 +448,8 @@ class MoeficationMoE(MoELayer):
         if bufs is None or bufs[0].shape != shape or bufs[0].dtype != x_host.dtype:
             bufs = [torch.empty(shape, dtype=x_host.dtype, device=dev) for _ in range(2)]
             self._host_bufs = bufs
-        done_run = [None, None]
+            self._host_done = [None, None]
+        done_run = self._host_done        # kernels that last read each buffer (kept across calls)
         for i, (lo, hi) in enumerate(bounds):
             xb = bufs[i & 1][: hi - lo]
             with torch.cuda.stream(s_in):
@@ -455,10 +466,19 @@ class MoeficationMoE(MoELayer):
                 s_out.wait_event(ev_run)
                 out_host[lo:hi].copy_(out, non_blocking=True)
                 out.record_stream(s_out)
-        for s_ in st:
-            cur.wait_stream(s_)
-        cur.synchronize()
+        if sync:
+            for s_ in st:
+                cur.wait_stream(s_)
+            cur.synchronize()
         return out_host
+
+    @staticmethod
+    def host_synchronize(device=None) -> None:
+        """Wait until every ``forward_host(..., sync=False)`` issued on ``device`` is complete."""
+        for dev, st in _HOST_STREAMS.items():
+            if device is None or torch.device(device) == dev:
+                for s_ in st:
+                    s_.synchronize()
 
     def last_workspace(self, n: int, device) -> ops.Workspace:
         """The cached buffers of the last call with ``n`` tokens: bit mask, token lists,

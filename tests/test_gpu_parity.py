@@ -219,3 +219,29 @@ def test_empty_and_error_paths():
     with pytest.raises(_capi.D2DError, match="INDEX_RANGE"):
         wsp.check_status()
     assert torch.equal(out, torch.zeros_like(out))      # nothing was added
+
+
+def test_forward_host_matches_forward():
+    """Host-buffer entry point: pipelined slices give the rule's bits and outputs of forward()."""
+    import d2dmoe_b200 as D
+    c = C.LayerCase("host", 16, 33, 128, 64, 8, tau=0.3, dtype="bf16")
+    t = C.make_tensors(c)
+    moe = D.MoeficationMoE(c.name, c.d, c.E, True, c.H, torch.nn.ReLU)
+    moe.router = D.MoeficationRouter(c.d, c.E, width=c.R, depth=2, bias=False, activation="relu",
+                                     output_activation="abs")
+    moe = moe.to(torch.bfloat16)
+    moe.load_state_dict({"experts.w1": t["w1"], "experts.b1": t["b1"], "experts.w2": t["w2"],
+                         "last_bias": t["last_bias"], "router.layers.0.weight": t["wa"],
+                         "router.layers.2.weight": t["wb"]})
+    moe = moe.cuda()
+    moe.forward_mode, moe.tau = "dynk_max", c.tau
+    ref, _ = moe(t["x"].cuda())
+    xh = t["x"].pin_memory()
+    o1 = moe.forward_host(xh, chunks=3)
+    o2 = torch.empty_like(xh).pin_memory()
+    o3 = torch.empty_like(xh).pin_memory()
+    moe.forward_host(xh, o2, chunks=5, sync=False)
+    moe.forward_host(xh, o3, chunks=2, sync=False)
+    D.MoeficationMoE.host_synchronize()
+    for o in (o1, o2, o3):
+        assert O.rel_err(o.float(), ref.float().cpu()) <= TOL["bf16"]
