@@ -342,9 +342,11 @@ struct Ctl {
   uint32_t tmem_base;
   int abort_flag;
   int total_tiles;
-  alignas(16) float bias_s[2][128];   // (read as float4) b1 of the current tile's expert, one copy per epilogue group
+  alignas(16) float bias_s[128];   // (read as float4) b1 of the current tile's expert
+  int total_full;                  // experts: number of full 128-row tiles (they come first)
+  uint8_t pidx[MAX_E];             // experts: expert of the k-th partial (tail) tile
   union {
-    int tstart[MAX_E + 1];  // experts: first tile of each expert
+    int tstart[MAX_E + 1];  // experts: first FULL tile of each expert
     int tile_cnt[MAX_E];    // router: per-expert counts of the current tile
   };
 };
@@ -361,14 +363,24 @@ __device__ __forceinline__ Tile tile_info(const Params& p, const Ctl* c, int til
     t.r0 = tile * TILE_M;
     t.nrows = (int)min((long long)TILE_M, p.N - (long long)t.r0);
   } else {
-    int lo = 0, hi = p.E;
-    while (hi - lo > 1) {
-      const int mid = (lo + hi) >> 1;
-      if (c->tstart[mid] <= tile) lo = mid; else hi = mid;
+    // Tile order: every full 128-row tile (expert-major), then the experts' partial tail
+    // tiles.  With the static round-robin over CTAs the last, incomplete round of a launch
+    // is then made of the cheap partial tiles.
+    if (tile < c->total_full) {
+      int lo = 0, hi = p.E;
+      while (hi - lo > 1) {
+        const int mid = (lo + hi) >> 1;
+        if (c->tstart[mid] <= tile) lo = mid; else hi = mid;
+      }
+      t.e = lo;
+      t.r0 = p.offsets[lo] + (tile - c->tstart[lo]) * TILE_M;
+      t.nrows = TILE_M;
+    } else {
+      t.e = c->pidx[tile - c->total_full];
+      const int n = p.offsets[t.e + 1] - p.offsets[t.e];
+      t.r0 = p.offsets[t.e] + (n / TILE_M) * TILE_M;
+      t.nrows = n % TILE_M;
     }
-    t.e = lo;
-    t.r0 = p.offsets[lo] + (tile - c->tstart[lo]) * TILE_M;
-    t.nrows = min(TILE_M, p.offsets[lo + 1] - t.r0);
   }
   return t;
 }
@@ -715,9 +727,8 @@ __device__ void role_epilogue(const Params& p, Ctl* c, uint32_t hs, uint32_t stg
       // stage this expert's bias in shared memory while GEMM1 is still running
       const float* bias =
           reinterpret_cast<const float*>(p.packed + (long long)t.e * g.stride + g.bias_off);
-      if (r < g.nsubw) c->bias_s[grp][r] = __ldg(bias + r);
-      if (grp == 0) asm volatile("bar.sync 2, 128;" ::: "memory");
-      else asm volatile("bar.sync 3, 128;" ::: "memory");
+      if (et < g.nsubw) c->bias_s[et] = __ldg(bias + et);
+      asm volatile("bar.sync 2, 256;" ::: "memory");
     }
     const uint32_t b1 = la ? (i & 1) : 0;
     const uint32_t acc1 = tmem + lane_base + (la ? b1 * 128 : 0);
@@ -737,7 +748,7 @@ __device__ void role_epilogue(const Params& p, Ctl* c, uint32_t hs, uint32_t stg
 #pragma unroll
         for (int q = 0; q < 4; ++q)
           *reinterpret_cast<float4*>(&bv[4 * q]) =
-              *(reinterpret_cast<const float4*>(&c->bias_s[grp][c0]) + q);
+              *(reinterpret_cast<const float4*>(&c->bias_s[c0]) + q);
       }
       tmem_wait_ld();
       if (MODE == MODE_ROUTER) {
@@ -923,10 +934,10 @@ __global__ void __launch_bounds__(NTHREADS, 1) mlp_tiles_kernel(const Params p) 
     fence_proxy_async();
   }
   if (MODE == MODE_EXPERTS && warp == 1) {
-    // first tile of every expert: all offsets loaded in parallel (lane l owns experts
-    // 4l..4l+3), exclusive scan of the per-expert tile counts across the warp
+    // tile tables: all offsets loaded in parallel (lane l owns experts 4l..4l+3), exclusive
+    // scans across the warp of the full-tile counts and of the "has a partial tile" flags
     const int lane = tid & 31;
-    int off[5], nt[4], sum = 0;
+    int off[5], nt[4], pt[4], sum = 0, psum = 0;
 #pragma unroll
     for (int q = 0; q < 5; ++q) {
       const int e = 4 * lane + q;
@@ -938,22 +949,33 @@ __global__ void __launch_bounds__(NTHREADS, 1) mlp_tiles_kernel(const Params p) 
       const int n = e < p.E ? off[q + 1] - off[q] : 0;
       if (e < p.E && (n < 0 || off[q + 1] > p.N * (long long)p.E))
         report(p.dev_status, D2D_ERR_INDEX_RANGE);
-      nt[q] = n > 0 ? (n + TILE_M - 1) / TILE_M : 0;
+      nt[q] = n > 0 ? n / TILE_M : 0;
+      pt[q] = (n > 0 && n % TILE_M != 0) ? 1 : 0;
       sum += nt[q];
+      psum += pt[q];
     }
-    int incl = sum;
+    int incl = sum, pincl = psum;
     for (int o = 1; o < 32; o <<= 1) {
       const int v = __shfl_up_sync(0xffffffffu, incl, o);
-      if (lane >= o) incl += v;
+      const int w = __shfl_up_sync(0xffffffffu, pincl, o);
+      if (lane >= o) {
+        incl += v;
+        pincl += w;
+      }
     }
-    int run = incl - sum;
+    int run = incl - sum, prun = pincl - psum;
 #pragma unroll
     for (int q = 0; q < 4; ++q) {
       const int e = 4 * lane + q;
       if (e <= p.E) c->tstart[e] = run;
+      if (pt[q]) c->pidx[prun] = (uint8_t)e;
       run += nt[q];
+      prun += pt[q];
     }
-    if (lane == 31) c->total_tiles = incl;
+    if (lane == 31) {
+      c->total_full = incl;
+      c->total_tiles = incl + pincl;
+    }
   }
   if (warp == WARP_MMA1) tmem_alloc(smem_u32(&c->tmem_base), 512);
   tc_fence_before();
