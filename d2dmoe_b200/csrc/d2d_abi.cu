@@ -115,9 +115,7 @@ int d2d_experts_ffn(const void* x, const int32_t* token_idx, const int32_t* offs
     int rc = launch_init_out(x, last_bias_opt, add_residual, out, N, d, dtype, s);
     if (rc != D2D_OK) return rc;
   }
-  // (the tensor-core kernel keeps per-expert tile counts in 16 bits)
-  if (experts_packed_opt && N <= 65535LL * 128 &&
-      umma_experts_supported(d, E, H, w_up_opt != nullptr, dtype))
+  if (experts_packed_opt && umma_experts_supported(d, E, H, w_up_opt != nullptr, dtype))
     return launch_experts_umma(x, token_idx, offsets, experts_packed_opt, out, N, d, E, H,
                                w_up_opt != nullptr, act, dev_status, s);
   return launch_experts_simt(x, token_idx, offsets, w1, b1_opt, w_up_opt, w2, out, N, d, E, H, act,
