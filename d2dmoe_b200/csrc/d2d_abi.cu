@@ -136,10 +136,20 @@ int d2d_moe_forward(const void* x, const void* wa, const void* wb, const void* r
   if (ws_bytes < compact_workspace_bytes(N, E)) return D2D_ERR_WORKSPACE;
   if (N == 0) return D2D_OK;
   if (scores_in_opt) {
-    rc = d2d_mask_from_scores(scores_in_opt, thresh_mult, mask_bits, N, E, dtype, dev_status,
-                              stream);
-    if (rc != D2D_OK) return rc;
-    rc = d2d_init_out(x, last_bias_opt, add_residual, out, N, d, dtype, stream);
+    // rule + counts table + output init in one launch when the shape allows it
+    rc = (dtype_ok(dtype) && out && d >= 1 && E >= 1 && (!add_residual || x))
+             ? launch_gate_scores_fused(scores_in_opt, thresh_mult, mask_bits, (int32_t*)ws, x,
+                                        last_bias_opt, add_residual, out, N, d, E, dtype,
+                                        (cudaStream_t)stream)
+             : D2D_ERR_UNSUPPORTED;
+    if (rc == D2D_OK) {
+      counts_ready = true;
+    } else if (rc == D2D_ERR_UNSUPPORTED) {
+      rc = d2d_mask_from_scores(scores_in_opt, thresh_mult, mask_bits, N, E, dtype, dev_status,
+                                stream);
+      if (rc != D2D_OK) return rc;
+      rc = d2d_init_out(x, last_bias_opt, add_residual, out, N, d, dtype, stream);
+    }
   } else if (router_packed_opt && x && wb && dtype_ok(dtype) && d >= 1 && R >= 1 && E >= 1 &&
              umma_router_supported(d, R, E, dtype)) {
     // the tensor-core router also fills the compaction's counts table

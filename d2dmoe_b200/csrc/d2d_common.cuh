@@ -88,6 +88,10 @@ int launch_router_mask_simt(const void* x, const void* wa, const void* wb, float
                             int dtype, int* dev_status, cudaStream_t s);
 int launch_mask_from_scores(const void* scores, float mult, uint32_t* mask_bits, int64_t N, int E,
                             int dtype, int* dev_status, cudaStream_t s);
+int launch_gate_scores_fused(const void* scores, float mult, uint32_t* mask_bits,
+                             int32_t* tile_counts, const void* x, const void* last_bias,
+                             int add_residual, void* out, int64_t N, int d, int E, int dtype,
+                             cudaStream_t s);
 int launch_init_out(const void* x, const void* last_bias, int add_residual, void* out, int64_t N,
                     int d, int dtype, cudaStream_t s);
 int launch_expand_mask(const uint32_t* mask_bits, void* rt, int64_t N, int E, int dtype,

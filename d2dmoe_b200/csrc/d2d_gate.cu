@@ -166,6 +166,70 @@ mask_from_scores_kernel(const T* __restrict__ scores, float mult, uint32_t* __re
   }
 }
 
+// The rule on given scores, fused with what the layer needs next: the compaction's counts
+// table (per 128-token tile) and the output's initial value.  One CTA = one 128-token
+// tile; warp w handles tokens 16w..16w+15 (lane = expert), then all threads write the
+// tile's initial output rows with 16-byte stores.  Needs d % (16/sizeof(T)) == 0.
+template <typename T>
+__global__ void __launch_bounds__(NT)
+gate_scores_fused_kernel(const T* __restrict__ scores, float mult,
+                         uint32_t* __restrict__ mask_bits, int32_t* __restrict__ tile_counts,
+                         const T* __restrict__ x, const T* __restrict__ last_bias,
+                         int add_residual, T* __restrict__ out, int64_t N, int d, int E) {
+  __shared__ int cnt[256];
+  constexpr int V = 16 / sizeof(T);
+  const int tid = threadIdx.x, lane = tid & 31, w = tid >> 5;
+  const int nw = (E + 31) / 32;
+  const int64_t t0 = (int64_t)blockIdx.x * 128;
+  for (int e = tid; e < E; e += NT) cnt[e] = 0;
+  __syncthreads();
+  int mine[8] = {0, 0, 0, 0, 0, 0, 0, 0};       // kept-count of expert lane+32j over my tokens
+  for (int i = 0; i < 16; ++i) {
+    const int64_t t = t0 + w * 16 + i;
+    if (t >= N) break;                           // warp-uniform
+    float s[8];
+    for (int j = 0; j < nw; ++j) {
+      const int e = lane + 32 * j;
+      s[j] = e < E ? DT<T>::to_f(scores[t * E + e]) : 0.f;
+    }
+    float m = -INFINITY;
+    for (int j = 0; j < nw; ++j)
+      if (lane + 32 * j < E) m = nanmax(m, s[j]);
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) m = nanmax(m, __shfl_xor_sync(0xffffffffu, m, o));
+    const float thr = DT<T>::round(__fmul_rn(m, mult));
+    for (int j = 0; j < nw; ++j) {
+      const bool keep = (lane + 32 * j < E) && (s[j] >= thr);
+      const uint32_t word = __ballot_sync(0xffffffffu, keep);
+      if (lane == 0) mask_bits[t * nw + j] = word;
+      mine[j] += keep ? 1 : 0;
+    }
+  }
+  for (int j = 0; j < nw; ++j)
+    if (lane + 32 * j < E && mine[j]) atomicAdd(&cnt[lane + 32 * j], mine[j]);
+  __syncthreads();
+  for (int e = tid; e < E; e += NT) tile_counts[(int64_t)blockIdx.x * E + e] = cnt[e];
+  if (out) {
+    const int dv = d / V;
+    const int rows = (int)min((int64_t)128, N - t0);
+    for (int i = tid; i < rows * dv; i += NT) {
+      const int r = i / dv, cv = i - r * dv;
+      uint4 o = make_uint4(0u, 0u, 0u, 0u);
+      if (last_bias) o = __ldg(reinterpret_cast<const uint4*>(last_bias) + cv);
+      if (add_residual) {
+        const uint4 xv = __ldg(reinterpret_cast<const uint4*>(x + (t0 + r) * d) + cv);
+        const T* a = reinterpret_cast<const T*>(&o);
+        const T* b = reinterpret_cast<const T*>(&xv);
+        T rr[V];
+#pragma unroll
+        for (int q = 0; q < V; ++q) rr[q] = DT<T>::from_f(DT<T>::to_f(a[q]) + DT<T>::to_f(b[q]));
+        o = *reinterpret_cast<const uint4*>(rr);
+      }
+      *(reinterpret_cast<uint4*>(out + (t0 + r) * d) + cv) = o;
+    }
+  }
+}
+
 template <typename T>
 __global__ void __launch_bounds__(NT)
 init_out_kernel(const T* __restrict__ x, const T* __restrict__ last_bias, int add_residual,
@@ -278,6 +342,29 @@ int launch_mask_from_scores(const void* scores, float mult, uint32_t* mask_bits,
     mask_from_scores_kernel<float><<<grid, NT, 0, s>>>((const float*)scores, mult, mask_bits, N, E);
   else
     mask_from_scores_kernel<bf16><<<grid, NT, 0, s>>>((const bf16*)scores, mult, mask_bits, N, E);
+  return cudaGetLastError() == cudaSuccess ? D2D_OK : D2D_ERR_LAUNCH;
+}
+
+// returns D2D_ERR_UNSUPPORTED when the shape does not allow the fused form (caller then uses
+// the separate kernels)
+int launch_gate_scores_fused(const void* scores, float mult, uint32_t* mask_bits,
+                             int32_t* tile_counts, const void* x, const void* last_bias,
+                             int add_residual, void* out, int64_t N, int d, int E, int dtype,
+                             cudaStream_t s) {
+  const int V = dtype == D2D_F32 ? 4 : 8;
+  auto al16 = [](const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; };
+  if (E > 256 || d % V != 0 || !al16(out) || !al16(x) || !al16(last_bias))
+    return D2D_ERR_UNSUPPORTED;
+  const int64_t grid = ceil_div64(N, 128);
+  if (grid > 0x7fffffffLL) return D2D_ERR_UNSUPPORTED;
+  if (dtype == D2D_F32)
+    gate_scores_fused_kernel<float><<<(unsigned)grid, NT, 0, s>>>(
+        (const float*)scores, mult, mask_bits, tile_counts, (const float*)x,
+        (const float*)last_bias, add_residual, (float*)out, N, d, E);
+  else
+    gate_scores_fused_kernel<bf16><<<(unsigned)grid, NT, 0, s>>>(
+        (const bf16*)scores, mult, mask_bits, tile_counts, (const bf16*)x,
+        (const bf16*)last_bias, add_residual, (bf16*)out, N, d, E);
   return cudaGetLastError() == cudaSuccess ? D2D_OK : D2D_ERR_LAUNCH;
 }
 
