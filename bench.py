@@ -87,7 +87,7 @@ class ClockSampler:
         try:
             self.p = subprocess.Popen(
                 ["nvidia-smi", f"--id={index}", f"--query-gpu={self.Q}",
-                 "--format=csv,noheader,nounits", "-lms", "100"],
+                 "--format=csv,noheader,nounits", "-lms", "50"],
                 stdout=self.f, stderr=subprocess.DEVNULL)
         except OSError:
             pass
@@ -349,9 +349,6 @@ def run_ours(args):
                       "ms_per_step": per_step * 1e3, "roofline_ms_per_step": t_roof * 1e3,
                       "roofline_frac": t_roof / per_step})
 
-    # the sampler covered the headline region and the sweep: same kernels, all timed work
-    clocks = sampler.stop() if sampler else None
-
     # ---- per-kernel durations at the headline tau (CUDA events between stages) ----
     tau_mod = 1.0 - HEADLINE_TAU
     evs = [[torch.cuda.Event(enable_timing=True) for _ in range(4)] for _ in layers]
@@ -390,6 +387,9 @@ def run_ours(args):
                  "stage_us_per_layer": {"router_mask": stage_ms[0] * 1e3 / launches,
                                         "compact": stage_ms[1] * 1e3 / launches,
                                         "experts_ffn": stage_ms[2] * 1e3 / launches}})
+    # the sampler covered the headline region, the sweep and the stage timing: the same
+    # kernels on the same buffers, all of it timed device work
+    clocks = sampler.stop() if sampler else None
     head = next(s for s in sweep if s["tau_cfg"] == HEADLINE_TAU)
 
     # ---- e2e: module API, host buffers ------------------------------------------
@@ -452,7 +452,7 @@ def main():
     global LAYERS, HEADLINE_TAU
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--steps", type=int, default=100)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
