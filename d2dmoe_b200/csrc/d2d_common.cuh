@@ -27,6 +27,17 @@ template <> struct DT<bf16> {
   }
 };
 
+// four consecutive elements as floats (16-byte load for float, 8-byte for bf16)
+__device__ __forceinline__ float4 load4(const float* p) {
+  return __ldg(reinterpret_cast<const float4*>(p));
+}
+__device__ __forceinline__ float4 load4(const bf16* p) {
+  const uint2 u = __ldg(reinterpret_cast<const uint2*>(p));
+  const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&u.x));
+  const float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&u.y));
+  return make_float4(a.x, a.y, b.x, b.y);
+}
+
 // ---- device status word ---------------------------------------------------
 // First error wins; kernels return early after reporting, they never trap.
 __device__ __forceinline__ void report(int* dev_status, int code) {

@@ -51,6 +51,11 @@ experts_simt_kernel(const T* __restrict__ x, const int32_t* __restrict__ token_i
   __syncthreads();
   const int total = tstart[E];
   const bool vec_ok = (d % 4 == 0);
+  // vector staging of x rows and weight rows: 4-element boundaries everywhere
+  const bool vec = (d % 4 == 0) && (H % 4 == 0) &&
+                   ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(w1) |
+                     reinterpret_cast<uintptr_t>(w2) | reinterpret_cast<uintptr_t>(w_up)) % 16 == 0);
+  const float4 z4 = make_float4(0.f, 0.f, 0.f, 0.f);
 
   for (int tile = blockIdx.x; tile < total; tile += gridDim.x) {
     int lo = 0, hi = E;                 // last e with tstart[e] <= tile
@@ -81,16 +86,36 @@ experts_simt_kernel(const T* __restrict__ x, const int32_t* __restrict__ token_i
         for (int j = 0; j < 4; ++j) { acc[i][j] = 0.f; accu[i][j] = 0.f; }
       for (int kc = 0; kc < d; kc += KC) {
         __syncthreads();
-        for (int i = tid; i < TM * KC; i += NT) {
-          const int r = i / KC, k = i % KC;
-          const int t = rows[r];
-          xs[r * XP + k] = (t >= 0 && kc + k < d) ? DT<T>::to_f(x[(int64_t)t * d + kc + k]) : 0.f;
-        }
-        for (int i = tid; i < KC * CB; i += NT) {
-          const int k = i / CB, c = i % CB;
-          const bool ok = (kc + k < d) && (hc + c < H);
-          ws[k * WP + c] = ok ? DT<T>::to_f(w1e[(int64_t)(kc + k) * H + hc + c]) : 0.f;
-          if (GLU) wu[k * WP + c] = ok ? DT<T>::to_f(wue[(int64_t)(kc + k) * H + hc + c]) : 0.f;
+        if (vec) {
+          {
+            const int r = tid >> 3, k = (tid & 7) << 2;
+            const int t = rows[r];
+            *reinterpret_cast<float4*>(&xs[r * XP + k]) =
+                (t >= 0 && kc + k < d) ? load4(x + (int64_t)t * d + kc + k) : z4;
+          }
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            const int k = (tid >> 5) + 8 * j, c = (tid & 31) << 2;
+            const bool ok = (kc + k < d) && (hc + c < H);
+            *reinterpret_cast<float4*>(&ws[k * WP + c]) =
+                ok ? load4(w1e + (int64_t)(kc + k) * H + hc + c) : z4;
+            if (GLU)
+              *reinterpret_cast<float4*>(&wu[k * WP + c]) =
+                  ok ? load4(wue + (int64_t)(kc + k) * H + hc + c) : z4;
+          }
+        } else {
+          for (int i = tid; i < TM * KC; i += NT) {
+            const int r = i / KC, k = i % KC;
+            const int t = rows[r];
+            xs[r * XP + k] =
+                (t >= 0 && kc + k < d) ? DT<T>::to_f(x[(int64_t)t * d + kc + k]) : 0.f;
+          }
+          for (int i = tid; i < KC * CB; i += NT) {
+            const int k = i / CB, c = i % CB;
+            const bool ok = (kc + k < d) && (hc + c < H);
+            ws[k * WP + c] = ok ? DT<T>::to_f(w1e[(int64_t)(kc + k) * H + hc + c]) : 0.f;
+            if (GLU) wu[k * WP + c] = ok ? DT<T>::to_f(wue[(int64_t)(kc + k) * H + hc + c]) : 0.f;
+          }
         }
         __syncthreads();
 #pragma unroll
@@ -145,10 +170,20 @@ experts_simt_kernel(const T* __restrict__ x, const int32_t* __restrict__ token_i
         for (int j = 0; j < 4; ++j) acc[i][j] = 0.f;
       for (int kc = 0; kc < H; kc += KC) {
         __syncthreads();
-        for (int i = tid; i < KC * CB; i += NT) {
-          const int k = i / CB, c = i % CB;
-          ws[k * WP + c] =
-              (kc + k < H && dc + c < d) ? DT<T>::to_f(w2e[(int64_t)(kc + k) * d + dc + c]) : 0.f;
+        if (vec) {
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            const int k = (tid >> 5) + 8 * j, c = (tid & 31) << 2;
+            *reinterpret_cast<float4*>(&ws[k * WP + c]) =
+                (kc + k < H && dc + c < d) ? load4(w2e + (int64_t)(kc + k) * d + dc + c) : z4;
+          }
+        } else {
+          for (int i = tid; i < KC * CB; i += NT) {
+            const int k = i / CB, c = i % CB;
+            ws[k * WP + c] = (kc + k < H && dc + c < d)
+                                 ? DT<T>::to_f(w2e[(int64_t)(kc + k) * d + dc + c])
+                                 : 0.f;
+          }
         }
         __syncthreads();
         const int kn = min(KC, H - kc);

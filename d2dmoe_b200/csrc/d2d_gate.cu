@@ -55,6 +55,8 @@ router_mask_simt_kernel(const T* __restrict__ x, const T* __restrict__ wa,
   float* hs = wsm + RC * KP;           // [TM][R]
   const int tid = threadIdx.x, lane = tid & 31, ty = tid >> 5;
   const int64_t t0 = (int64_t)blockIdx.x * TM;
+  // vector staging needs rows that start on a 4-element boundary
+  const bool vec = (d % 4 == 0) && ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(wa)) % 16 == 0);
 
   for (int rc = 0; rc < R; rc += RC) {
     float acc[4][4];
@@ -64,15 +66,30 @@ router_mask_simt_kernel(const T* __restrict__ x, const T* __restrict__ wa,
       for (int j = 0; j < 4; ++j) acc[i][j] = 0.f;
     for (int kc = 0; kc < d; kc += KC) {
       __syncthreads();
-      for (int i = tid; i < TM * KC; i += NT) {
-        const int r = i / KC, k = i % KC;
+      if (vec) {
+        // one 4-element vector per thread and pass: row = tid / 8 (+32 per pass), k = 4*(tid%8)
+        const int r = tid >> 3, k = (tid & 7) << 2;
         const int64_t t = t0 + r;
-        xs[r * KP + k] = (t < N && kc + k < d) ? DT<T>::to_f(x[t * d + kc + k]) : 0.f;
-      }
-      for (int i = tid; i < RC * KC; i += NT) {
-        const int c = i / KC, k = i % KC;
-        wsm[c * KP + k] =
-            (rc + c < R && kc + k < d) ? DT<T>::to_f(wa[(int64_t)(rc + c) * d + kc + k]) : 0.f;
+        const float4 z = make_float4(0.f, 0.f, 0.f, 0.f);
+        *reinterpret_cast<float4*>(&xs[r * KP + k]) =
+            (t < N && kc + k < d) ? load4(x + t * d + kc + k) : z;
+#pragma unroll
+        for (int j = 0; j < RC / 32; ++j) {
+          const int c = r + 32 * j;
+          *reinterpret_cast<float4*>(&wsm[c * KP + k]) =
+              (rc + c < R && kc + k < d) ? load4(wa + (int64_t)(rc + c) * d + kc + k) : z;
+        }
+      } else {
+        for (int i = tid; i < TM * KC; i += NT) {
+          const int r = i / KC, k = i % KC;
+          const int64_t t = t0 + r;
+          xs[r * KP + k] = (t < N && kc + k < d) ? DT<T>::to_f(x[t * d + kc + k]) : 0.f;
+        }
+        for (int i = tid; i < RC * KC; i += NT) {
+          const int c = i / KC, k = i % KC;
+          wsm[c * KP + k] =
+              (rc + c < R && kc + k < d) ? DT<T>::to_f(wa[(int64_t)(rc + c) * d + kc + k]) : 0.f;
+        }
       }
       __syncthreads();
 #pragma unroll
