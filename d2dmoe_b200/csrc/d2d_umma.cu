@@ -46,8 +46,9 @@ constexpr int SLOT = TILE_M * 128;   // 16 KB: 128 rows x 64 bf16, also the weig
 constexpr int NA_MAX = 6;            // ring A stages (upper bound)
 constexpr int NB_MAX = 6;            // ring B stages (upper bound)
 constexpr int SLOTS_TOTAL = 14;      // ring A + ring B + hidden tile + staging (224 KB)
-constexpr int NTHREADS = 480;
-constexpr int WARP_MMA1 = 8, WARP_MMA2 = 9, WARP_BULK = 10, WARP_PROD0 = 11;
+constexpr int NTHREADS = 480;            // router form
+constexpr int NTHREADS_EXPERTS = 608;    // + four warps that write the output rows
+constexpr int WARP_MMA1 = 8, WARP_MMA2 = 9, WARP_BULK = 10, WARP_PROD0 = 11, WARP_WR0 = 15;
 constexpr int MAX_E = 128;
 constexpr uint32_t WAIT_LIMIT = 1u << 22;
 constexpr int MODE_EXPERTS = 0, MODE_ROUTER = 1;
@@ -339,6 +340,7 @@ struct Ctl {
   unsigned long long fullA[NA_MAX], emptyA[NA_MAX], fullB[NB_MAX], emptyB[NB_MAX];
   unsigned long long fullB2[NB_MAX], emptyB2[NB_MAX];
   unsigned long long acc1_full[2], acc1_empty[2], hs_full, hs_empty, acc2_full[2], acc2_empty[2];
+  unsigned long long sfull[2][4], sempty[2][4];   // staging unit of (epilogue group, row quarter)
   uint32_t tmem_base;
   int abort_flag;
   int total_tiles;
@@ -672,7 +674,7 @@ __device__ void role_epilogue(const Params& p, Ctl* c, uint32_t hs, uint32_t stg
   const uint32_t lane_base = (uint32_t)(r & ~31) << 16;
   const uint32_t hs_row = hs + (r >> 3) * 1024 + (r & 7) * 128;
   const bool la = lookahead(g);
-  uint32_t i = 0, ph_mine = 0;
+  uint32_t i = 0, ph_mine = 0, ph_stg = 0;
   // Router without residual: every token's initial output is the same row (last_bias or
   // zeros).  Keep that row in shared memory and let the TMA engine write it once per
   // token, instead of spending the epilogue warps' store bandwidth on it.
@@ -774,20 +776,11 @@ __device__ void role_epilogue(const Params& p, Ctl* c, uint32_t hs, uint32_t stg
     mbar_arrive(smem_u32(&c->hs_full));
     // ---- epilogue 2 -------------------------------------------------------------
     if (MODE == MODE_EXPERTS) {
-      long long tok = -1;
-      if (r < t.nrows) {
-        tok = p.token_idx[t.r0 + r];
-        if (tok < 0 || tok >= p.N) tok = -1;     // reported by the producer
-      }
-      const int rl = lane >> 3, pl = lane & 7;
-      // In the read-back, this lane serves rows it*4 + rl (it = 0..7) of the warp: fetch
-      // their output row pointers once per tile (null = row past the tail).
-      bf16* orow[8];
-#pragma unroll
-      for (int it = 0; it < 8; ++it) {
-        const long long tk = __shfl_sync(0xffffffffu, tok, it * 4 + rl);
-        orow[it] = tk < 0 ? nullptr : p.out + tk * p.d + pl * 8;
-      }
+      // accumulator -> bf16 -> this warp's 32 x 128-byte staging block; the writer warp of
+      // the same row quarter adds it to the output rows, so this warp never waits on the
+      // global write path
+      const uint32_t bar_full = smem_u32(&c->sfull[grp][w8 & 3]);
+      const uint32_t bar_empty = smem_u32(&c->sempty[grp][w8 & 3]);
       for (int nci = grp; nci < g.nc; nci += 2) {
         if (!mbar_wait_fast(smem_u32(&c->acc2_full[grp]), ph_mine, af, p.dev_status)) return;
         ph_mine ^= 1;
@@ -802,6 +795,7 @@ __device__ void role_epilogue(const Params& p, Ctl* c, uint32_t hs, uint32_t stg
             tc_fence_before();
             mbar_arrive(smem_u32(&c->acc2_empty[grp]));
           }
+          if (!mbar_wait_fast(bar_empty, ph_stg ^ 1, af, p.dev_status)) return;
           // bf16 -> this warp's staging rows (piece XOR row: conflict-free 16-byte stores)
 #pragma unroll
           for (int pc = 0; pc < 8; ++pc) {
@@ -812,21 +806,8 @@ __device__ void role_epilogue(const Params& p, Ctl* c, uint32_t hs, uint32_t stg
                                   __uint_as_float(v[8 * pc + 2 * q + 1]));
             st_shared_v4(stg_w + lane * 128 + ((pc ^ (lane & 7)) << 4), ww[0], ww[1], ww[2], ww[3]);
           }
-          __syncwarp();
-          // read back row-contiguous: 8 lanes cover one row's 128 bytes, so one red
-          // instruction touches 4 rows (4 cache lines) instead of 32
-          const int col = nci * g.nd + hf * 64;
-          uint4 val[8];
-#pragma unroll
-          for (int it = 0; it < 8; ++it) {      // all shared loads first, then all reds
-            const int rr = it * 4 + rl;
-            val[it] = ld_shared_v4(stg_w + rr * 128 + ((pl ^ (rr & 7)) << 4));
-          }
-          __syncwarp();                         // staging may be overwritten from here on
-#pragma unroll
-          for (int it = 0; it < 8; ++it)
-            if (orow[it])
-              red_add_bf16x8(orow[it] + col, val[it].x, val[it].y, val[it].z, val[it].w);
+          mbar_arrive(bar_full);
+          ph_stg ^= 1;
         }
       }
     } else if (grp == 0) {
@@ -892,10 +873,203 @@ __device__ void role_epilogue(const Params& p, Ctl* c, uint32_t hs, uint32_t stg
 }
 
 // ---------------------------------------------------------------------------
+// experts form: epilogue roles
+// ---------------------------------------------------------------------------
+// 16 hidden columns as 8 packed bf16 pairs, with the upstream rounding points
+// (T(x W1), + b1, activation, x T(x W_up)) done in packed bf16 arithmetic: one
+// float->bf16x2 conversion per pair instead of one conversion per rounding point.
+template <int ACT>
+__device__ __forceinline__ void ep1_pairs(const uint32_t* v, const uint32_t* u, const uint32_t* bp,
+                                          bool glu, uint32_t* w) {
+#pragma unroll
+  for (int q = 0; q < 8; ++q) {
+    __nv_bfloat162 h =
+        __floats2bfloat162_rn(__uint_as_float(v[2 * q]), __uint_as_float(v[2 * q + 1]));
+    h = __hadd2_rn(h, *reinterpret_cast<const __nv_bfloat162*>(&bp[q]));
+    if (ACT == D2D_RELU) {
+      h = __hmax2(h, __float2bfloat162_rn(0.f));
+    } else {
+      const float2 f = __bfloat1622float2(h);
+      h = __floats2bfloat162_rn(activate(f.x, ACT), activate(f.y, ACT));
+    }
+    if (glu) {
+      const __nv_bfloat162 uu =
+          __floats2bfloat162_rn(__uint_as_float(u[2 * q]), __uint_as_float(u[2 * q + 1]));
+      h = __hmul2_rn(h, uu);
+    }
+    w[q] = *reinterpret_cast<uint32_t*>(&h);
+  }
+}
+
+// Warps 0-3: accumulator 1 -> bias, activation (x up-projection) -> bf16 hidden tile in
+// shared memory, one tile after another.  Thread = tile row = TMEM lane.
+__device__ void role_ep1_experts(const Params& p, Ctl* c, uint32_t hs, uint32_t tmem, int et) {
+  volatile int* af = &c->abort_flag;
+  const Geo& g = p.g;
+  const int r = et;
+  const uint32_t lane_base = (uint32_t)(r & ~31) << 16;
+  const uint32_t hs_row = hs + (r >> 3) * 1024 + (r & 7) * 128;
+  const bool la = lookahead(g);
+  uint32_t* bias_p = reinterpret_cast<uint32_t*>(c->bias_s);   // [2][64] packed pairs
+  const int npair = g.nsubw >> 1;
+  uint32_t i = 0;
+  for (int tile = blockIdx.x; tile < c->total_tiles; tile += gridDim.x, ++i) {
+    const Tile t = tile_info<MODE_EXPERTS>(p, c, tile);
+    // this expert's bias as bf16 pairs; two copies alternate so that a warp already on the
+    // next tile never overwrites pairs another warp still reads
+    uint32_t* bp = bias_p + (i & 1) * 64;
+    if (et < npair) {
+      const float2 b = __ldg(reinterpret_cast<const float2*>(p.packed + (long long)t.e * g.stride +
+                                                             g.bias_off) + et);
+      bp[et] = pack_bf16x2(b.x, b.y);
+    }
+    asm volatile("bar.sync 2, 128;" ::: "memory");
+    const uint32_t b1 = la ? (i & 1) : 0;
+    const uint32_t acc1 = tmem + lane_base + (la ? b1 * 128 : 0);
+    if (!mbar_wait_fast(smem_u32(&c->acc1_full[b1]), la ? ((i >> 1) & 1) : (i & 1), af,
+                        p.dev_status))
+      return;
+    if (!mbar_wait_fast(smem_u32(&c->hs_empty), (i & 1) ^ 1, af, p.dev_status)) return;
+    tc_fence_after();
+    for (int c0 = 0; c0 < g.nsubw; c0 += 16) {
+      uint32_t v[16], u[16], w[8], bb[8];
+      tmem_ld16(acc1 + c0, v);
+      if (p.glu) tmem_ld16(acc1 + 128 + c0, u);
+      const uint4 q0 = *reinterpret_cast<const uint4*>(bp + (c0 >> 1));
+      const uint4 q1 = *reinterpret_cast<const uint4*>(bp + (c0 >> 1) + 4);
+      bb[0] = q0.x; bb[1] = q0.y; bb[2] = q0.z; bb[3] = q0.w;
+      bb[4] = q1.x; bb[5] = q1.y; bb[6] = q1.z; bb[7] = q1.w;
+      tmem_wait_ld();
+      switch (p.act) {      // uniform branch around the element loop
+        case D2D_RELU: ep1_pairs<D2D_RELU>(v, u, bb, p.glu != 0, w); break;
+        case D2D_GELU: ep1_pairs<D2D_GELU>(v, u, bb, p.glu != 0, w); break;
+        case D2D_TANH: ep1_pairs<D2D_TANH>(v, u, bb, p.glu != 0, w); break;
+        case D2D_LEAKY_RELU: ep1_pairs<D2D_LEAKY_RELU>(v, u, bb, p.glu != 0, w); break;
+        default: ep1_pairs<D2D_GELU_TANH>(v, u, bb, p.glu != 0, w); break;
+      }
+      const uint32_t base = hs_row + (c0 >> 6) * SLOT;
+      const int j0 = (c0 & 63) >> 3;
+      st_shared_v4(base + (((j0) ^ (r & 7)) << 4), w[0], w[1], w[2], w[3]);
+      st_shared_v4(base + (((j0 + 1) ^ (r & 7)) << 4), w[4], w[5], w[6], w[7]);
+    }
+    tc_fence_before();
+    mbar_arrive(smem_u32(&c->acc1_empty[b1]));     // acc1 buffer read completely
+    fence_proxy_async();     // ordinary shared stores -> visible to the MMA's async reads
+    mbar_arrive(smem_u32(&c->hs_full));
+  }
+}
+
+// Warps 4-7: accumulator 2 -> bf16 -> staging blocks.  Warp q owns two 32-row x 128-byte
+// blocks and fills them alternately; writer warp q adds them to the output rows.  This
+// role never touches global memory, so the accumulators are handed back to the GEMM2
+// warp as fast as the write path drains.
+__device__ void role_ep2_experts(const Params& p, Ctl* c, uint32_t stg, uint32_t tmem, int et) {
+  volatile int* af = &c->abort_flag;
+  const Geo& g = p.g;
+  const int lane = et & 31, q = et >> 5;
+  const uint32_t lane_base = (uint32_t)(et & ~31) << 16;
+  const int halves = g.nd >> 6;
+  uint32_t phbits = 0, n = 0;
+  for (int tile = blockIdx.x; tile < c->total_tiles; tile += gridDim.x) {
+    for (int nci = 0; nci < g.nc; ++nci) {
+      const uint32_t buf = nci & 1;
+      if (!mbar_wait_fast(smem_u32(&c->acc2_full[buf]), (phbits >> buf) & 1, af, p.dev_status))
+        return;
+      phbits ^= 1u << buf;
+      tc_fence_after();
+      for (int hf = 0; hf < halves; ++hf, ++n) {
+        uint32_t v[64];
+        tmem_ld32(tmem + lane_base + 256 + buf * 128 + hf * 64, v);
+        tmem_ld32(tmem + lane_base + 256 + buf * 128 + hf * 64 + 32, v + 32);
+        tmem_wait_ld();
+        if (hf == halves - 1) {     // accumulator buffer read completely: hand it back
+          tc_fence_before();
+          mbar_arrive(smem_u32(&c->acc2_empty[buf]));
+        }
+        const uint32_t blk = n & 1;
+        if (!mbar_wait_fast(smem_u32(&c->sempty[blk][q]), ((n >> 1) & 1) ^ 1, af, p.dev_status))
+          return;
+        const uint32_t dst = stg + (blk * 4 + q) * 4096 + lane * 128;
+        // piece XOR row: conflict-free 16-byte stores
+#pragma unroll
+        for (int pc = 0; pc < 8; ++pc) {
+          uint32_t ww[4];
+#pragma unroll
+          for (int k = 0; k < 4; ++k)
+            ww[k] = pack_bf16x2(__uint_as_float(v[8 * pc + 2 * k]),
+                                __uint_as_float(v[8 * pc + 2 * k + 1]));
+          st_shared_v4(dst + ((pc ^ (lane & 7)) << 4), ww[0], ww[1], ww[2], ww[3]);
+        }
+        mbar_arrive(smem_u32(&c->sfull[blk][q]));
+      }
+    }
+  }
+}
+
+// Writer warps: warp q adds the staged bf16 blocks of row quarter q to the output rows.
+// The global write path takes about 24 bytes per clock and SM for vector reds whichever
+// warps issue them, so it gets warps of its own.  A lane reads its rows back
+// row-contiguous (8 lanes cover one row's 128 bytes), so one red instruction touches 4
+// cache lines instead of 32.
+__device__ void role_writer(const Params& p, Ctl* c, uint32_t stg, int wt) {
+  volatile int* af = &c->abort_flag;
+  const Geo& g = p.g;
+  const int lane = wt & 31, q = wt >> 5;
+  const int rl = lane >> 3, pl = lane & 7;
+  const int halves = g.nd >> 6;
+  uint32_t n = 0;
+  int tile = blockIdx.x;
+  const int total = c->total_tiles, step = gridDim.x;
+  Tile t = {0, 0, 0};
+  long long tok = -1;
+  if (tile < total) {
+    t = tile_info<MODE_EXPERTS>(p, c, tile);
+    const int r = q * 32 + lane;
+    if (r < t.nrows) tok = p.token_idx[t.r0 + r];
+  }
+  for (; tile < total; tile += step) {
+    if (tok < 0 || tok >= p.N) tok = -1;      // out-of-range indices are reported by the producer
+    bf16* orow[8];
+#pragma unroll
+    for (int it = 0; it < 8; ++it) {
+      const long long tk = __shfl_sync(0xffffffffu, tok, it * 4 + rl);
+      orow[it] = tk < 0 ? nullptr : p.out + tk * p.d + pl * 8;
+    }
+    // rows of the next tile: the load is in flight while this tile's blocks are written
+    tok = -1;
+    if (tile + step < total) {
+      t = tile_info<MODE_EXPERTS>(p, c, tile + step);
+      const int r = q * 32 + lane;
+      if (r < t.nrows) tok = p.token_idx[t.r0 + r];
+    }
+    for (int nci = 0; nci < g.nc; ++nci) {
+      for (int hf = 0; hf < halves; ++hf, ++n) {
+        const uint32_t blk = n & 1;
+        const uint32_t src = stg + (blk * 4 + q) * 4096;
+        if (!mbar_wait_fast(smem_u32(&c->sfull[blk][q]), (n >> 1) & 1, af, p.dev_status)) return;
+        uint4 val[8];
+#pragma unroll
+        for (int it = 0; it < 8; ++it) {      // all shared loads first, then all reds
+          const int rr = it * 4 + rl;
+          val[it] = ld_shared_v4(src + rr * 128 + ((pl ^ (rr & 7)) << 4));
+        }
+        mbar_arrive(smem_u32(&c->sempty[blk][q]));   // block may be overwritten
+        const int col = nci * g.nd + hf * 64;
+#pragma unroll
+        for (int it = 0; it < 8; ++it)
+          if (orow[it])
+            red_add_bf16x8(orow[it] + col, val[it].x, val[it].y, val[it].z, val[it].w);
+      }
+    }
+  }
+}
+
+// ---------------------------------------------------------------------------
 // kernel
 // ---------------------------------------------------------------------------
 template <int MODE>
-__global__ void __launch_bounds__(NTHREADS, 1) mlp_tiles_kernel(const Params p) {
+__global__ void __launch_bounds__(MODE == MODE_EXPERTS ? NTHREADS_EXPERTS : NTHREADS, 1)
+mlp_tiles_kernel(const Params p) {
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw = smem_u32(smem_raw);
   const uint32_t base = (raw + 1023u) & ~1023u;
@@ -920,13 +1094,19 @@ __global__ void __launch_bounds__(NTHREADS, 1) mlp_tiles_kernel(const Params p) 
       mbar_init(smem_u32(&c->fullB2[i]), 1);
       mbar_init(smem_u32(&c->emptyB2[i]), 1);
     }
-    mbar_init(smem_u32(&c->hs_full), 256);
+    // experts form: warps 0-3 write the hidden tile, warps 4-7 read accumulator 2
+    constexpr uint32_t EP1_THREADS = MODE == MODE_EXPERTS ? 128 : 256;
+    mbar_init(smem_u32(&c->hs_full), EP1_THREADS);
     mbar_init(smem_u32(&c->hs_empty), 1);
     for (int i = 0; i < 2; ++i) {
       mbar_init(smem_u32(&c->acc1_full[i]), 1);
-      mbar_init(smem_u32(&c->acc1_empty[i]), 256);
+      mbar_init(smem_u32(&c->acc1_empty[i]), EP1_THREADS);
       mbar_init(smem_u32(&c->acc2_full[i]), 1);
       mbar_init(smem_u32(&c->acc2_empty[i]), 128);
+      for (int q = 0; q < 4; ++q) {
+        mbar_init(smem_u32(&c->sfull[i][q]), 32);
+        mbar_init(smem_u32(&c->sempty[i][q]), 32);
+      }
     }
     c->abort_flag = 0;
     if (MODE == MODE_ROUTER) c->total_tiles = (int)((p.N + TILE_M - 1) / TILE_M);
@@ -983,8 +1163,12 @@ __global__ void __launch_bounds__(NTHREADS, 1) mlp_tiles_kernel(const Params p) 
   tc_fence_after();
   const uint32_t tmem = c->tmem_base;
 
-  if (warp < 8) {
-    role_epilogue<MODE>(p, c, hs, stg, tmem, tid);
+  if (MODE == MODE_EXPERTS && warp < 4) {
+    role_ep1_experts(p, c, hs, tmem, tid);
+  } else if (MODE == MODE_EXPERTS && warp < 8) {
+    role_ep2_experts(p, c, stg, tmem, tid - 128);
+  } else if (warp < 8) {
+    role_epilogue<MODE_ROUTER>(p, c, hs, stg, tmem, tid);
     bulk_wait_all();       // TMA row stores read shared memory: finish before the CTA ends
   } else if (warp == WARP_MMA1) {
     role_mma1<MODE>(p, c, ringA, ringB, tmem);
@@ -992,9 +1176,11 @@ __global__ void __launch_bounds__(NTHREADS, 1) mlp_tiles_kernel(const Params p) 
     role_mma2<MODE>(p, c, ringB2, hs, tmem);
   } else if (warp == WARP_BULK) {
     role_bulk<MODE>(p, c, ringB, ringB2);
-  } else {
+  } else if (warp < WARP_WR0) {
     role_producer<MODE>(p, c, ringA, tid - WARP_PROD0 * 32);
     cp_async_wait_all();
+  } else if (MODE == MODE_EXPERTS) {
+    role_writer(p, c, stg, tid - WARP_WR0 * 32);
   }
 
   tc_fence_before();
@@ -1106,7 +1292,7 @@ int launch(const Params& p, long long max_tiles, cudaStream_t s) {
   }
   long long grid = max_tiles < sm_count() ? max_tiles : sm_count();
   if (grid < 1) grid = 1;
-  k<<<(unsigned)grid, NTHREADS, smem, s>>>(p);
+  k<<<(unsigned)grid, MODE == MODE_EXPERTS ? NTHREADS_EXPERTS : NTHREADS, smem, s>>>(p);
   return cudaGetLastError() == cudaSuccess ? D2D_OK : D2D_ERR_LAUNCH;
 }
 
