@@ -400,30 +400,6 @@ struct RingPos {
   }
 };
 
-// Whole-warp bounded wait on up to three barriers at once: lane j polls barrier j, so
-// the warp pays one shared-memory round trip instead of one per barrier.  The result is
-// warp-uniform.
-__device__ __forceinline__ bool warp_wait(uint32_t bar0, uint32_t par0, volatile int* af,
-                                          int* dev_status, uint32_t bar1 = 0, uint32_t par1 = 0,
-                                          uint32_t bar2 = 0, uint32_t par2 = 0) {
-  const uint32_t lane = threadIdx.x & 31;
-  const uint32_t bar = lane == 0 ? bar0 : lane == 1 ? bar1 : lane == 2 ? bar2 : 0u;
-  const uint32_t par = lane == 0 ? par0 : lane == 1 ? par1 : par2;
-  for (uint32_t i = 0; i < WAIT_LIMIT; ++i) {
-    const bool ok = bar == 0u || mbar_try_wait(bar, par);
-    if (__all_sync(0xffffffffu, ok)) return true;
-    if (i > 64) {
-      __nanosleep(i > 4096 ? 256 : 32);
-      if ((i & 63) == 0 && __any_sync(0xffffffffu, *af != 0)) return false;
-    }
-  }
-  if (lane == 0) {
-    *af = 1;
-    report(dev_status, D2D_ERR_TIMEOUT);
-  }
-  return false;
-}
-
 // With one weight subtile per k-chunk (nsub == 1) the first accumulator is double
 // buffered and GEMM1 of the next tile is issued before GEMM2 of the current one, so the
 // tensor pipe works while the epilogue warps turn acc1 into the hidden tile.
@@ -477,8 +453,12 @@ __device__ void role_producer(const Params& p, Ctl* c, uint32_t ringA, int pt) {
   }
 }
 
-// Weight tiles for both rings.  The two streams (W1 tiles for the GEMM1 warp, W2 pieces
-// for the GEMM2 warp) advance independently: whichever ring has a free stage gets its
+// The three issuing roles below (weight loads, GEMM1, GEMM2) each run in ONE thread of
+// their warp for the whole launch: their loops are chains of dependent instructions, so
+// warp votes, elections and re-convergence per k-chunk only lengthen the chain.
+
+// Weight tiles for both rings.  The two streams (W1 tiles for the GEMM1 thread, W2 pieces
+// for the GEMM2 thread) advance independently: whichever ring has a free stage gets its
 // next tile, so neither GEMM waits for the other's weights.
 template <int MODE>
 __device__ void role_bulk(const Params& p, Ctl* c, uint32_t ringB, uint32_t ringB2) {
@@ -487,6 +467,8 @@ __device__ void role_bulk(const Params& p, Ctl* c, uint32_t ringB, uint32_t ring
   const uint32_t b1 = g.nsubw * 128, b2 = g.nd * 128;
   const int n1 = g.kc1 * g.nsub, n2 = g.nc * g.kc2;
   const int step = gridDim.x, total = c->total_tiles;
+  const uint32_t fullB = smem_u32(c->fullB), emptyB = smem_u32(c->emptyB);
+  const uint32_t fullB2 = smem_u32(c->fullB2), emptyB2 = smem_u32(c->emptyB2);
   RingPos r1 = {0, 0}, r2 = {0, 0};
   int t1 = blockIdx.x, t2 = blockIdx.x, j1 = 0, j2 = 0;
   const uint8_t *pe1 = nullptr, *pe2 = nullptr;
@@ -494,15 +476,10 @@ __device__ void role_bulk(const Params& p, Ctl* c, uint32_t ringB, uint32_t ring
   uint32_t idle = 0;
   while (t1 < total || t2 < total) {
     bool progress = false;
-    // every decision below is warp-uniform (votes), so elect.sync sees the whole warp
-    if (t1 < total &&
-        __all_sync(0xffffffffu, mbar_test_wait(smem_u32(&c->emptyB[r1.s]), r1.ph ^ 1))) {
-      const uint32_t bar = smem_u32(&c->fullB[r1.s]);
-      if (elect_one()) {
-        mbar_arrive_expect_tx(bar, b1);
-        bulk_g2s(ringB + r1.s * SLOT, pe1 + (long long)j1 * b1, b1, bar);
-      }
-      __syncwarp();
+    if (t1 < total && mbar_test_wait(emptyB + 8 * r1.s, r1.ph ^ 1)) {
+      const uint32_t bar = fullB + 8 * r1.s;
+      mbar_arrive_expect_tx(bar, b1);
+      bulk_g2s(ringB + r1.s * SLOT, pe1 + (long long)j1 * b1, b1, bar);
       r1.next(g.nb);
       if (++j1 == n1) {
         j1 = 0;
@@ -511,14 +488,10 @@ __device__ void role_bulk(const Params& p, Ctl* c, uint32_t ringB, uint32_t ring
       }
       progress = true;
     }
-    if (t2 < total &&
-        __all_sync(0xffffffffu, mbar_test_wait(smem_u32(&c->emptyB2[r2.s]), r2.ph ^ 1))) {
-      const uint32_t bar = smem_u32(&c->fullB2[r2.s]);
-      if (elect_one()) {
-        mbar_arrive_expect_tx(bar, b2);
-        bulk_g2s(ringB2 + r2.s * SLOT, pe2 + g.w1_bytes + (long long)j2 * b2, b2, bar);
-      }
-      __syncwarp();
+    if (t2 < total && mbar_test_wait(emptyB2 + 8 * r2.s, r2.ph ^ 1)) {
+      const uint32_t bar = fullB2 + 8 * r2.s;
+      mbar_arrive_expect_tx(bar, b2);
+      bulk_g2s(ringB2 + r2.s * SLOT, pe2 + g.w1_bytes + (long long)j2 * b2, b2, bar);
       r2.next(g.nb2);
       if (++j2 == n2) {
         j2 = 0;
@@ -531,12 +504,10 @@ __device__ void role_bulk(const Params& p, Ctl* c, uint32_t ringB, uint32_t ring
       idle = 0;
     } else {
       if (++idle > 64) __nanosleep(idle > 4096 ? 256 : 32);
-      if ((idle & 63) == 0 && __any_sync(0xffffffffu, *af != 0)) return;
+      if ((idle & 63) == 0 && *af != 0) return;
       if (idle >= WAIT_LIMIT) {
-        if ((threadIdx.x & 31) == 0) {
-          *af = 1;
-          report(p.dev_status, D2D_ERR_TIMEOUT);
-        }
+        *af = 1;
+        report(p.dev_status, D2D_ERR_TIMEOUT);
         return;
       }
     }
@@ -544,96 +515,111 @@ __device__ void role_bulk(const Params& p, Ctl* c, uint32_t ringB, uint32_t ring
 }
 
 // GEMM1 stream: acc1[buffer][sub] = A(rows, d) * W1sub(d, nsubw), one tile after another.
+// Only the low word of a shared-memory descriptor changes with the stage and the k-step
+// (16-byte units: one slot = 1024, one k-step of 16 elements = 2).
 template <int MODE>
 __device__ void role_mma1(const Params& p, Ctl* c, uint32_t ringA, uint32_t ringB,
-                          uint32_t tmem_in) {
+                          uint32_t tmem) {
   volatile int* af = &c->abort_flag;
   const Geo& g = p.g;
-  const uint32_t tmem = __shfl_sync(0xffffffffu, tmem_in, 0);
   const uint32_t idesc1 = instr_desc(TILE_M, g.nsubw);
-  const uint64_t descA0 = smem_desc(ringA), descB0 = smem_desc(ringB);
-  const bool la = lookahead(g);
-  RingPos pa = {0, 0}, pb = {0, 0};
-  uint32_t i = 0;
-  for (int tile = blockIdx.x; tile < c->total_tiles; tile += gridDim.x, ++i) {
+  const uint64_t dA = smem_desc(ringA), dB = smem_desc(ringB);
+  const uint32_t hi = (uint32_t)(dA >> 32), alo0 = (uint32_t)dA, blo0 = (uint32_t)dB;
+  const uint32_t fullA = smem_u32(c->fullA), emptyA = smem_u32(c->emptyA);
+  const uint32_t fullB = smem_u32(c->fullB), emptyB = smem_u32(c->emptyB);
+  const bool la = lookahead(g), two = g.nsub == 2;
+  const uint32_t na = g.na, nb = g.nb;
+  const int kc1 = g.kc1, total = c->total_tiles;
+  uint32_t sa = 0, pha = 0, sb = 0, phb = 0, i = 0;
+  for (int tile = blockIdx.x; tile < total; tile += gridDim.x, ++i) {
     const uint32_t b = la ? (i & 1) : 0;
     const uint32_t use = la ? (i >> 1) : i;              // how often this buffer was used
     const uint32_t acc = tmem + (la ? b * 128 : 0);
     // the epilogue warps must have read the previous contents of this buffer
-    if (!warp_wait(smem_u32(&c->acc1_empty[b]), (use & 1) ^ 1, af, p.dev_status)) return;
+    if (!mbar_wait_fast(smem_u32(&c->acc1_empty[b]), (use & 1) ^ 1, af, p.dev_status)) return;
     tc_fence_after();
-    for (int kc = 0; kc < g.kc1; ++kc) {
-      const uint32_t sb0 = pb.s, ph0 = pb.ph;
-      pb.next(g.nb);
-      const uint32_t sb1 = pb.s, ph1 = pb.ph;
-      if (g.nsub == 2) pb.next(g.nb);
-      if (!warp_wait(smem_u32(&c->fullA[pa.s]), pa.ph, af, p.dev_status,
-                     smem_u32(&c->fullB[sb0]), ph0,
-                     g.nsub == 2 ? smem_u32(&c->fullB[sb1]) : 0u, ph1))
-        return;
+    for (int kc = 0; kc < kc1; ++kc) {
+      const uint32_t alo = alo0 + sa * (SLOT >> 4), blo = blo0 + sb * (SLOT >> 4);
+      if (!mbar_wait_fast(fullA + 8 * sa, pha, af, p.dev_status)) return;
+      if (!mbar_wait_fast(fullB + 8 * sb, phb, af, p.dev_status)) return;
       tc_fence_after();
-      // descriptors advance in 16-byte units: one slot = 1024 units, one k-step = 2
-      const uint64_t ad = descA0 + (uint64_t)(pa.s * (SLOT >> 4));
-      const uint64_t bd0 = descB0 + (uint64_t)(sb0 * (SLOT >> 4));
-      const uint64_t bd1 = descB0 + (uint64_t)(sb1 * (SLOT >> 4));
-      if (elect_one()) {
 #pragma unroll
-        for (int k = 0; k < 4; ++k) {
-          umma_bf16(acc, ad + 2 * k, bd0 + 2 * k, idesc1, (kc | k) != 0);
-          if (g.nsub == 2) umma_bf16(acc + 128, ad + 2 * k, bd1 + 2 * k, idesc1, (kc | k) != 0);
-        }
-        umma_commit(smem_u32(&c->emptyA[pa.s]));
-        umma_commit(smem_u32(&c->emptyB[sb0]));
-        if (g.nsub == 2) umma_commit(smem_u32(&c->emptyB[sb1]));
-        if (kc == g.kc1 - 1) umma_commit(smem_u32(&c->acc1_full[b]));
+      for (uint32_t k = 0; k < 4; ++k)
+        umma_bf16(acc, ((uint64_t)hi << 32) | (alo + 2 * k), ((uint64_t)hi << 32) | (blo + 2 * k),
+                  idesc1, (kc | k) != 0);
+      umma_commit(emptyB + 8 * sb);
+      if (++sb == nb) {
+        sb = 0;
+        phb ^= 1;
       }
-      __syncwarp();
-      pa.next(g.na);
+      if (two) {
+        const uint32_t blo1 = blo0 + sb * (SLOT >> 4);
+        if (!mbar_wait_fast(fullB + 8 * sb, phb, af, p.dev_status)) return;
+        tc_fence_after();
+#pragma unroll
+        for (uint32_t k = 0; k < 4; ++k)
+          umma_bf16(acc + 128, ((uint64_t)hi << 32) | (alo + 2 * k),
+                    ((uint64_t)hi << 32) | (blo1 + 2 * k), idesc1, (kc | k) != 0);
+        umma_commit(emptyB + 8 * sb);
+        if (++sb == nb) {
+          sb = 0;
+          phb ^= 1;
+        }
+      }
+      umma_commit(emptyA + 8 * sa);
+      if (++sa == na) {
+        sa = 0;
+        pha ^= 1;
+      }
     }
+    umma_commit(smem_u32(&c->acc1_full[b]));
   }
 }
 
 // GEMM2 stream: acc2[chunk & 1] = Hs(rows, K2) * W2chunk(K2, nd) for every chunk of a tile.
 template <int MODE>
 __device__ void role_mma2(const Params& p, Ctl* c, uint32_t ringB2, uint32_t hs,
-                          uint32_t tmem_in) {
+                          uint32_t tmem) {
   volatile int* af = &c->abort_flag;
   const Geo& g = p.g;
-  const uint32_t tmem = __shfl_sync(0xffffffffu, tmem_in, 0);
   const uint32_t idesc2 = instr_desc(TILE_M, g.nd);
-  const uint64_t descB0 = smem_desc(ringB2), descH0 = smem_desc(hs);
-  RingPos pb = {0, 0};
-  uint32_t ph_acc2[2] = {0, 0};
-  uint32_t i = 0;
-  for (int tile = blockIdx.x; tile < c->total_tiles; tile += gridDim.x, ++i) {
-    if (!warp_wait(smem_u32(&c->hs_full), i & 1, af, p.dev_status)) return;
+  const uint64_t dB = smem_desc(ringB2), dH = smem_desc(hs);
+  const uint32_t hi = (uint32_t)(dB >> 32), blo0 = (uint32_t)dB, hlo0 = (uint32_t)dH;
+  const uint32_t fullB2 = smem_u32(c->fullB2), emptyB2 = smem_u32(c->emptyB2);
+  const uint32_t nb2 = g.nb2;
+  const int nc = g.nc, kc2 = g.kc2, total = c->total_tiles;
+  uint32_t s = 0, ph = 0, accbits = 0, i = 0;
+  for (int tile = blockIdx.x; tile < total; tile += gridDim.x, ++i) {
+    if (!mbar_wait_fast(smem_u32(&c->hs_full), i & 1, af, p.dev_status)) return;
     tc_fence_after();
-    for (int nci = 0; nci < g.nc; ++nci) {
+    for (int nci = 0; nci < nc; ++nci) {
       const uint32_t buf = nci & 1;
-      for (int k2 = 0; k2 < g.kc2; ++k2) {
-        if (!warp_wait(smem_u32(&c->fullB2[pb.s]), pb.ph, af, p.dev_status,
-                       k2 == 0 ? smem_u32(&c->acc2_empty[buf]) : 0u, ph_acc2[buf] ^ 1))
-          return;
-        if (k2 == 0) ph_acc2[buf] ^= 1;
-        tc_fence_after();
-        const uint64_t hd = descH0 + (uint64_t)(k2 * (SLOT >> 4));
-        const uint64_t bd = descB0 + (uint64_t)(pb.s * (SLOT >> 4));
-        const int ksteps = min(4, (g.K2 - k2 * 64) >> 4);
-        if (elect_one()) {
-#pragma unroll
-          for (int k = 0; k < 4; ++k)
-            if (k < ksteps)
-              umma_bf16(tmem + 256 + buf * 128, hd + 2 * k, bd + 2 * k, idesc2, (k2 | k) != 0);
-          umma_commit(smem_u32(&c->emptyB2[pb.s]));
-          if (k2 == g.kc2 - 1) {
-            umma_commit(smem_u32(&c->acc2_full[buf]));
-            if (nci == g.nc - 1) umma_commit(smem_u32(&c->hs_empty));
-          }
+      const uint32_t acc = tmem + 256 + buf * 128;
+      for (int k2 = 0; k2 < kc2; ++k2) {
+        const uint32_t blo = blo0 + s * (SLOT >> 4), hlo = hlo0 + k2 * (SLOT >> 4);
+        if (!mbar_wait_fast(fullB2 + 8 * s, ph, af, p.dev_status)) return;
+        if (k2 == 0) {
+          if (!mbar_wait_fast(smem_u32(&c->acc2_empty[buf]), ((accbits >> buf) & 1) ^ 1, af,
+                              p.dev_status))
+            return;
+          accbits ^= 1u << buf;
         }
-        __syncwarp();
-        pb.next(g.nb2);
+        tc_fence_after();
+        const int ksteps = min(4, (g.K2 - k2 * 64) >> 4);
+#pragma unroll
+        for (int k = 0; k < 4; ++k)
+          if (k < ksteps)
+            umma_bf16(acc, ((uint64_t)hi << 32) | (hlo + 2 * k), ((uint64_t)hi << 32) | (blo + 2 * k),
+                      idesc2, (k2 | k) != 0);
+        umma_commit(emptyB2 + 8 * s);
+        if (++s == nb2) {
+          s = 0;
+          ph ^= 1;
+        }
       }
+      umma_commit(smem_u32(&c->acc2_full[buf]));
     }
+    umma_commit(smem_u32(&c->hs_empty));
   }
 }
 
@@ -1171,11 +1157,14 @@ mlp_tiles_kernel(const Params p) {
     role_epilogue<MODE_ROUTER>(p, c, hs, stg, tmem, tid);
     bulk_wait_all();       // TMA row stores read shared memory: finish before the CTA ends
   } else if (warp == WARP_MMA1) {
-    role_mma1<MODE>(p, c, ringA, ringB, tmem);
+    if (elect_one()) role_mma1<MODE>(p, c, ringA, ringB, tmem);
+    __syncwarp();
   } else if (warp == WARP_MMA2) {
-    role_mma2<MODE>(p, c, ringB2, hs, tmem);
+    if (elect_one()) role_mma2<MODE>(p, c, ringB2, hs, tmem);
+    __syncwarp();
   } else if (warp == WARP_BULK) {
-    role_bulk<MODE>(p, c, ringB, ringB2);
+    if (elect_one()) role_bulk<MODE>(p, c, ringB, ringB2);
+    __syncwarp();
   } else if (warp < WARP_WR0) {
     role_producer<MODE>(p, c, ringA, tid - WARP_PROD0 * 32);
     cp_async_wait_all();
@@ -1186,6 +1175,7 @@ mlp_tiles_kernel(const Params p) {
   tc_fence_before();
   __syncthreads();
   if (warp == WARP_MMA1) {
+    __syncwarp();
     tc_fence_after();
     tmem_dealloc(tmem, 512);
   }
