@@ -38,6 +38,35 @@ __device__ __forceinline__ float4 load4(const bf16* p) {
   return make_float4(a.x, a.y, b.x, b.y);
 }
 
+// ---- programmatic dependent launch ----------------------------------------
+// A kernel launched with launch_pdl may start while the previous kernel of the stream is
+// still running; it must call grid_dependency_wait() before it touches memory written by
+// earlier kernels.  grid_launch_dependents() lets the next such kernel be scheduled early.
+// Both are no-ops for kernels launched the ordinary way.
+__device__ __forceinline__ void grid_dependency_wait() {
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+}
+__device__ __forceinline__ void grid_launch_dependents() {
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}
+template <typename... KArgs, typename... Args>
+inline int launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem,
+                      cudaStream_t s, Args... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = s;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  if (cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...) == cudaSuccess) return D2D_OK;
+  cudaGetLastError();
+  return D2D_ERR_LAUNCH;
+}
+
 // ---- device status word ---------------------------------------------------
 // First error wins; kernels return early after reporting, they never trap.
 __device__ __forceinline__ void report(int* dev_status, int code) {

@@ -64,11 +64,13 @@ compact_scatter_kernel(const uint32_t* __restrict__ mask_bits, const int32_t* __
   const int nw = (E + 31) / 32;
   const int chunk = blockIdx.x;
 
+  grid_launch_dependents();
   for (int i = tid; i < ROWS * E; i += NTS) cnt[i] = 0;
   for (int e = tid; e < E; e += NTS) {
     tot[e] = 0;
     pre[e] = 0;
   }
+  grid_dependency_wait();      // mask and counts table come from the previous kernel
   __syncthreads();
   // column sums of the counts table: thread (grp, e) adds up tiles grp, grp+groups, ...
   // in registers (coalesced over e), then one shared atomic per thread
@@ -193,10 +195,8 @@ int launch_compact(const uint32_t* mask_bits, int32_t* token_idx, int32_t* offse
                              (int)smem) != cudaSuccess)
       return D2D_ERR_LAUNCH;
   }
-  compact_scatter_kernel<<<(unsigned)nchunks, NTS, smem, s>>>(mask_bits, counts_ws, token_idx,
-                                                             offsets, N, E, (int)ntiles,
-                                                             dev_status);
-  return cudaGetLastError() == cudaSuccess ? D2D_OK : D2D_ERR_LAUNCH;
+  return launch_pdl(compact_scatter_kernel, dim3((unsigned)nchunks), dim3(NTS), smem, s, mask_bits,
+                    (const int32_t*)counts_ws, token_idx, offsets, N, E, (int)ntiles, dev_status);
 }
 
 }  // namespace d2d

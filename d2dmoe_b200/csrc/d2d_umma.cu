@@ -1068,6 +1068,11 @@ mlp_tiles_kernel(const Params p) {
   Ctl* c = reinterpret_cast<Ctl*>(
       aligned + (size_t)(p.g.na + p.g.nb + p.g.nb2 + p.g.kc2 + p.g.stg) * SLOT);
   const int tid = threadIdx.x, warp = tid >> 5;
+  // Programmatic dependent launch: the next kernel of the stream may be scheduled as soon as
+  // every CTA of this one has passed this point (its CTAs still wait for this grid to
+  // finish before they read anything); this CTA in turn initialises its barriers while the
+  // previous kernel drains and reads global memory only after the wait below.
+  grid_launch_dependents();
 
   if (tid == 0) {
     for (int i = 0; i < NA_MAX; ++i) {
@@ -1099,6 +1104,7 @@ mlp_tiles_kernel(const Params p) {
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     fence_proxy_async();
   }
+  grid_dependency_wait();
   if (MODE == MODE_EXPERTS && warp == 1) {
     // tile tables: all offsets loaded in parallel (lane l owns experts 4l..4l+3), exclusive
     // scans across the warp of the full-tile counts and of the "has a partial tile" flags
@@ -1282,8 +1288,8 @@ int launch(const Params& p, long long max_tiles, cudaStream_t s) {
   }
   long long grid = max_tiles < sm_count() ? max_tiles : sm_count();
   if (grid < 1) grid = 1;
-  k<<<(unsigned)grid, MODE == MODE_EXPERTS ? NTHREADS_EXPERTS : NTHREADS, smem, s>>>(p);
-  return cudaGetLastError() == cudaSuccess ? D2D_OK : D2D_ERR_LAUNCH;
+  return launch_pdl(k, dim3((unsigned)grid), dim3(MODE == MODE_EXPERTS ? NTHREADS_EXPERTS : NTHREADS),
+                    smem, s, p);
 }
 
 }  // namespace
