@@ -67,6 +67,20 @@ int d2d_mask_from_scores(const void* scores, float thresh_mult, uint32_t* mask_b
                                  (cudaStream_t)stream);
 }
 
+int d2d_mask_rule_from_scores(const void* scores, int rule, int k, float tau, uint32_t* mask_bits,
+                              int64_t N, int E, int dtype, int* dev_status, d2d_stream_t stream) {
+  if (!scores || !mask_bits || N < 0 || E < 1) return D2D_ERR_BAD_ARG;
+  if (!dtype_ok(dtype)) return D2D_ERR_UNSUPPORTED;
+  if (rule == D2D_RULE_TOPK) {
+    if (k < 1 || k > E) return D2D_ERR_BAD_ARG;      // torch.topk raises for k out of range
+  } else if (rule != D2D_RULE_DYNK) {
+    return D2D_ERR_BAD_ARG;
+  }
+  (void)dev_status;
+  if (N == 0) return D2D_OK;
+  return launch_gate_rule(scores, rule, k, tau, mask_bits, N, E, dtype, (cudaStream_t)stream);
+}
+
 int d2d_init_out(const void* x, const void* last_bias_opt, int add_residual, void* out, int64_t N,
                  int d, int dtype, d2d_stream_t stream) {
   if (!out || N < 0 || d < 1 || (add_residual && !x)) return D2D_ERR_BAD_ARG;

@@ -183,6 +183,98 @@ mask_from_scores_kernel(const T* __restrict__ scores, float mult, uint32_t* __re
   }
 }
 
+// The other two routing rules of MoeficationMoE.gate on given scores
+// (architectures/moe/moefication.py:59-79), one warp per token, lane = expert (+32j):
+//   top-k : keep the k largest scores (NaN counts as largest, equal scores: lower index
+//           first, as torch.topk does on the host);
+//   dynk  : shares = T(s / T(sum s)); experts in descending share order; keep the first,
+//           and every further one while the cumulative share before it (fp32 running sum
+//           in that order, rounded to T per element, as torch.cumsum does) is < T(tau).
+// `before(a, ia, b, ib)`: a precedes b in the descending order used by both rules.
+template <typename T> struct Acc { typedef float type; };
+template <> struct Acc<float> { typedef double type; };
+
+__device__ __forceinline__ bool before(float a, int ia, float b, int ib) {
+  const bool an = a != a, bn = b != b;
+  if (an || bn) return an && (!bn || ia < ib);
+  return a > b || (a == b && ia < ib);
+}
+
+template <typename T>
+__global__ void __launch_bounds__(NT)
+gate_rule_kernel(const T* __restrict__ scores, int rule, int k, float tau,
+                 uint32_t* __restrict__ mask_bits, int64_t N, int E) {
+  __shared__ float sorted_s[NT / 32][256];
+  const int lane = threadIdx.x & 31, wi = threadIdx.x >> 5;
+  const int64_t warp = ((int64_t)blockIdx.x * NT + threadIdx.x) >> 5;
+  const int64_t nwarps = ((int64_t)gridDim.x * NT) >> 5;
+  const int nw = (E + 31) / 32;
+  const float tau_t = DT<T>::round(tau);
+  float* srt = sorted_s[wi];
+  for (int64_t t = warp; t < N; t += nwarps) {
+    float s[8];
+    int rank[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const int e = lane + 32 * j;
+      s[j] = (j < nw && e < E) ? DT<T>::to_f(scores[t * E + e]) : 0.f;
+      rank[j] = 0;
+    }
+    if (rule == D2D_RULE_DYNK) {
+      float tot = 0.f;
+#pragma unroll
+      for (int j = 0; j < 8; ++j)
+        if (j < nw && lane + 32 * j < E) tot += s[j];
+      for (int o = 16; o > 0; o >>= 1) tot += __shfl_xor_sync(0xffffffffu, tot, o);
+      tot = DT<T>::round(tot);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) s[j] = DT<T>::round(s[j] / tot);
+    }
+    // rank of each of my experts = number of experts that precede it
+#pragma unroll
+    for (int jj = 0; jj < 8; ++jj) {
+      if (jj >= nw) break;
+      for (int l = 0; l < 32; ++l) {
+        const int eo = l + 32 * jj;
+        if (eo >= E) break;                    // warp-uniform
+        const float v = __shfl_sync(0xffffffffu, s[jj], l);
+#pragma unroll
+        for (int j = 0; j < 8; ++j)
+          if (j < nw && before(v, eo, s[j], lane + 32 * j)) ++rank[j];
+      }
+    }
+    bool keep[8];
+    if (rule == D2D_RULE_TOPK) {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) keep[j] = rank[j] < k;
+    } else {
+      __syncwarp();
+#pragma unroll
+      for (int j = 0; j < 8; ++j)
+        if (j < nw && lane + 32 * j < E) srt[rank[j]] = s[j];
+      __syncwarp();
+#pragma unroll
+      for (int j = 0; j < 8; ++j) keep[j] = rank[j] == 0;
+      // running sum in the accumulation type torch.cumsum uses on the host: double for
+      // fp32 tensors, float for bf16
+      typename Acc<T>::type acc = 0;
+      for (int r = 0; r + 1 < E; ++r) {
+        acc += srt[r];
+        const bool more = DT<T>::round((float)acc) < tau_t;   // expert of rank r+1 still needed
+#pragma unroll
+        for (int j = 0; j < 8; ++j)
+          if (rank[j] == r + 1) keep[j] = more;
+      }
+    }
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      if (j >= nw) break;
+      const uint32_t word = __ballot_sync(0xffffffffu, keep[j] && lane + 32 * j < E);
+      if (lane == 0) mask_bits[t * nw + j] = word;
+    }
+  }
+}
+
 // The rule on given scores, fused with what the layer needs next: the compaction's counts
 // table (per 128-token tile) and the output's initial value.  One CTA = one 128-token
 // tile; warp w handles tokens 16w..16w+15 (lane = expert), then all threads write the
@@ -359,6 +451,17 @@ int launch_mask_from_scores(const void* scores, float mult, uint32_t* mask_bits,
     mask_from_scores_kernel<float><<<grid, NT, 0, s>>>((const float*)scores, mult, mask_bits, N, E);
   else
     mask_from_scores_kernel<bf16><<<grid, NT, 0, s>>>((const bf16*)scores, mult, mask_bits, N, E);
+  return cudaGetLastError() == cudaSuccess ? D2D_OK : D2D_ERR_LAUNCH;
+}
+
+int launch_gate_rule(const void* scores, int rule, int k, float tau, uint32_t* mask_bits,
+                     int64_t N, int E, int dtype, cudaStream_t s) {
+  if (E > 256) return D2D_ERR_UNSUPPORTED;
+  const int grid = grid_for(N, NT / 32, 148 * 8);
+  if (dtype == D2D_F32)
+    gate_rule_kernel<float><<<grid, NT, 0, s>>>((const float*)scores, rule, k, tau, mask_bits, N, E);
+  else
+    gate_rule_kernel<bf16><<<grid, NT, 0, s>>>((const bf16*)scores, rule, k, tau, mask_bits, N, E);
   return cudaGetLastError() == cudaSuccess ? D2D_OK : D2D_ERR_LAUNCH;
 }
 

@@ -344,27 +344,24 @@ class MoeficationMoE(MoELayer):
         if self.forward_mode == "all":
             return torch.ones(x.size(0), x.size(1), self.num_experts, dtype=x.dtype,
                               device=x.device)
-        if self.forward_mode == "topk":
-            s = self.router(x)
-            top = torch.topk(s, k=self.k, dim=-1)[1]
-            rt = torch.zeros_like(s)
-            rt.scatter_(2, top, 1.0)
-            return rt
-        if self.forward_mode == "dynk":
-            s = self.router(x)
-            shares = s / s.sum(dim=-1, keepdim=True)
-            srt, idx = torch.sort(shares, dim=-1, descending=True)
-            m = torch.cumsum(srt, dim=-1) < self.tau
-            m = m.roll(shifts=1, dims=-1)
-            m[..., 0] = True
-            return m.gather(dim=-1, index=idx.argsort(dim=-1)).to(x.dtype)
-        if self.forward_mode == "dynk_max":
+        if self.forward_mode in ("topk", "dynk", "dynk_max"):
             s = self.router(x)
             wsp = self._wsp.get(s.numel() // s.size(-1), self.num_experts, x.device)
             s2 = s.reshape(-1, s.size(-1)).contiguous()
-            ops.mask_from_scores(s2, self.tau, wsp)
+            self._rule_mask(s2, wsp)
             return ops.expand_mask(wsp, s2.size(0), s2.size(1), s.dtype).view(s.shape)
         raise ValueError(f"Unsupported forward_mode: {self.forward_mode}")
+
+    def _rule_mask(self, s2, wsp):
+        """Mask bits of the current routing rule from scores [N, E], on the device."""
+        if self.forward_mode == "topk":
+            if not 1 <= int(self.k) <= s2.size(1):
+                raise RuntimeError("selected index k out of range")       # as torch.topk
+            ops.mask_rule_from_scores(s2, "topk", wsp, k=self.k)
+        elif self.forward_mode == "dynk":
+            ops.mask_rule_from_scores(s2, "dynk", wsp, tau=self.tau)
+        else:
+            ops.mask_from_scores(s2, self.tau, wsp)
 
     @torch.no_grad()
     def forward(self, x):
@@ -401,6 +398,14 @@ class MoeficationMoE(MoELayer):
                             wsp, w_up=p["w_up"], scores=s2, last_bias=last_bias,
                             add_residual=self.add_residual_connection,
                             experts_packed=self.experts.packed())
+            rt = ops.expand_mask(wsp, N, E, s.dtype).view(*orig_size[:-1], E)
+        elif self.forward_mode in ("topk", "dynk"):
+            s = self.router(x)
+            self._rule_mask(s.reshape(N, E).contiguous(), wsp)
+            ops.compact(wsp, N, E)
+            ops.experts_ffn(x2d, wsp, p["w1"], p["b1"], p["w2"], p["act"], out, w_up=p["w_up"],
+                            packed=self.experts.packed(), last_bias=last_bias,
+                            add_residual=self.add_residual_connection, accumulate=False)
             rt = ops.expand_mask(wsp, N, E, s.dtype).view(*orig_size[:-1], E)
         else:
             rt = self.gate(x)

@@ -98,6 +98,25 @@ def router_mask(x2d, wa, wb, tau, wsp: Workspace, *, packed=None, scores_out=Non
           "d2d_router_mask")
 
 
+RULE_TOPK, RULE_DYNK = 1, 2
+
+
+def mask_rule_from_scores(scores2d, rule: str, wsp: Workspace, k=None, tau=None):
+    """Mask bits for the 'topk' / 'dynk' (cumulative share) rules of the upstream gate
+    (architectures/moe/moefication.py:59-79) on given scores [N, E]."""
+    _cu(scores2d)
+    N, E = scores2d.shape
+    if rule == "topk":
+        r, kk, tt = RULE_TOPK, int(k), 0.0
+    elif rule == "dynk":
+        r, kk, tt = RULE_DYNK, 0, float(tau)
+    else:
+        raise ValueError(f"unknown rule {rule!r}")
+    check(lib.d2d_mask_rule_from_scores(_ptr(scores2d), r, kk, tt, _ptr(wsp.mask_bits), N, E,
+                                        _dt(scores2d), _ptr(wsp.status), _stream()),
+          "d2d_mask_rule_from_scores")
+
+
 def mask_from_scores(scores2d, tau, wsp: Workspace):
     _cu(scores2d)
     N, E = scores2d.shape

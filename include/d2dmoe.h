@@ -94,6 +94,21 @@ int d2d_router_mask(const void* x, const void* wa, const void* wb,
 int d2d_mask_from_scores(const void* scores, float thresh_mult, uint32_t* mask_bits,
                          int64_t N, int E, int dtype, int* dev_status, d2d_stream_t stream);
 
+/* The other routing rules of MoeficationMoE.gate, on given scores:
+ *   D2D_RULE_TOPK  keep the k largest scores per token
+ *                  (architectures/moe/moefication.py:59-63);
+ *   D2D_RULE_DYNK  cumulative-share rule: shares = s / sum(s), experts in descending
+ *                  share order, keep the first and every further one while the
+ *                  cumulative share before it is < tau
+ *                  (architectures/moe/moefication.py:64-79).
+ * k is used by TOPK only (1 <= k <= E), tau by DYNK only (compared in the tensor dtype,
+ * as the upstream comparison of a tensor with a Python float does). */
+#define D2D_RULE_TOPK 1
+#define D2D_RULE_DYNK 2
+int d2d_mask_rule_from_scores(const void* scores, int rule, int k, float tau,
+                              uint32_t* mask_bits, int64_t N, int E, int dtype,
+                              int* dev_status, d2d_stream_t stream);
+
 /* out[t,:] = last_bias_opt (+ x[t,:]): the epilogue of MoeficationMoE.forward
  * (architectures/moe/moefication.py:96-99) as an initial value. */
 int d2d_init_out(const void* x, const void* last_bias_opt, int add_residual, void* out,

@@ -44,3 +44,40 @@ def golden_scores(g, c):
 
 def golden_mask(g, c):
     return O.unpack_mask(g["mask_bits"], c.E)
+
+
+# -- topk / dynk rules --------------------------------------------------------------
+def gate_fixture_items():
+    """(case, rule, parameter, upstream mask [N,E] bool, upstream scores in the case dtype)
+    for every mask of tests/golden/gates.npz."""
+    gz = np.load(GOLDEN / "gates.npz")
+    by_name = {c.name: c for c in all_cases()}
+    out = []
+    for key in gz.files:
+        name, rule, par = key.split("/")
+        c = by_name[name]
+        out.append((c, rule, float(par) if rule == "dynk" else int(par), gz[key]))
+    return out
+
+
+def gate_fixture_ids():
+    return [k for k in np.load(GOLDEN / "gates.npz").files]
+
+
+def rule_tie_tokens(scores, rule, par, window):
+    """Tokens whose decision sits inside the tie window: top-k with the k-th and (k+1)-th
+    largest scores closer than window*max, or a cumulative share within `window` of tau."""
+    s = scores.double()
+    if rule == "topk":
+        if par >= s.shape[-1]:
+            return torch.zeros(s.shape[0], dtype=torch.bool)
+        srt = torch.sort(s, dim=-1, descending=True).values
+        return (srt[:, par - 1] - srt[:, par]).abs() <= window * srt[:, 0].abs()
+    sh = s / s.sum(-1, keepdim=True)
+    cum = torch.cumsum(torch.sort(sh, dim=-1, descending=True).values, dim=-1)
+    near = (cum - par).abs() <= window
+    ties = torch.zeros_like(near)
+    srt = torch.sort(sh, dim=-1, descending=True).values
+    ties[:, 1:] = (srt[:, 1:] - srt[:, :-1]).abs() <= window * srt[:, :1]
+    # an equal pair matters only where the threshold falls between its members
+    return near.any(-1) | (ties & near.roll(1, -1)).any(-1)

@@ -3,7 +3,8 @@ import numpy as np
 import pytest
 import torch
 
-from helpers import C, O, TOL, WINDOW, all_cases, case_ids, golden_mask, golden_scores, load_golden
+from helpers import (C, O, TOL, WINDOW, all_cases, case_ids, gate_fixture_ids, gate_fixture_items,
+                     golden_mask, golden_scores, load_golden, rule_tie_tokens)
 
 pytestmark = pytest.mark.gpu
 
@@ -34,6 +35,29 @@ def test_mask_from_upstream_scores_bit_exact(c):
     wsp = ops.Workspace.allocate(c.N, c.E, "cuda")
     ops.mask_from_scores(dev(golden_scores(g, c)), c.tau, wsp)
     assert np.array_equal(bits_of(wsp, c.N), g["mask_bits"])      # zero exclusions
+    wsp.check_status()
+
+
+@pytest.mark.parametrize("item", gate_fixture_items(), ids=gate_fixture_ids())
+def test_topk_and_dynk_rules(item):
+    """The top-k and cumulative-share rules on the upstream scores against the routing tensor
+    the upstream gate returned: every token outside the tie window must agree exactly."""
+    from d2dmoe_b200 import ops
+    c, rule, par, bits = item
+    g, _ = load_golden(c)
+    s = golden_scores(g, c).reshape(c.N, c.E)
+    wsp = ops.Workspace.allocate(c.N, c.E, "cuda")
+    if rule == "topk":
+        ops.mask_rule_from_scores(dev(s), "topk", wsp, k=par)
+    else:
+        ops.mask_rule_from_scores(dev(s), "dynk", wsp, tau=par)
+    m = O.unpack_mask(bits_of(wsp, c.N), c.E)
+    ref = O.unpack_mask(bits, c.E)
+    bad = (m != ref).any(-1)
+    tie = rule_tie_tokens(s, rule, par, WINDOW[c.dtype])
+    assert (bad & ~tie).sum().item() == 0, f"{int(bad.sum())} tokens differ, {int(tie.sum())} in window"
+    if c.dtype == "bf16":
+        assert bad.sum().item() == 0         # bf16 sums are exact in fp32: no order effects
     wsp.check_status()
 
 

@@ -3,7 +3,8 @@ import numpy as np
 import pytest
 import torch
 
-from helpers import O, TOL, WINDOW, all_cases, case_ids, golden_mask, golden_scores, load_golden
+from helpers import (O, TOL, WINDOW, all_cases, case_ids, gate_fixture_ids, gate_fixture_items,
+                     golden_mask, golden_scores, load_golden)
 
 
 @pytest.mark.parametrize("c", all_cases(), ids=case_ids())
@@ -75,3 +76,14 @@ def test_gate_edge_cases():
     assert m[2].tolist() == [True, False, False]
     assert not m[1, 1]
     assert O.dynk_max_mask(s[2:], 1.0).all()
+
+
+@pytest.mark.parametrize("item", gate_fixture_items(), ids=gate_fixture_ids())
+def test_topk_and_dynk_rules_match_upstream_gate(item):
+    """The oracle's restatement of the 'topk' and cumulative 'dynk' gates against what the
+    upstream MoeficationMoE.gate returned for the same scores (tests/golden/gates.npz)."""
+    c, rule, par, bits = item
+    g, _ = load_golden(c)
+    s = golden_scores(g, c).reshape(c.N, c.E)
+    m = O.gate_topk(s, par) if rule == "topk" else O.gate_dynk_cumulative(s, par)
+    assert torch.equal(m, O.unpack_mask(bits, c.E))
