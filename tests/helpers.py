@@ -64,20 +64,24 @@ def gate_fixture_ids():
     return [k for k in np.load(GOLDEN / "gates.npz").files]
 
 
-def rule_tie_tokens(scores, rule, par, window):
-    """Tokens whose decision sits inside the tie window: top-k with the k-th and (k+1)-th
-    largest scores closer than window*max, or a cumulative share within `window` of tau."""
-    s = scores.double()
+def rule_tie_tokens(scores, rule, par, window, ref_mask):
+    """Tokens whose decision sits inside the tie window.  top-k: the k-th and (k+1)-th largest
+    scores closer than window*max.  dynk: a cumulative share within `window` of tau, or the
+    boundary of the upstream selection falling inside a group of (nearly) equal shares —
+    which member of such a group is taken depends on the order an unstable sort leaves."""
+    E = scores.shape[-1]
     if rule == "topk":
-        if par >= s.shape[-1]:
-            return torch.zeros(s.shape[0], dtype=torch.bool)
-        srt = torch.sort(s, dim=-1, descending=True).values
+        if par >= E:
+            return torch.zeros(scores.shape[0], dtype=torch.bool)
+        srt = torch.sort(scores.double(), dim=-1, descending=True).values
         return (srt[:, par - 1] - srt[:, par]).abs() <= window * srt[:, 0].abs()
-    sh = s / s.sum(-1, keepdim=True)
-    cum = torch.cumsum(torch.sort(sh, dim=-1, descending=True).values, dim=-1)
-    near = (cum - par).abs() <= window
-    ties = torch.zeros_like(near)
+    sh = (scores / scores.sum(-1, keepdim=True)).double()       # shares in the tensor dtype
     srt = torch.sort(sh, dim=-1, descending=True).values
-    ties[:, 1:] = (srt[:, 1:] - srt[:, :-1]).abs() <= window * srt[:, :1]
-    # an equal pair matters only where the threshold falls between its members
-    return near.any(-1) | (ties & near.roll(1, -1)).any(-1)
+    # bf16 shares add up exactly in fp32, so only fp32 tensors have a summation-order window
+    near = ((torch.cumsum(srt, dim=-1) - par).abs() <= window).any(-1)
+    if scores.dtype == torch.bfloat16:
+        near = torch.zeros_like(near)
+    n = ref_mask.sum(-1).clamp(max=E - 1)                        # first rank left out upstream
+    idx = torch.arange(scores.shape[0])
+    group = (srt[idx, n - 1] - srt[idx, n]).abs() <= window * srt[:, 0]
+    return near | (group & (ref_mask.sum(-1) < E))
