@@ -623,49 +623,35 @@ __device__ void role_mma2(const Params& p, Ctl* c, uint32_t ringB2, uint32_t hs,
   }
 }
 
-// 16 hidden columns of epilogue 1: accumulator -> bias/activation (x up-projection) with
-// the upstream rounding points -> bf16 -> two 16-byte pieces of the swizzled hidden tile
-template <int MODE, int ACT>
-__device__ __forceinline__ void ep1_block(const Params& p, const uint32_t* v, const uint32_t* u,
-                                          const float* bv, uint32_t* w) {
+// Router form, 16 hidden columns of epilogue 1: relu(T(x Wa^T)) as 8 packed bf16 pairs
+__device__ __forceinline__ void ep1_router_pairs(const uint32_t* v, uint32_t* w) {
 #pragma unroll
   for (int q = 0; q < 8; ++q) {
-    float h0 = bfr(__uint_as_float(v[2 * q])), h1 = bfr(__uint_as_float(v[2 * q + 1]));
-    if (MODE == MODE_ROUTER) {
-      h0 = fmaxf(h0, 0.f);
-      h1 = fmaxf(h1, 0.f);
-    } else {
-      h0 = bfr(activate(bfr(h0 + bv[2 * q]), ACT));
-      h1 = bfr(activate(bfr(h1 + bv[2 * q + 1]), ACT));
-      if (p.glu) {
-        h0 = bfr(h0 * bfr(__uint_as_float(u[2 * q])));
-        h1 = bfr(h1 * bfr(__uint_as_float(u[2 * q + 1])));
-      }
-    }
-    w[q] = pack_bf16x2(h0, h1);
+    __nv_bfloat162 h =
+        __floats2bfloat162_rn(__uint_as_float(v[2 * q]), __uint_as_float(v[2 * q + 1]));
+    h = __hmax2(h, __float2bfloat162_rn(0.f));
+    w[q] = *reinterpret_cast<uint32_t*>(&h);
   }
 }
 
-// Epilogue warps: 8 warps in two groups.  Warp w reads TMEM lanes 32*(w%4)..+31 (= tile
-// rows); group w/4 takes every other 16-column block of epilogue 1 and every other
-// chunk of epilogue 2 (chunk c lives in accumulator buffer c & 1 = its group).
-template <int MODE>
-__device__ void role_epilogue(const Params& p, Ctl* c, uint32_t hs, uint32_t stg, uint32_t tmem,
-                              int et) {
+// Router form, epilogue warps: 8 warps in two groups.  Warp w reads TMEM lanes
+// 32*(w%4)..+31 (= tile rows); group w/4 takes every other 16-column block of epilogue 1;
+// group 0 then turns the scores into mask words and counts.
+__device__ void role_epilogue_router(const Params& p, Ctl* c, uint32_t hs, uint32_t stg,
+                                     uint32_t tmem, int et) {
+  constexpr int MODE = MODE_ROUTER;
   volatile int* af = &c->abort_flag;
   const Geo& g = p.g;
   const int lane = et & 31, w8 = et >> 5, grp = w8 >> 2;
   const int r = et & 127;                                   // tile row = TMEM lane
-  const uint32_t stg_w = stg + w8 * 4096;                   // 32 rows x 128 B of staging
   const uint32_t lane_base = (uint32_t)(r & ~31) << 16;
   const uint32_t hs_row = hs + (r >> 3) * 1024 + (r & 7) * 128;
   const bool la = lookahead(g);
-  uint32_t i = 0, ph_mine = 0, ph_stg = 0;
-  // Router without residual: every token's initial output is the same row (last_bias or
+  uint32_t i = 0, ph_mine = 0;
+  // Without residual: every token's initial output is the same row (last_bias or
   // zeros).  Keep that row in shared memory and let the TMA engine write it once per
   // token, instead of spending the epilogue warps' store bandwidth on it.
-  const bool tma_init = MODE == MODE_ROUTER && p.out_init && !p.add_residual &&
-                        p.d * 2 <= SLOT;
+  const bool tma_init = p.out_init && !p.add_residual && p.d * 2 <= SLOT;
   if (tma_init) {
     for (int c8 = et; c8 < (p.d >> 3); c8 += 256) {
       uint4 bz = make_uint4(0u, 0u, 0u, 0u);
@@ -683,7 +669,7 @@ __device__ void role_epilogue(const Params& p, Ctl* c, uint32_t hs, uint32_t stg
           bulk_s2g(p.out_init + ((long long)t.r0 + row) * p.d, stg, (uint32_t)p.d * 2);
         bulk_commit();
       }
-    } else if (MODE == MODE_ROUTER && p.out_init) {
+    } else if (p.out_init) {
       // initial value of the layer output for this tile's tokens: last_bias (+ x).
       // Lane = one 16-byte column piece (kept in a register), rows of this warp inside.
       const int v8 = p.d >> 3;
@@ -711,45 +697,20 @@ __device__ void role_epilogue(const Params& p, Ctl* c, uint32_t hs, uint32_t stg
       }
     }
     // ---- epilogue 1: acc1 -> bf16 hidden tile in shared memory ------------------
-    if (MODE == MODE_EXPERTS) {
-      // stage this expert's bias in shared memory while GEMM1 is still running
-      const float* bias =
-          reinterpret_cast<const float*>(p.packed + (long long)t.e * g.stride + g.bias_off);
-      if (et < g.nsubw) c->bias_s[et] = __ldg(bias + et);
-      asm volatile("bar.sync 2, 256;" ::: "memory");
-    }
     const uint32_t b1 = la ? (i & 1) : 0;
     const uint32_t acc1 = tmem + lane_base + (la ? b1 * 128 : 0);
-    if (!mbar_wait(smem_u32(&c->acc1_full[b1]), la ? ((i >> 1) & 1) : (i & 1), af, p.dev_status))
+    if (!mbar_wait_fast(smem_u32(&c->acc1_full[b1]), la ? ((i >> 1) & 1) : (i & 1), af,
+                        p.dev_status))
       return;
     if (!mbar_wait_fast(smem_u32(&c->hs_empty), (i & 1) ^ 1, af, p.dev_status)) return;
     tc_fence_after();
     const int nblk = g.nsubw >> 4;
-    const int nsub1 = (MODE == MODE_ROUTER) ? g.nsub : 1;
-    for (int bi = grp; bi < nsub1 * nblk; bi += 2) {
+    for (int bi = grp; bi < g.nsub * nblk; bi += 2) {
       const int sub = bi / nblk, c0 = (bi - sub * nblk) << 4;
-      uint32_t v[16], u[16], w[8];
-      float bv[16];
+      uint32_t v[16], w[8];
       tmem_ld16(acc1 + sub * 128 + c0, v);
-      if (MODE == MODE_EXPERTS && p.glu) tmem_ld16(acc1 + 128 + c0, u);
-      if (MODE == MODE_EXPERTS) {
-#pragma unroll
-        for (int q = 0; q < 4; ++q)
-          *reinterpret_cast<float4*>(&bv[4 * q]) =
-              *(reinterpret_cast<const float4*>(&c->bias_s[c0]) + q);
-      }
       tmem_wait_ld();
-      if (MODE == MODE_ROUTER) {
-        ep1_block<MODE, D2D_RELU>(p, v, u, bv, w);
-      } else {
-        switch (p.act) {      // uniform branch around the element loop
-          case D2D_RELU: ep1_block<MODE, D2D_RELU>(p, v, u, bv, w); break;
-          case D2D_GELU: ep1_block<MODE, D2D_GELU>(p, v, u, bv, w); break;
-          case D2D_TANH: ep1_block<MODE, D2D_TANH>(p, v, u, bv, w); break;
-          case D2D_LEAKY_RELU: ep1_block<MODE, D2D_LEAKY_RELU>(p, v, u, bv, w); break;
-          default: ep1_block<MODE, D2D_GELU_TANH>(p, v, u, bv, w); break;
-        }
-      }
+      ep1_router_pairs(v, w);
       const int hc = sub * g.nsubw + c0;          // hidden column of v[0]
       const uint32_t base = hs_row + (hc >> 6) * SLOT;
       const int j0 = (hc & 63) >> 3;
@@ -760,44 +721,9 @@ __device__ void role_epilogue(const Params& p, Ctl* c, uint32_t hs, uint32_t stg
     mbar_arrive(smem_u32(&c->acc1_empty[b1]));     // acc1 buffer read completely
     fence_proxy_async();     // ordinary shared stores -> visible to the MMA's async reads
     mbar_arrive(smem_u32(&c->hs_full));
-    // ---- epilogue 2 -------------------------------------------------------------
-    if (MODE == MODE_EXPERTS) {
-      // accumulator -> bf16 -> this warp's 32 x 128-byte staging block; the writer warp of
-      // the same row quarter adds it to the output rows, so this warp never waits on the
-      // global write path
-      const uint32_t bar_full = smem_u32(&c->sfull[grp][w8 & 3]);
-      const uint32_t bar_empty = smem_u32(&c->sempty[grp][w8 & 3]);
-      for (int nci = grp; nci < g.nc; nci += 2) {
-        if (!mbar_wait_fast(smem_u32(&c->acc2_full[grp]), ph_mine, af, p.dev_status)) return;
-        ph_mine ^= 1;
-        tc_fence_after();
-        const int halves = g.nd >> 6;
-        for (int hf = 0; hf < halves; ++hf) {
-          uint32_t v[64];
-          tmem_ld32(tmem + lane_base + 256 + grp * 128 + hf * 64, v);
-          tmem_ld32(tmem + lane_base + 256 + grp * 128 + hf * 64 + 32, v + 32);
-          tmem_wait_ld();
-          if (hf == halves - 1) {     // accumulator buffer read completely: hand it back
-            tc_fence_before();
-            mbar_arrive(smem_u32(&c->acc2_empty[grp]));
-          }
-          if (!mbar_wait_fast(bar_empty, ph_stg ^ 1, af, p.dev_status)) return;
-          // bf16 -> this warp's staging rows (piece XOR row: conflict-free 16-byte stores)
-#pragma unroll
-          for (int pc = 0; pc < 8; ++pc) {
-            uint32_t ww[4];
-#pragma unroll
-            for (int q = 0; q < 4; ++q)
-              ww[q] = pack_bf16x2(__uint_as_float(v[8 * pc + 2 * q]),
-                                  __uint_as_float(v[8 * pc + 2 * q + 1]));
-            st_shared_v4(stg_w + lane * 128 + ((pc ^ (lane & 7)) << 4), ww[0], ww[1], ww[2], ww[3]);
-          }
-          mbar_arrive(bar_full);
-          ph_stg ^= 1;
-        }
-      }
-    } else if (grp == 0) {
-      if (!mbar_wait(smem_u32(&c->acc2_full[0]), ph_mine, af, p.dev_status)) return;
+    // ---- scores -> mask words, counts ---------------------------------------------
+    if (grp == 0) {
+      if (!mbar_wait_fast(smem_u32(&c->acc2_full[0]), ph_mine, af, p.dev_status)) return;
       ph_mine ^= 1;
       tc_fence_after();
       const int E = p.E;
@@ -1160,7 +1086,7 @@ mlp_tiles_kernel(const Params p) {
   } else if (MODE == MODE_EXPERTS && warp < 8) {
     role_ep2_experts(p, c, stg, tmem, tid - 128);
   } else if (warp < 8) {
-    role_epilogue<MODE_ROUTER>(p, c, hs, stg, tmem, tid);
+    role_epilogue_router(p, c, hs, stg, tmem, tid);
     bulk_wait_all();       // TMA row stores read shared memory: finish before the CTA ends
   } else if (warp == WARP_MMA1) {
     if (elect_one()) role_mma1<MODE>(p, c, ringA, ringB, tmem);
