@@ -247,6 +247,46 @@ def test_other_forward_modes_match_oracle():
         assert O.rel_err(out.reshape(c.N, c.d).cpu(), ex) <= TOL["fp32"]
 
 
+def test_fused_forward_in_a_cuda_graph():
+    """The one-call layer issues no host synchronisation and allocates nothing, so it can be
+    captured in a CUDA graph; a replay on new input contents must give the new result."""
+    from d2dmoe_b200 import ops
+    c = C.LayerCase("graph", 4, 197, 256, 64, 16, tau=0.2, dtype="bf16")
+    t = C.make_tensors(c)
+    x = dev(t["x"].reshape(c.N, c.d))
+    w1, b1, w2 = dev(t["w1"]), dev(t["b1"]), dev(t["w2"])
+    wa, wb, lb = dev(t["wa"]), dev(t["wb"]), dev(t["last_bias"].reshape(-1))
+    rp, ep = ops.prepack_router(wa, wb), ops.prepack_experts(w1, b1, w2)
+    wsp = ops.Workspace.allocate(c.N, c.E, "cuda")
+    out = torch.empty_like(x)
+
+    def call():
+        ops.moe_forward(x, wa, wb, c.tau, w1, b1, w2, c.act, out, wsp, last_bias=lb,
+                        router_packed=rp, experts_packed=ep)
+    call()
+    torch.cuda.synchronize()
+    ref1 = out.clone()
+    side = torch.cuda.Stream()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.stream(side):
+        call()                                         # warm-up on the capture stream
+        side.synchronize()
+        with torch.cuda.graph(graph, stream=side):
+            call()
+    x2 = torch.roll(x, 7, 0).contiguous()
+    x.copy_(x2)
+    out.fill_(float("nan"))
+    graph.replay()
+    torch.cuda.synchronize()
+    got2 = out.clone()
+    call()                                             # same input, eager
+    torch.cuda.synchronize()
+    wsp.check_status()
+    assert torch.isfinite(got2.float()).all()
+    assert O.rel_err(got2.float().cpu(), out.float().cpu()) <= TOL["bf16"]
+    assert O.rel_err(torch.roll(ref1, 7, 0).float().cpu(), got2.float().cpu()) <= TOL["bf16"]
+
+
 def test_empty_and_error_paths():
     from d2dmoe_b200 import ops, _capi
     import d2dmoe_b200 as D
