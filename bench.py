@@ -323,6 +323,8 @@ def run_ours(args):
     sampler = ClockSampler(local) if rank == 0 else None
     ms = timed(lambda: step(1.0 - HEADLINE_TAU), steps, warmup, dist)
     value = world * tokens_step * steps / (ms * 1e-3)
+    from d2dmoe_b200 import _capi
+    launches_per_call = int(_capi.lib.d2d_last_forward_launches())   # as the library counted
     if args.quick:
         clocks = sampler.stop() if sampler else None
         if dist is not None:
@@ -440,7 +442,9 @@ def run_ours(args):
         "tau_sweep": sweep, "roofline": roof,
         "e2e": {"value": e2e_val, "unit": "tokens/s", "h2d_bytes_per_step": bytes_x,
                 "d2h_bytes_per_step": bytes_x, "api": "MoeficationMoE.forward_host (pinned host x -> pinned host out, 4 slices per layer, layers pipelined)"},
-        "gpu_launches": steps * LAYERS * 3,     # router+mask, compaction scatter, expert FFN
+        # kernels per layer call as the library counted them for the last call: router+mask
+        # (+ token lists), [compaction scatter], expert FFN
+        "gpu_launches": steps * LAYERS * launches_per_call,
         "clocks": clocks, "check": check,
     }
     if cpu is not None:

@@ -13,6 +13,9 @@ inline bool dtype_ok(int dt) { return dt == D2D_F32 || dt == D2D_BF16; }
 
 inline size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
 
+// kernels issued by the calling thread's last d2d_moe_forward
+thread_local int g_last_forward_launches = 0;
+
 }  // namespace
 
 extern "C" {
@@ -143,8 +146,9 @@ int d2d_moe_forward(const void* x, const void* wa, const void* wb, const void* r
                     void* out, uint32_t* mask_bits, int32_t* token_idx, int32_t* offsets,
                     int64_t N, int d, int R, int E, int H, int act, int dtype, void* ws,
                     size_t ws_bytes, int* dev_status, d2d_stream_t stream) {
-  int rc;
+  int rc, nl = 0;
   bool counts_ready = false;
+  g_last_forward_launches = 0;
   if (!wa && !scores_in_opt) return D2D_ERR_BAD_ARG;
   if (!mask_bits || !token_idx || !offsets || !ws || !aligned(ws, 16)) return D2D_ERR_BAD_ARG;
   if (ws_bytes < compact_workspace_bytes(N, E)) return D2D_ERR_WORKSPACE;
@@ -158,11 +162,13 @@ int d2d_moe_forward(const void* x, const void* wa, const void* wb, const void* r
              : D2D_ERR_UNSUPPORTED;
     if (rc == D2D_OK) {
       counts_ready = true;
+      nl += 1;
     } else if (rc == D2D_ERR_UNSUPPORTED) {
       rc = d2d_mask_from_scores(scores_in_opt, thresh_mult, mask_bits, N, E, dtype, dev_status,
                                 stream);
       if (rc != D2D_OK) return rc;
       rc = d2d_init_out(x, last_bias_opt, add_residual, out, N, d, dtype, stream);
+      nl += 2;
     }
   } else if (router_packed_opt && x && wb && dtype_ok(dtype) && d >= 1 && R >= 1 && E >= 1 &&
              umma_router_supported(d, R, E, dtype)) {
@@ -171,18 +177,24 @@ int d2d_moe_forward(const void* x, const void* wa, const void* wb, const void* r
                                  last_bias_opt, add_residual, out, (int32_t*)ws, N, d, R, E,
                                  dev_status, (cudaStream_t)stream);
     counts_ready = true;
+    nl += 1;
   } else {
     rc = d2d_router_mask(x, wa, wb, router_packed_opt, thresh_mult, mask_bits, nullptr,
                          last_bias_opt, add_residual, out, N, d, R, E, dtype, dev_status, stream);
+    nl += 1;
   }
   if (rc != D2D_OK) return rc;
   rc = launch_compact(mask_bits, token_idx, offsets, N, E, (int32_t*)ws, dev_status,
                       (cudaStream_t)stream, counts_ready);
   if (rc != D2D_OK) return rc;
+  nl += counts_ready ? 1 : 2;
+  g_last_forward_launches = nl + 1;
   return d2d_experts_ffn(x, token_idx, offsets, w1, b1_opt, w_up_opt, w2, experts_packed_opt,
                          nullptr, 0, /*accumulate=*/1, out, N, d, E, H, act, dtype, dev_status,
                          stream);
 }
+
+int d2d_last_forward_launches(void) { return g_last_forward_launches; }
 
 int d2d_prepack_experts_bytes(int d, int E, int H, int glu, int dtype, size_t* bytes) {
   if (!bytes || d < 1 || E < 1 || H < 1) return D2D_ERR_BAD_ARG;

@@ -187,6 +187,10 @@ int d2d_moe_forward(const void* x, const void* wa, const void* wb, const void* r
  * parameters in place (architectures/moe/moe_impls.py:137-146,276-284); here the
  * module owns a packed copy and refreshes it when the parameters change.
  * *_bytes returns 0 bytes when the shape has no tensor-core path. */
+/* Number of kernels the calling thread's last d2d_moe_forward issued (3 on the tensor-core
+ * path: router + rule, compaction scatter, expert FFN; more on the general-shape paths).  Introspection for benchmarks; no upstream counterpart. */
+int d2d_last_forward_launches(void);
+
 int d2d_prepack_experts_bytes(int d, int E, int H, int glu, int dtype, size_t* bytes /* host */);
 int d2d_prepack_experts(const void* w1, const void* b1_opt, const void* w_up_opt, const void* w2,
                         void* packed, int d, int E, int H, int dtype, d2d_stream_t stream);

@@ -166,6 +166,10 @@ def test_fused_forward_writes_every_row(c):
         o = out.cpu().float()
         assert torch.isfinite(o).all()
         assert O.rel_err(o, _exact(c, t, m)) <= TOL[c.dtype]
+        # the token lists the call leaves behind are the compaction of that mask
+        off_ref, idx_ref = O.expert_token_lists(m)
+        off, idx = lists_of(wsp, c.E)
+        assert np.array_equal(off, np.asarray(off_ref)) and np.array_equal(idx, np.asarray(idx_ref))
 
 
 @pytest.mark.parametrize("c", all_cases(), ids=case_ids())
