@@ -157,19 +157,29 @@ class LayerState:
         ev[3].record()
 
 
-def timed(fn, steps, warmup, dist=None):
+def timed(fn, steps, warmup, dist=None, quantiles=None):
+    """Device time of `steps` back-to-back calls of fn (CUDA events on the launching stream,
+    max over ranks).  With `quantiles` (a dict) an event is also recorded after every step and
+    the 2.5 / 50 / 97.5 % quantiles of the per-step times are stored in it."""
     for _ in range(warmup):
         fn()
     if dist is not None:
         dist.barrier()
     torch.cuda.synchronize()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e0.record()
-    for _ in range(steps):
+    ev = [torch.cuda.Event(enable_timing=True) for _ in range(steps + 1 if quantiles is not None else 2)]
+    ev[0].record()
+    for i in range(steps):
         fn()
-    e1.record()
+        if quantiles is not None:
+            ev[i + 1].record()
+    if quantiles is None:
+        ev[1].record()
     torch.cuda.synchronize()
-    ms = e0.elapsed_time(e1)
+    ms = ev[0].elapsed_time(ev[-1])
+    if quantiles is not None and steps >= 2:
+        per = sorted(ev[i].elapsed_time(ev[i + 1]) for i in range(steps))
+        q = lambda f: per[min(steps - 1, max(0, int(round(f * (steps - 1)))))]      # noqa: E731
+        quantiles.update({"p2.5": q(0.025), "p50": q(0.5), "p97.5": q(0.975)})
     if dist is not None:
         t = torch.tensor([ms], device="cuda")
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
@@ -321,7 +331,8 @@ def run_ours(args):
 
     # ---- headline: tau_cfg 0.9, device-resident ---------------------------------
     sampler = ClockSampler(local) if rank == 0 else None
-    ms = timed(lambda: step(1.0 - HEADLINE_TAU), steps, warmup, dist)
+    step_q = {}
+    ms = timed(lambda: step(1.0 - HEADLINE_TAU), steps, warmup, dist, quantiles=step_q)
     value = world * tokens_step * steps / (ms * 1e-3)
     from d2dmoe_b200 import _capi
     launches_per_call = int(_capi.lib.d2d_last_forward_launches())   # as the library counted
@@ -438,6 +449,7 @@ def run_ours(args):
         "n_gpus": world, "steps": steps, "warmup": warmup, "ms_per_step": ms / steps,
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
         "data": "synthetic", "config": workload_config(world),
+        "ms_per_step_quantiles": step_q,
         "mean_k": head["mean_k"], "roofline_frac_layer_path": head["roofline_frac"],
         "tau_sweep": sweep, "roofline": roof,
         "e2e": {"value": e2e_val, "unit": "tokens/s", "h2d_bytes_per_step": bytes_x,
