@@ -291,6 +291,39 @@ def test_fused_forward_in_a_cuda_graph():
     assert O.rel_err(torch.roll(ref1, 7, 0).float().cpu(), got2.float().cpu()) <= TOL["bf16"]
 
 
+def test_fused_forward_on_two_streams():
+    """Two layers issued alternately on two streams (each with its own workspace and output)
+    give what they give one after the other: kernels wait only for their own stream's
+    predecessor."""
+    from d2dmoe_b200 import ops
+    c = C.LayerCase("streams", 8, 197, 256, 64, 16, tau=0.3, dtype="bf16")
+    t = C.make_tensors(c)
+    w1, b1, w2 = dev(t["w1"]), dev(t["b1"]), dev(t["w2"])
+    wa, wb, lb = dev(t["wa"]), dev(t["wb"]), dev(t["last_bias"].reshape(-1))
+    rp, ep = ops.prepack_router(wa, wb), ops.prepack_experts(w1, b1, w2)
+    xs = [dev(t["x"].reshape(c.N, c.d)), dev(torch.roll(t["x"].reshape(c.N, c.d), 5, 0))]
+    wsp = [ops.Workspace.allocate(c.N, c.E, "cuda") for _ in range(2)]
+    outs = [torch.empty_like(xs[0]) for _ in range(2)]
+    ref = []
+    for i in range(2):
+        ops.moe_forward(xs[i], wa, wb, c.tau, w1, b1, w2, c.act, outs[i], wsp[i], last_bias=lb,
+                        router_packed=rp, experts_packed=ep)
+        torch.cuda.synchronize()
+        ref.append(outs[i].clone())
+        outs[i].fill_(float("nan"))
+    streams = [torch.cuda.Stream(), torch.cuda.Stream()]
+    torch.cuda.synchronize()
+    for rep in range(6):
+        for i in range(2):
+            with torch.cuda.stream(streams[i]):
+                ops.moe_forward(xs[i], wa, wb, c.tau, w1, b1, w2, c.act, outs[i], wsp[i],
+                                last_bias=lb, router_packed=rp, experts_packed=ep)
+    torch.cuda.synchronize()
+    for i in range(2):
+        wsp[i].check_status()
+        assert O.rel_err(outs[i].float().cpu(), ref[i].float().cpu()) <= TOL["bf16"]
+
+
 def test_empty_and_error_paths():
     from d2dmoe_b200 import ops, _capi
     import d2dmoe_b200 as D
