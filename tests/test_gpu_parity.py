@@ -291,6 +291,24 @@ def test_fused_forward_in_a_cuda_graph():
     assert O.rel_err(torch.roll(ref1, 7, 0).float().cpu(), got2.float().cpu()) <= TOL["bf16"]
 
 
+@pytest.mark.parametrize("n", [4700, 4800])
+def test_general_shape_router_mid_sizes(n):
+    """fp32 router + rule of the general-shape kernel at a few thousand tokens with a narrow
+    router (d=96, R=64): scores against the oracle, mask exactly the rule on those scores."""
+    from d2dmoe_b200 import ops
+    c = C.LayerCase("tiles", 1, n, 96, 32, 24, R=64, tau=0.2)
+    t = C.make_tensors(c)
+    x2d = dev(t["x"].reshape(c.N, c.d))
+    wsp = ops.Workspace.allocate(c.N, c.E, "cuda")
+    scores = torch.empty(c.N, c.E, dtype=torch.float32, device="cuda")
+    ops.router_mask(x2d, dev(t["wa"]), dev(t["wb"]), c.tau, wsp, scores_out=scores)
+    s_ref = O.router_scores(t["x"].reshape(c.N, c.d), t["wa"], t["wb"])
+    assert O.rel_err(scores.cpu(), s_ref) <= 1e-5
+    m = O.unpack_mask(bits_of(wsp, c.N), c.E)
+    assert torch.equal(m, O.dynk_max_mask(scores.cpu(), c.tau))
+    wsp.check_status()
+
+
 def test_fused_forward_on_two_streams():
     """Two layers issued alternately on two streams (each with its own workspace and output)
     give what they give one after the other: kernels wait only for their own stream's
