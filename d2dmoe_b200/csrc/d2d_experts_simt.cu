@@ -84,25 +84,33 @@ experts_simt_kernel(const T* __restrict__ x, const int32_t* __restrict__ token_i
       for (int i = 0; i < 4; ++i)
 #pragma unroll
         for (int j = 0; j < 4; ++j) { acc[i][j] = 0.f; accu[i][j] = 0.f; }
+      // Vector path: the vectors of k-chunk kc+1 are loaded into registers before the
+      // products of chunk kc start, so the load latency hides behind the arithmetic.
+      const int xr = tid >> 3, xk = (tid & 7) << 2;          // x tile: row, k offset
+      const int wk = tid >> 5, wc = (tid & 31) << 2;         // weight tile: k row (+8 per pass), column
+      float4 px = z4, pw[4], pu[4];
+      auto prefetch1 = [&](int kc) {
+        const int t = rows[xr];
+        px = (t >= 0 && kc + xk < d) ? load4(x + (int64_t)t * d + kc + xk) : z4;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const int k = wk + 8 * j;
+          const bool ok = (kc + k < d) && (hc + wc < H);
+          pw[j] = ok ? load4(w1e + (int64_t)(kc + k) * H + hc + wc) : z4;
+          if (GLU) pu[j] = ok ? load4(wue + (int64_t)(kc + k) * H + hc + wc) : z4;
+        }
+      };
+      if (vec) prefetch1(0);
       for (int kc = 0; kc < d; kc += KC) {
         __syncthreads();
         if (vec) {
-          {
-            const int r = tid >> 3, k = (tid & 7) << 2;
-            const int t = rows[r];
-            *reinterpret_cast<float4*>(&xs[r * XP + k]) =
-                (t >= 0 && kc + k < d) ? load4(x + (int64_t)t * d + kc + k) : z4;
-          }
+          *reinterpret_cast<float4*>(&xs[xr * XP + xk]) = px;
 #pragma unroll
           for (int j = 0; j < 4; ++j) {
-            const int k = (tid >> 5) + 8 * j, c = (tid & 31) << 2;
-            const bool ok = (kc + k < d) && (hc + c < H);
-            *reinterpret_cast<float4*>(&ws[k * WP + c]) =
-                ok ? load4(w1e + (int64_t)(kc + k) * H + hc + c) : z4;
-            if (GLU)
-              *reinterpret_cast<float4*>(&wu[k * WP + c]) =
-                  ok ? load4(wue + (int64_t)(kc + k) * H + hc + c) : z4;
+            *reinterpret_cast<float4*>(&ws[(wk + 8 * j) * WP + wc]) = pw[j];
+            if (GLU) *reinterpret_cast<float4*>(&wu[(wk + 8 * j) * WP + wc]) = pu[j];
           }
+          if (kc + KC < d) prefetch1(kc + KC);
         } else {
           for (int i = tid; i < TM * KC; i += NT) {
             const int r = i / KC, k = i % KC;
@@ -168,15 +176,23 @@ experts_simt_kernel(const T* __restrict__ x, const int32_t* __restrict__ token_i
       for (int i = 0; i < 4; ++i)
 #pragma unroll
         for (int j = 0; j < 4; ++j) acc[i][j] = 0.f;
+      const int wk = tid >> 5, wc = (tid & 31) << 2;
+      float4 pw[4];
+      auto prefetch2 = [&](int kc) {
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const int k = wk + 8 * j;
+          pw[j] = (kc + k < H && dc + wc < d) ? load4(w2e + (int64_t)(kc + k) * d + dc + wc) : z4;
+        }
+      };
+      if (vec) prefetch2(0);
       for (int kc = 0; kc < H; kc += KC) {
         __syncthreads();
         if (vec) {
 #pragma unroll
-          for (int j = 0; j < 4; ++j) {
-            const int k = (tid >> 5) + 8 * j, c = (tid & 31) << 2;
-            *reinterpret_cast<float4*>(&ws[k * WP + c]) =
-                (kc + k < H && dc + c < d) ? load4(w2e + (int64_t)(kc + k) * d + dc + c) : z4;
-          }
+          for (int j = 0; j < 4; ++j)
+            *reinterpret_cast<float4*>(&ws[(wk + 8 * j) * WP + wc]) = pw[j];
+          if (kc + KC < H) prefetch2(kc + KC);
         } else {
           for (int i = tid; i < KC * CB; i += NT) {
             const int k = i / CB, c = i % CB;

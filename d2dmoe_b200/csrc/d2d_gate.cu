@@ -64,21 +64,30 @@ router_mask_simt_kernel(const T* __restrict__ x, const T* __restrict__ wa,
     for (int i = 0; i < 4; ++i)
 #pragma unroll
       for (int j = 0; j < 4; ++j) acc[i][j] = 0.f;
+    // Vector path: one 4-element vector per thread and pass (row = tid / 8 (+32 per pass),
+    // k = 4*(tid%8)).  The vectors of k-chunk kc+1 are loaded into registers before the
+    // products of chunk kc start, so the load latency hides behind the arithmetic.
+    const int vr = tid >> 3, vk = (tid & 7) << 2;
+    const float4 z = make_float4(0.f, 0.f, 0.f, 0.f);
+    float4 px = z, pw[RC / 32];
+    auto prefetch = [&](int kc) {
+      const int64_t t = t0 + vr;
+      px = (t < N && kc + vk < d) ? load4(x + t * d + kc + vk) : z;
+#pragma unroll
+      for (int j = 0; j < RC / 32; ++j) {
+        const int c = vr + 32 * j;
+        pw[j] = (rc + c < R && kc + vk < d) ? load4(wa + (int64_t)(rc + c) * d + kc + vk) : z;
+      }
+    };
+    if (vec) prefetch(0);
     for (int kc = 0; kc < d; kc += KC) {
       __syncthreads();
       if (vec) {
-        // one 4-element vector per thread and pass: row = tid / 8 (+32 per pass), k = 4*(tid%8)
-        const int r = tid >> 3, k = (tid & 7) << 2;
-        const int64_t t = t0 + r;
-        const float4 z = make_float4(0.f, 0.f, 0.f, 0.f);
-        *reinterpret_cast<float4*>(&xs[r * KP + k]) =
-            (t < N && kc + k < d) ? load4(x + t * d + kc + k) : z;
+        *reinterpret_cast<float4*>(&xs[vr * KP + vk]) = px;
 #pragma unroll
-        for (int j = 0; j < RC / 32; ++j) {
-          const int c = r + 32 * j;
-          *reinterpret_cast<float4*>(&wsm[c * KP + k]) =
-              (rc + c < R && kc + k < d) ? load4(wa + (int64_t)(rc + c) * d + kc + k) : z;
-        }
+        for (int j = 0; j < RC / 32; ++j)
+          *reinterpret_cast<float4*>(&wsm[(vr + 32 * j) * KP + vk]) = pw[j];
+        if (kc + KC < d) prefetch(kc + KC);
       } else {
         for (int i = tid; i < TM * KC; i += NT) {
           const int r = i / KC, k = i % KC;
