@@ -59,6 +59,32 @@ def test_topk_and_dynk_rules(item):
     wsp.check_status()
 
 
+@pytest.mark.parametrize("E", [24, 96, 130])
+def test_rule_kernel_equals_c_oracle_bf16(E):
+    """bf16 scores add up exactly in fp32 and both sides order equal values by index, so the
+    rule kernel and the C restatement must agree on every bit, ties included."""
+    import ctypes as CT
+    from d2dmoe_b200 import ops
+    from oracle.build_c import build
+    lib = CT.CDLL(str(build()))
+    N = 20000
+    g = torch.Generator().manual_seed(E)
+    s = torch.exp(1.5 * torch.randn(N, E, generator=g)).to(torch.bfloat16)
+    a = s.view(torch.int16).numpy().view(np.uint16)
+    nw = (E + 31) // 32
+    wsp = ops.Workspace.allocate(N, E, "cuda")
+    for rule, r, k, tau in (("topk", 1, 3, 0.0), ("dynk", 2, 0, 0.7)):
+        ref = np.zeros((N, nw), dtype=np.uint32)
+        lib.d2d_oracle_rule_bf16(a.ctypes.data_as(CT.c_void_p), r, k, CT.c_float(tau),
+                                 ref.ctypes.data_as(CT.c_void_p), CT.c_long(N), E)
+        if rule == "topk":
+            ops.mask_rule_from_scores(dev(s), "topk", wsp, k=k)
+        else:
+            ops.mask_rule_from_scores(dev(s), "dynk", wsp, tau=tau)
+        assert np.array_equal(bits_of(wsp, N), ref), rule
+    wsp.check_status()
+
+
 @pytest.mark.parametrize("c", all_cases(), ids=case_ids())
 def test_router_mask(c):
     from d2dmoe_b200 import ops
