@@ -53,7 +53,10 @@ int d2d_router_mask(const void* x, const void* wa, const void* wb, const void* r
   if (!dtype_ok(dtype)) return D2D_ERR_UNSUPPORTED;
   if (N == 0) return D2D_OK;
   cudaStream_t s = (cudaStream_t)stream;
-  if (router_packed_opt && umma_router_supported(d, R, E, dtype))
+  // the tensor-core router moves x, last_bias and the output's initial value in 16-byte
+  // pieces; buffers that do not allow that take the general-shape kernel
+  if (router_packed_opt && umma_router_supported(d, R, E, dtype) && aligned(x, 16) &&
+      aligned(last_bias_opt, 16) && aligned(out_init_opt, 16) && aligned(router_packed_opt, 1024))
     return launch_router_mask_umma(x, router_packed_opt, thresh_mult, mask_bits, scores_opt,
                                    last_bias_opt, add_residual, out_init_opt, nullptr, N, d, R, E,
                                    dev_status, s);
@@ -132,7 +135,8 @@ int d2d_experts_ffn(const void* x, const int32_t* token_idx, const int32_t* offs
     int rc = launch_init_out(x, last_bias_opt, add_residual, out, N, d, dtype, s);
     if (rc != D2D_OK) return rc;
   }
-  if (experts_packed_opt && umma_experts_supported(d, E, H, w_up_opt != nullptr, dtype))
+  if (experts_packed_opt && umma_experts_supported(d, E, H, w_up_opt != nullptr, dtype) &&
+      aligned(experts_packed_opt, 1024))
     return launch_experts_umma(x, token_idx, offsets, experts_packed_opt, out, N, d, E, H,
                                w_up_opt != nullptr, act, dev_status, s);
   return launch_experts_simt(x, token_idx, offsets, w1, b1_opt, w_up_opt, w2, out, N, d, E, H, act,
@@ -151,6 +155,12 @@ int d2d_moe_forward(const void* x, const void* wa, const void* wb, const void* r
   g_last_forward_launches = 0;
   if (!wa && !scores_in_opt) return D2D_ERR_BAD_ARG;
   if (!mask_bits || !token_idx || !offsets || !ws || !aligned(ws, 16)) return D2D_ERR_BAD_ARG;
+  // every argument check of the later stages comes before the first launch
+  if (!x || !w1 || !w2 || !out || N < 0 || d < 1 || E < 1 || H < 1) return D2D_ERR_BAD_ARG;
+  if (!aligned(out, 16) || !aligned(x, 16) || !aligned(mask_bits, 4) || !aligned(token_idx, 4) ||
+      !aligned(offsets, 4))
+    return D2D_ERR_BAD_ARG;
+  if (!dtype_ok(dtype) || act < D2D_RELU || act > D2D_GELU_TANH) return D2D_ERR_UNSUPPORTED;
   if (ws_bytes < compact_workspace_bytes(N, E)) return D2D_ERR_WORKSPACE;
   if (N == 0) return D2D_OK;
   if (scores_in_opt) {
@@ -170,8 +180,8 @@ int d2d_moe_forward(const void* x, const void* wa, const void* wb, const void* r
       rc = d2d_init_out(x, last_bias_opt, add_residual, out, N, d, dtype, stream);
       nl += 2;
     }
-  } else if (router_packed_opt && x && wb && dtype_ok(dtype) && d >= 1 && R >= 1 && E >= 1 &&
-             umma_router_supported(d, R, E, dtype)) {
+  } else if (router_packed_opt && wb && R >= 1 && umma_router_supported(d, R, E, dtype) &&
+             aligned(last_bias_opt, 16) && aligned(router_packed_opt, 1024)) {
     // the tensor-core router also fills the compaction's counts table
     rc = launch_router_mask_umma(x, router_packed_opt, thresh_mult, mask_bits, nullptr,
                                  last_bias_opt, add_residual, out, (int32_t*)ws, N, d, R, E,
@@ -187,7 +197,7 @@ int d2d_moe_forward(const void* x, const void* wa, const void* wb, const void* r
   rc = launch_compact(mask_bits, token_idx, offsets, N, E, (int32_t*)ws, dev_status,
                       (cudaStream_t)stream, counts_ready);
   if (rc != D2D_OK) return rc;
-  nl += counts_ready ? 1 : 2;
+  nl += counts_ready ? 2 : 3;      // [count,] scan, scatter
   g_last_forward_launches = nl + 1;
   return d2d_experts_ffn(x, token_idx, offsets, w1, b1_opt, w_up_opt, w2, experts_packed_opt,
                          nullptr, 0, /*accumulate=*/1, out, N, d, E, H, act, dtype, dev_status,
@@ -195,6 +205,11 @@ int d2d_moe_forward(const void* x, const void* wa, const void* wb, const void* r
 }
 
 int d2d_last_forward_launches(void) { return g_last_forward_launches; }
+
+int d2d_debug_configure(int wait_limit_log2, int withhold_weight_tile) {
+  umma_debug_configure(wait_limit_log2, withhold_weight_tile);
+  return D2D_OK;
+}
 
 int d2d_prepack_experts_bytes(int d, int E, int H, int glu, int dtype, size_t* bytes) {
   if (!bytes || d < 1 || E < 1 || H < 1) return D2D_ERR_BAD_ARG;

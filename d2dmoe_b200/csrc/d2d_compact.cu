@@ -5,11 +5,14 @@
 // The sort only serves to bring each expert's tokens to the front of its column;
 // a compaction gives the same set per expert, here in ascending token order.
 //
-// Two launches:
+// Three launches:
 //   count   : counts[tile][e] = tokens of the 128-token tile that keep expert e
 //             (skipped when the router kernel already wrote the table)
-//   scatter : one CTA per 256 tokens rebuilds its base from the counts table (sum over
-//             earlier tiles + exclusive scan over experts) and writes its token indices.
+//   scan    : per expert, exclusive prefix of the counts along the tiles, in place;
+//             the expert totals go to the extra row counts[ntiles][.]
+//   scatter : one CTA per 256 tokens reads the prefix row of its first tile and the
+//             totals row (E values each), scans the totals over the experts and
+//             writes its token indices.
 // Integer work, bit-exact by construction; HBM traffic is the mask (read twice)
 // plus 4 bytes per kept token-expert pair.
 #include "d2d_common.cuh"
@@ -18,12 +21,13 @@ namespace d2d {
 namespace {
 
 constexpr int NT = 256;
-constexpr int NTS = 1024;                // scatter CTA: 8 warps do the rows, all 32 sweep the table
+constexpr int NTS = 256;                 // scatter CTA: one warp per row of 32 tokens
 constexpr int ROWS = 8;                  // rows of 32 tokens per scatter CTA (one per warp)
 constexpr int CHUNK = ROWS * 32;
 constexpr int CTILE = 128;               // granularity of the counts table
 constexpr int TILES_PER_CHUNK = CHUNK / CTILE;
 constexpr int MAX_E = 256;
+constexpr int SCAN_NT = 1024;            // scan CTA: 32 experts x 32 segments of the tile range
 
 // one warp = one 128-token tile; lane b ends up with the count of expert 32j+b
 __global__ void __launch_bounds__(NT)
@@ -52,68 +56,84 @@ compact_count_kernel(const uint32_t* __restrict__ mask_bits, int32_t* __restrict
   }
 }
 
+// CTA b owns experts 32b..32b+31.  Thread (seg, el) first adds up the counts of expert
+// 32b+el over its segment of the tile range (a warp reads 32 consecutive experts of one
+// tile: one 128-byte line), the 32 segment sums of each expert are scanned in shared
+// memory, and a second pass over the segment replaces every count by the number of
+// tokens of that expert in earlier tiles.  Row ntiles receives the totals.
+__global__ void __launch_bounds__(SCAN_NT)
+compact_scan_kernel(int32_t* __restrict__ counts, int ntiles, int E) {
+  __shared__ int seg_sum[32][33];
+  const int el = threadIdx.x & 31, seg = threadIdx.x >> 5;
+  const int e = blockIdx.x * 32 + el;
+  const int per = (ntiles + 31) / 32;
+  const int t0 = min(seg * per, ntiles), t1 = min(t0 + per, ntiles);
+  grid_launch_dependents();
+  grid_dependency_wait();      // the counts table comes from the previous kernel
+  int sum = 0;
+  if (e < E) {
+    int t = t0;
+    for (; t + 3 < t1; t += 4) {     // four independent loads in flight
+      const int a = counts[(int64_t)t * E + e], b = counts[(int64_t)(t + 1) * E + e];
+      const int c = counts[(int64_t)(t + 2) * E + e], d = counts[(int64_t)(t + 3) * E + e];
+      sum += a + b + c + d;
+    }
+    for (; t < t1; ++t) sum += counts[(int64_t)t * E + e];
+  }
+  seg_sum[seg][el] = sum;
+  __syncthreads();
+  if (seg == 0) {
+    int run = 0;
+    for (int s = 0; s < 32; ++s) {
+      const int v = seg_sum[s][el];
+      seg_sum[s][el] = run;
+      run += v;
+    }
+    if (e < E) counts[(int64_t)ntiles * E + e] = run;
+  }
+  __syncthreads();
+  if (e < E) {
+    int run = seg_sum[seg][el];
+    for (int t = t0; t < t1; ++t) {
+      const int v = counts[(int64_t)t * E + e];
+      counts[(int64_t)t * E + e] = run;
+      run += v;
+    }
+  }
+}
+
 __global__ void __launch_bounds__(NTS)
-compact_scatter_kernel(const uint32_t* __restrict__ mask_bits, const int32_t* __restrict__ counts,
+compact_scatter_kernel(const uint32_t* __restrict__ mask_bits, const int32_t* __restrict__ prefix,
                        int32_t* __restrict__ token_idx, int32_t* __restrict__ offsets, int64_t N,
                        int E, int ntiles, int* dev_status) {
   extern __shared__ int sm[];
   int* cnt = sm;                 // [ROWS][E] -> becomes each row's write base
   int* tot = cnt + ROWS * E;     // [E]   total per expert, then exclusive offsets
-  int* pre = tot + E;            // [E]   tokens of expert e in earlier chunks
   const int tid = threadIdx.x, lane = tid & 31, w = tid >> 5;
   const int nw = (E + 31) / 32;
   const int chunk = blockIdx.x;
+  const int64_t t = (int64_t)chunk * CHUNK + w * 32 + lane;
 
   grid_launch_dependents();
   for (int i = tid; i < ROWS * E; i += NTS) cnt[i] = 0;
-  for (int e = tid; e < E; e += NTS) {
-    tot[e] = 0;
-    pre[e] = 0;
-  }
-  grid_dependency_wait();      // mask and counts table come from the previous kernel
   __syncthreads();
-  // column sums of the counts table: thread (grp, e) adds up tiles grp, grp+groups, ...
-  // in registers (coalesced over e), then one shared atomic per thread
-  {
-    const int groups = max(1, NTS / E);
-    const int first_tile = chunk * TILES_PER_CHUNK;
-    const int e = tid % E, grp = tid / E;
-    if (grp < groups) {
-      int a = 0, b = 0;
-      int t = grp;
-      // eight independent loads in flight per thread (the loop is latency-bound otherwise)
-      for (; t + 7 * groups < ntiles; t += 8 * groups) {
-        int v[8];
+  grid_dependency_wait();      // mask and prefix table come from the previous kernels
+  for (int e = tid; e < E; e += NTS) tot[e] = prefix[(int64_t)ntiles * E + e];
+  // per-row popcounts of this chunk; the words stay in registers for the second pass
+  uint32_t word[MAX_E / 32];
 #pragma unroll
-        for (int u = 0; u < 8; ++u) v[u] = __ldg(counts + (int64_t)(t + u * groups) * E + e);
+  for (int j = 0; j < MAX_E / 32; ++j) word[j] = (j < nw && t < N) ? mask_bits[t * nw + j] : 0u;
 #pragma unroll
-        for (int u = 0; u < 8; ++u) {
-          a += v[u];
-          if (t + u * groups < first_tile) b += v[u];
-        }
-      }
-      for (; t < ntiles; t += groups) {
-        const int v = __ldg(counts + (int64_t)t * E + e);
-        a += v;
-        if (t < first_tile) b += v;
-      }
-      atomicAdd(&tot[e], a);
-      atomicAdd(&pre[e], b);
+  for (int j = 0; j < MAX_E / 32; ++j) {
+    if (j >= nw) break;
+    if (__ballot_sync(0xffffffffu, word[j] != 0u) == 0u) continue;
+    const int nb = min(32, E - 32 * j);
+    int mine = 0;
+    for (int b = 0; b < nb; ++b) {
+      const int cb = __popc(__ballot_sync(0xffffffffu, (word[j] >> b) & 1u));
+      if (lane == b) mine = cb;
     }
-  }
-  // per-row popcounts of this chunk
-  if (w < ROWS) {                    // warps 0..ROWS-1 own one row of 32 tokens each
-    const int row = w;
-    const int64_t t = (int64_t)chunk * CHUNK + row * 32 + lane;
-    for (int j = 0; j < nw; ++j) {
-      const uint32_t word = t < N ? mask_bits[t * nw + j] : 0u;
-      if (__ballot_sync(0xffffffffu, word != 0u) == 0u) continue;
-      const int nb = min(32, E - 32 * j);
-      for (int b = 0; b < nb; ++b) {
-        const uint32_t v = __ballot_sync(0xffffffffu, (word >> b) & 1u);
-        if (lane == 0) cnt[row * E + 32 * j + b] = __popc(v);
-      }
-    }
+    if (lane < nb) cnt[w * E + 32 * j + lane] = mine;
   }
   __syncthreads();
   // exclusive scan of the expert totals (E <= 256: one warp, 8 values per lane)
@@ -143,7 +163,7 @@ compact_scatter_kernel(const uint32_t* __restrict__ mask_bits, const int32_t* __
   __syncthreads();
   for (int e = tid; e < E; e += NTS) {
     if (chunk == 0) offsets[e] = tot[e];
-    int run = tot[e] + pre[e];
+    int run = tot[e] + prefix[(int64_t)chunk * TILES_PER_CHUNK * E + e];
     for (int row = 0; row < ROWS; ++row) {
       const int c = cnt[row * E + e];
       cnt[row * E + e] = run;
@@ -151,20 +171,17 @@ compact_scatter_kernel(const uint32_t* __restrict__ mask_bits, const int32_t* __
     }
   }
   __syncthreads();
-  if (w < ROWS) {                    // warps 0..ROWS-1 own one row of 32 tokens each
-    const int row = w;
-    const int64_t t = (int64_t)chunk * CHUNK + row * 32 + lane;
-    for (int j = 0; j < nw; ++j) {
-      const uint32_t word = t < N ? mask_bits[t * nw + j] : 0u;
-      if (__ballot_sync(0xffffffffu, word != 0u) == 0u) continue;
-      const int nb = min(32, E - 32 * j);
-      for (int b = 0; b < nb; ++b) {
-        const uint32_t bit = (word >> b) & 1u;
-        const uint32_t v = __ballot_sync(0xffffffffu, bit);
-        if (bit) {
-          const int rank = __popc(v & ((1u << lane) - 1u));
-          token_idx[cnt[row * E + 32 * j + b] + rank] = (int32_t)t;
-        }
+#pragma unroll
+  for (int j = 0; j < MAX_E / 32; ++j) {
+    if (j >= nw) break;
+    if (__ballot_sync(0xffffffffu, word[j] != 0u) == 0u) continue;
+    const int nb = min(32, E - 32 * j);
+    for (int b = 0; b < nb; ++b) {
+      const uint32_t bit = (word[j] >> b) & 1u;
+      const uint32_t v = __ballot_sync(0xffffffffu, bit);
+      if (bit) {
+        const int rank = __popc(v & ((1u << lane) - 1u));
+        token_idx[cnt[w * E + 32 * j + b] + rank] = (int32_t)t;
       }
     }
   }
@@ -172,9 +189,10 @@ compact_scatter_kernel(const uint32_t* __restrict__ mask_bits, const int32_t* __
 
 }  // namespace
 
+// counts table: one row of E cells per 128-token tile, plus the totals row
 size_t compact_workspace_bytes(int64_t n_max, int E) {
   const int64_t ntiles = ceil_div64(n_max > 0 ? n_max : 1, CTILE);
-  return (size_t)ntiles * (size_t)E * sizeof(int32_t);
+  return (size_t)(ntiles + 1) * (size_t)E * sizeof(int32_t);
 }
 
 int launch_compact(const uint32_t* mask_bits, int32_t* token_idx, int32_t* offsets, int64_t N,
@@ -182,19 +200,23 @@ int launch_compact(const uint32_t* mask_bits, int32_t* token_idx, int32_t* offse
                    bool counts_ready) {
   if (E > MAX_E || E < 1) return D2D_ERR_UNSUPPORTED;
   if (N * (int64_t)E > 0x7fffffffLL) return D2D_ERR_UNSUPPORTED;   // int32 offsets
-  const int64_t ntiles = ceil_div64(N > 0 ? N : 1, CTILE);
-  const int64_t nchunks = ceil_div64(N > 0 ? N : 1, CHUNK);
+  if (N == 0) {
+    // no tokens: every list is empty; no kernel reads the (unwritten) counts table
+    return cudaMemsetAsync(offsets, 0, sizeof(int32_t) * ((size_t)E + 1), s) == cudaSuccess
+               ? D2D_OK
+               : D2D_ERR_LAUNCH;
+  }
+  const int64_t ntiles = ceil_div64(N, CTILE);
+  const int64_t nchunks = ceil_div64(N, CHUNK);
   if (!counts_ready) {
     compact_count_kernel<<<(unsigned)ceil_div64(ntiles, NT / 32), NT, 0, s>>>(mask_bits, counts_ws,
                                                                              N, E);
     if (cudaGetLastError() != cudaSuccess) return D2D_ERR_LAUNCH;
   }
-  const size_t smem = sizeof(int) * ((size_t)ROWS * E + 2 * (size_t)E);
-  if (smem > 48 * 1024) {
-    if (cudaFuncSetAttribute(compact_scatter_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                             (int)smem) != cudaSuccess)
-      return D2D_ERR_LAUNCH;
-  }
+  int rc = launch_pdl(compact_scan_kernel, dim3((unsigned)ceil_div(E, 32)), dim3(SCAN_NT), 0, s,
+                      counts_ws, (int)ntiles, E);
+  if (rc != D2D_OK) return rc;
+  const size_t smem = sizeof(int) * ((size_t)ROWS * E + (size_t)E);
   return launch_pdl(compact_scatter_kernel, dim3((unsigned)nchunks), dim3(NTS), smem, s, mask_bits,
                     (const int32_t*)counts_ws, token_idx, offsets, N, E, (int)ntiles, dev_status);
 }
@@ -216,14 +238,17 @@ int launch_compact(const uint32_t* mask_bits, int32_t* token_idx, int32_t* offse
 // D2D_ERR_SCRATCH_LIMIT before anything is launched.
 //
 // The table is shared by every call in the process and keeps the previous call's
-// contents.  Nothing in it needs clearing: the count kernel writes every cell the
-// scatter kernel later reads (all E cells of each of the ceil(N/128) tiles).
+// contents.  Nothing in it needs clearing: for N > 0 the count kernel writes all E cells
+// of each of the ceil(N/128) tile rows, the scan kernel then writes the totals row, and
+// the scatter kernel reads nothing else; for N = 0 no kernel touches the table (the
+// offsets are simply set to zero).
 // Two calls that run concurrently on one GPU (different streams) would overwrite
 // each other's counts: keep such calls on one stream or order them with events.
 // ---------------------------------------------------------------------------
 #define D2D_NOALLOC_MAX_CELLS (2048 * 128)
 
-static __device__ __align__(256) int32_t g_noalloc_counts[D2D_NOALLOC_MAX_CELLS];
+// + one row of up to 256 expert totals behind the tile rows
+static __device__ __align__(256) int32_t g_noalloc_counts[D2D_NOALLOC_MAX_CELLS + 256];
 
 namespace {
 

@@ -36,6 +36,9 @@
 //
 // Every wait is bounded: when one runs out the kernel records D2D_ERR_TIMEOUT in the
 // status word, all roles leave their loops, TMEM is freed and the kernel returns.
+#include <atomic>
+#include <mutex>
+
 #include "d2d_umma_api.cuh"
 
 namespace d2d {
@@ -50,7 +53,7 @@ constexpr int NTHREADS = 480;            // router form
 constexpr int NTHREADS_EXPERTS = 608;    // + four warps that write the output rows
 constexpr int WARP_MMA1 = 8, WARP_MMA2 = 9, WARP_BULK = 10, WARP_PROD0 = 11, WARP_WR0 = 15;
 constexpr int MAX_E = 128;
-constexpr uint32_t WAIT_LIMIT = 1u << 22;
+constexpr uint32_t WAIT_LIMIT = 1u << 22;   // polls of one bounded wait (about a second)
 constexpr int MODE_EXPERTS = 0, MODE_ROUTER = 1;
 
 struct Geo {
@@ -89,6 +92,8 @@ struct Params {
   bf16* out_init;
   int32_t* tile_counts;     // [tiles][E]: per-expert kept-token counts of each 128-token tile
   int* dev_status;
+  uint32_t wait_limit;      // polls per bounded wait
+  int withhold;             // test hook: CTA 0 never loads its first weight tile
 };
 
 Geo experts_geo(int d, int H, bool glu) {
@@ -176,9 +181,11 @@ __device__ __forceinline__ bool mbar_test_wait(uint32_t bar, uint32_t parity) {
   return ok != 0;
 }
 // Bounded wait.  false = gave up (this thread's limit ran out, or another role did).
+// abort_flag[1] holds the poll limit of this launch (Ctl::wait_limit).
 __device__ __noinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag,
                                        int* dev_status) {
-  for (uint32_t i = 0; i < WAIT_LIMIT; ++i) {
+  const uint32_t limit = (uint32_t)abort_flag[1];
+  for (uint32_t i = 0; i < limit; ++i) {
     if (mbar_try_wait(bar, parity)) return true;
     if (i > 64) {
       __nanosleep(i > 4096 ? 256 : 32);
@@ -343,6 +350,7 @@ struct Ctl {
   unsigned long long sfull[2][4], sempty[2][4];   // staging unit of (epilogue group, row quarter)
   uint32_t tmem_base;
   int abort_flag;
+  int wait_limit;                  // must follow abort_flag (mbar_wait reads abort_flag[1])
   int total_tiles;
   alignas(16) float bias_s[128];   // (read as float4) b1 of the current tile's expert
   int total_full;                  // experts: number of full 128-row tiles (they come first)
@@ -474,12 +482,17 @@ __device__ void role_bulk(const Params& p, Ctl* c, uint32_t ringB, uint32_t ring
   const uint8_t *pe1 = nullptr, *pe2 = nullptr;
   if (t1 < total) pe1 = pe2 = p.packed + (long long)tile_info<MODE>(p, c, t1).e * g.stride;
   uint32_t idle = 0;
+  bool withheld = p.withhold != 0 && blockIdx.x == 0;
   while (t1 < total || t2 < total) {
     bool progress = false;
     if (t1 < total && mbar_test_wait(emptyB + 8 * r1.s, r1.ph ^ 1)) {
       const uint32_t bar = fullB + 8 * r1.s;
-      mbar_arrive_expect_tx(bar, b1);
-      bulk_g2s(ringB + r1.s * SLOT, pe1 + (long long)j1 * b1, b1, bar);
+      if (withheld) {
+        withheld = false;      // test hook: this stage never fills, its consumer's wait runs out
+      } else {
+        mbar_arrive_expect_tx(bar, b1);
+        bulk_g2s(ringB + r1.s * SLOT, pe1 + (long long)j1 * b1, b1, bar);
+      }
       r1.next(g.nb);
       if (++j1 == n1) {
         j1 = 0;
@@ -505,7 +518,7 @@ __device__ void role_bulk(const Params& p, Ctl* c, uint32_t ringB, uint32_t ring
     } else {
       if (++idle > 64) __nanosleep(idle > 4096 ? 256 : 32);
       if ((idle & 63) == 0 && *af != 0) return;
-      if (idle >= WAIT_LIMIT) {
+      if (idle >= p.wait_limit) {
         *af = 1;
         report(p.dev_status, D2D_ERR_TIMEOUT);
         return;
@@ -1026,6 +1039,7 @@ mlp_tiles_kernel(const Params p) {
       }
     }
     c->abort_flag = 0;
+    c->wait_limit = (int)p.wait_limit;
     if (MODE == MODE_ROUTER) c->total_tiles = (int)((p.N + TILE_M - 1) / TILE_M);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     fence_proxy_async();
@@ -1104,6 +1118,10 @@ mlp_tiles_kernel(const Params p) {
     role_writer(p, c, stg, tid - WARP_WR0 * 32);
   }
 
+  // A launch that gave up may still have copies and MMAs in flight that use this CTA's
+  // shared and tensor memory: give them time to land before both are released.
+  if (*reinterpret_cast<volatile int*>(&c->abort_flag) != 0)
+    for (int i = 0; i < 64; ++i) __nanosleep(1000);
   tc_fence_before();
   __syncthreads();
   if (warp == WARP_MMA1) {
@@ -1179,16 +1197,21 @@ __global__ void prepack_router_kernel(const bf16* __restrict__ wa, const bf16* _
   }
 }
 
-int sm_count() {
-  static int n = 0;
-  if (n == 0) {
-    int dev = 0;
-    if (cudaGetDevice(&dev) != cudaSuccess) return 148;
-    if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0)
-      n = 148;
-  }
-  return n;
-}
+// Facts of one device, looked up with that device current.  The shared-memory opt-in of
+// a kernel (cudaFuncSetAttribute) holds for the current device only, as does the SM count,
+// so both are cached per device index; the lock makes first use from several host threads
+// safe.
+constexpr int MAX_DEVICES = 64;
+struct DeviceFacts {
+  int sms = 0;
+  size_t smem_optin[2] = {0, 0};      // per MODE: largest dynamic shared memory opted in
+};
+DeviceFacts g_dev[MAX_DEVICES];
+std::mutex g_dev_lock;
+
+// test hooks (d2d_debug_configure): process-wide, read at launch
+std::atomic<uint32_t> g_wait_limit{WAIT_LIMIT};
+std::atomic<int> g_withhold{0};
 
 static_assert(1024 + (size_t)SLOTS_TOTAL * SLOT + sizeof(Ctl) + 64 <= 232448,
               "shared-memory plan exceeds the 227 KB a CTA may use");
@@ -1198,21 +1221,37 @@ size_t smem_bytes(const Geo& g) {
 }
 
 template <int MODE>
-int launch(const Params& p, long long max_tiles, cudaStream_t s) {
+int launch(Params& p, long long max_tiles, cudaStream_t s) {
   const size_t smem = smem_bytes(p.g);
   auto k = mlp_tiles_kernel<MODE>;
-  static bool attr_set[2] = {false, false};
-  static size_t attr_val[2] = {0, 0};
-  if (!attr_set[MODE] || attr_val[MODE] < smem) {
-    if (cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) !=
-        cudaSuccess) {
-      cudaGetLastError();
-      return D2D_ERR_LAUNCH;
-    }
-    attr_set[MODE] = true;
-    attr_val[MODE] = smem;
+  int dev = -1, sms = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= MAX_DEVICES) {
+    cudaGetLastError();
+    return D2D_ERR_NO_DEVICE;
   }
-  long long grid = max_tiles < sm_count() ? max_tiles : sm_count();
+  {
+    std::lock_guard<std::mutex> hold(g_dev_lock);
+    DeviceFacts& f = g_dev[dev];
+    if (f.sms == 0 &&
+        (cudaDeviceGetAttribute(&f.sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess ||
+         f.sms <= 0)) {
+      cudaGetLastError();
+      f.sms = 0;
+      return D2D_ERR_NO_DEVICE;
+    }
+    if (f.smem_optin[MODE] < smem) {
+      if (cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) !=
+          cudaSuccess) {
+        cudaGetLastError();
+        return D2D_ERR_LAUNCH;
+      }
+      f.smem_optin[MODE] = smem;
+    }
+    sms = f.sms;
+  }
+  p.wait_limit = g_wait_limit.load();
+  p.withhold = g_withhold.load();
+  long long grid = max_tiles < sms ? max_tiles : sms;
   if (grid < 1) grid = 1;
   return launch_pdl(k, dim3((unsigned)grid), dim3(MODE == MODE_EXPERTS ? NTHREADS_EXPERTS : NTHREADS),
                     smem, s, p);
@@ -1260,6 +1299,12 @@ int launch_experts_umma(const void* x, const int32_t* token_idx, const int32_t* 
   p.dev_status = dev_status;
   const long long max_tiles = (N * (long long)E + TILE_M - 1) / TILE_M + E;
   return launch<MODE_EXPERTS>(p, max_tiles, s);
+}
+
+void umma_debug_configure(int wait_limit_log2, int withhold_weight_tile) {
+  g_wait_limit.store(wait_limit_log2 >= 4 && wait_limit_log2 <= 22 ? 1u << wait_limit_log2
+                                                                    : WAIT_LIMIT);
+  g_withhold.store(withhold_weight_tile ? 1 : 0);
 }
 
 bool umma_router_supported(int d, int R, int E, int dtype) {

@@ -21,4 +21,8 @@ int launch_router_mask_umma(const void* x, const void* packed, float mult, uint3
                             int32_t* tile_counts, int64_t N, int d, int R, int E, int* dev_status,
                             cudaStream_t s);
 
+// test hooks: poll limit of the bounded device waits (2^log2, out of range = default) and
+// a flag that makes CTA 0 of the next launches skip its first weight tile
+void umma_debug_configure(int wait_limit_log2, int withhold_weight_tile);
+
 }  // namespace d2d

@@ -74,9 +74,18 @@ class _WorkspaceCache:
 
 
 class _PackedCache:
-    """Packed weight images, rebuilt when any source parameter changes."""
+    """Packed weight images, rebuilt when a source parameter changes.
+
+    A change is seen through the parameter's storage address, shape, dtype and version
+    counter, i.e. ``load_state_dict``, ``.to()``, ``copy_`` and other in-place tensor ops.
+    Writes that bypass the version counter (``p.data.copy_(...)``, raw pointer writes) are
+    not seen: call ``invalidate()`` (``module.invalidate_packed()``) after those."""
 
     def __init__(self):
+        self._key = None
+        self._buf = None
+
+    def invalidate(self):
         self._key = None
         self._buf = None
 
@@ -153,6 +162,10 @@ class B200KernelExperts(ExpertsLayer):
                                                             None if p["b1"] is None else p["b1"].detach(),
                                                             p["w2"].detach(),
                                                             None if p["w_up"] is None else p["w_up"].detach()))
+
+    def invalidate_packed(self):
+        """Drop the packed weight copy (needed only after writes through ``.data``)."""
+        self._packed.invalidate()
 
     def _check_mode(self):
         if self._forward_mode not in _KERNEL_MODES:
@@ -283,6 +296,10 @@ class MoeficationRouter(nn.Module):
     def packed(self):
         wa, wb = self.layers[0].weight, self.layers[2].weight
         return self._packed.get((wa, wb), lambda: ops.prepack_router(wa.detach(), wb.detach()))
+
+    def invalidate_packed(self):
+        """Drop the packed weight copy (needed only after writes through ``.data``)."""
+        self._packed.invalidate()
 
     def forward(self, x):
         for layer in self.layers:
@@ -451,7 +468,16 @@ class MoeficationMoE(MoELayer):
         rows = max(hi - lo for lo, hi in bounds)
         shape = (rows,) + tuple(x_host.shape[1:])
         if bufs is None or bufs[0].shape != shape or bufs[0].dtype != x_host.dtype:
-            bufs = [torch.empty(shape, dtype=x_host.dtype, device=dev) for _ in range(2)]
+            # Copies and kernels of earlier sync=False calls may still use the old staging
+            # buffers: drain the three streams before they go back to the allocator (a host
+            # wait, but only when the slice shape changes), and allocate the new ones on the
+            # copy stream that writes them, telling the allocator which stream reads them.
+            for s_ in st:
+                s_.synchronize()
+            with torch.cuda.stream(s_in):
+                bufs = [torch.empty(shape, dtype=x_host.dtype, device=dev) for _ in range(2)]
+            for b in bufs:
+                b.record_stream(s_run)
             self._host_bufs = bufs
             self._host_done = [None, None]
         done_run = self._host_done        # kernels that last read each buffer (kept across calls)

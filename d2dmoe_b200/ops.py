@@ -25,6 +25,7 @@ def _dt(t: torch.Tensor) -> int:
 
 
 def _cu(*ts):
+    dev = None
     for t in ts:
         if t is None:
             continue
@@ -32,14 +33,36 @@ def _cu(*ts):
             raise RuntimeError("d2dmoe_b200 runs on CUDA tensors only (there is no CPU path)")
         if not t.is_contiguous():
             raise ValueError("d2dmoe_b200 needs contiguous tensors")
+        if dev is None:
+            dev = t.device
+        elif t.device != dev:
+            raise ValueError(f"tensors of one call live on different devices: {dev} and {t.device}")
 
 
 def _ptr(t):
     return None if t is None else C.c_void_p(t.data_ptr())
 
 
-def _stream():
-    return C.c_void_p(torch.cuda.current_stream().cuda_stream)
+class _on:
+    """Make the device of ``t`` current for a library call (kernels launch on the current
+    device) and hand out that device's current stream.  A no-op when it is current already."""
+
+    __slots__ = ("dev", "ctx")
+
+    def __init__(self, t):
+        self.dev = t.device if isinstance(t, torch.Tensor) else torch.device(t)
+        self.ctx = None
+
+    def __enter__(self):
+        if self.dev.index is not None and self.dev.index != torch.cuda.current_device():
+            self.ctx = torch.cuda.device(self.dev)
+            self.ctx.__enter__()
+        return C.c_void_p(torch.cuda.current_stream(self.dev).cuda_stream)
+
+    def __exit__(self, *exc):
+        if self.ctx is not None:
+            self.ctx.__exit__(*exc)
+        return False
 
 
 def threshold_multiplier(tau: float) -> float:
@@ -91,11 +114,12 @@ def router_mask(x2d, wa, wb, tau, wsp: Workspace, *, packed=None, scores_out=Non
     _cu(x2d, wa, wb, packed, scores_out, last_bias, out_init)
     N, d = x2d.shape
     R, E = wa.shape[0], wb.shape[0]
-    check(lib.d2d_router_mask(_ptr(x2d), _ptr(wa), _ptr(wb), _ptr(packed),
-                              threshold_multiplier(tau), _ptr(wsp.mask_bits), _ptr(scores_out),
-                              _ptr(last_bias), int(add_residual), _ptr(out_init),
-                              N, d, R, E, _dt(x2d), _ptr(wsp.status), _stream()),
-          "d2d_router_mask")
+    with _on(x2d) as st:
+        check(lib.d2d_router_mask(_ptr(x2d), _ptr(wa), _ptr(wb), _ptr(packed),
+                                  threshold_multiplier(tau), _ptr(wsp.mask_bits), _ptr(scores_out),
+                                  _ptr(last_bias), int(add_residual), _ptr(out_init),
+                                  N, d, R, E, _dt(x2d), _ptr(wsp.status), st),
+              "d2d_router_mask")
 
 
 RULE_TOPK, RULE_DYNK = 1, 2
@@ -112,55 +136,62 @@ def mask_rule_from_scores(scores2d, rule: str, wsp: Workspace, k=None, tau=None)
         r, kk, tt = RULE_DYNK, 0, float(tau)
     else:
         raise ValueError(f"unknown rule {rule!r}")
-    check(lib.d2d_mask_rule_from_scores(_ptr(scores2d), r, kk, tt, _ptr(wsp.mask_bits), N, E,
-                                        _dt(scores2d), _ptr(wsp.status), _stream()),
-          "d2d_mask_rule_from_scores")
+    with _on(scores2d) as st:
+        check(lib.d2d_mask_rule_from_scores(_ptr(scores2d), r, kk, tt, _ptr(wsp.mask_bits), N, E,
+                                            _dt(scores2d), _ptr(wsp.status), st),
+              "d2d_mask_rule_from_scores")
 
 
 def mask_from_scores(scores2d, tau, wsp: Workspace):
     _cu(scores2d)
     N, E = scores2d.shape
-    check(lib.d2d_mask_from_scores(_ptr(scores2d), threshold_multiplier(tau), _ptr(wsp.mask_bits),
-                                   N, E, _dt(scores2d), _ptr(wsp.status), _stream()),
-          "d2d_mask_from_scores")
+    with _on(scores2d) as st:
+        check(lib.d2d_mask_from_scores(_ptr(scores2d), threshold_multiplier(tau),
+                                       _ptr(wsp.mask_bits), N, E, _dt(scores2d), _ptr(wsp.status),
+                                       st), "d2d_mask_from_scores")
 
 
 def pack_mask(routing2d, wsp: Workspace):
     _cu(routing2d)
     N, E = routing2d.shape
-    check(lib.d2d_pack_mask(_ptr(routing2d), _ptr(wsp.mask_bits), N, E, _dt(routing2d), _stream()),
-          "d2d_pack_mask")
+    with _on(routing2d) as st:
+        check(lib.d2d_pack_mask(_ptr(routing2d), _ptr(wsp.mask_bits), N, E, _dt(routing2d), st),
+              "d2d_pack_mask")
 
 
 def expand_mask(wsp: Workspace, N: int, E: int, dtype) -> torch.Tensor:
     rt = torch.empty(N, E, dtype=dtype, device=wsp.mask_bits.device)
-    check(lib.d2d_expand_mask(_ptr(wsp.mask_bits), _ptr(rt), N, E, _DT[dtype], _stream()),
-          "d2d_expand_mask")
+    with _on(rt) as st:
+        check(lib.d2d_expand_mask(_ptr(wsp.mask_bits), _ptr(rt), N, E, _DT[dtype], st),
+              "d2d_expand_mask")
     return rt
 
 
 def init_out(x2d, last_bias, add_residual, out):
     _cu(x2d, last_bias, out)
     N, d = out.shape
-    check(lib.d2d_init_out(_ptr(x2d), _ptr(last_bias), int(add_residual), _ptr(out), N, d,
-                           _dt(out), _stream()), "d2d_init_out")
+    with _on(out) as st:
+        check(lib.d2d_init_out(_ptr(x2d), _ptr(last_bias), int(add_residual), _ptr(out), N, d,
+                               _dt(out), st), "d2d_init_out")
 
 
 def compact(wsp: Workspace, N: int, E: int):
-    check(lib.d2d_compact(_ptr(wsp.mask_bits), _ptr(wsp.token_idx), _ptr(wsp.offsets), N, E,
-                          _ptr(wsp.ws), wsp.ws.numel(), _ptr(wsp.status), _stream()),
-          "d2d_compact")
+    with _on(wsp.mask_bits) as st:
+        check(lib.d2d_compact(_ptr(wsp.mask_bits), _ptr(wsp.token_idx), _ptr(wsp.offsets), N, E,
+                              _ptr(wsp.ws), wsp.ws.numel(), _ptr(wsp.status), st),
+              "d2d_compact")
 
 
 def experts_ffn(x2d, wsp: Workspace, w1, b1, w2, act: str, out, *, w_up=None, packed=None,
                 last_bias=None, add_residual=False, accumulate=False):
-    _cu(x2d, w1, b1, w2, w_up, packed, last_bias, out)
+    _cu(x2d, w1, b1, w2, w_up, packed, last_bias, out, wsp.token_idx)
     N, d = x2d.shape
     E, _, H = w1.shape
-    check(lib.d2d_experts_ffn(_ptr(x2d), _ptr(wsp.token_idx), _ptr(wsp.offsets), _ptr(w1),
-                              _ptr(b1), _ptr(w_up), _ptr(w2), _ptr(packed), _ptr(last_bias),
-                              int(add_residual), int(accumulate), _ptr(out), N, d, E, H, ACT[act],
-                              _dt(x2d), _ptr(wsp.status), _stream()), "d2d_experts_ffn")
+    with _on(x2d) as st:
+        check(lib.d2d_experts_ffn(_ptr(x2d), _ptr(wsp.token_idx), _ptr(wsp.offsets), _ptr(w1),
+                                  _ptr(b1), _ptr(w_up), _ptr(w2), _ptr(packed), _ptr(last_bias),
+                                  int(add_residual), int(accumulate), _ptr(out), N, d, E, H,
+                                  ACT[act], _dt(x2d), _ptr(wsp.status), st), "d2d_experts_ffn")
 
 
 def moe_forward(x2d, wa, wb, tau, w1, b1, w2, act: str, out, wsp: Workspace, *, w_up=None,
@@ -168,16 +199,19 @@ def moe_forward(x2d, wa, wb, tau, w1, b1, w2, act: str, out, wsp: Workspace, *, 
                 experts_packed=None):
     """Whole layer in one library call: router+mask (or mask from ``scores``) ->
     compaction -> expert FFN with scatter-add into ``out``."""
-    _cu(x2d, wa, wb, w1, b1, w2, w_up, scores, last_bias, out, router_packed, experts_packed)
+    _cu(x2d, wa, wb, w1, b1, w2, w_up, scores, last_bias, out, router_packed, experts_packed,
+        wsp.mask_bits)
     N, d = x2d.shape
     E, _, H = w1.shape
     R = wa.shape[0] if wa is not None else 0
-    check(lib.d2d_moe_forward(_ptr(x2d), _ptr(wa), _ptr(wb), _ptr(router_packed), _ptr(scores),
-                              threshold_multiplier(tau), _ptr(w1), _ptr(b1), _ptr(w_up), _ptr(w2),
-                              _ptr(experts_packed), _ptr(last_bias), int(add_residual), _ptr(out),
-                              _ptr(wsp.mask_bits), _ptr(wsp.token_idx), _ptr(wsp.offsets),
-                              N, d, R, E, H, ACT[act], _dt(x2d), _ptr(wsp.ws), wsp.ws.numel(),
-                              _ptr(wsp.status), _stream()), "d2d_moe_forward")
+    with _on(x2d) as st:
+        check(lib.d2d_moe_forward(_ptr(x2d), _ptr(wa), _ptr(wb), _ptr(router_packed), _ptr(scores),
+                                  threshold_multiplier(tau), _ptr(w1), _ptr(b1), _ptr(w_up),
+                                  _ptr(w2), _ptr(experts_packed), _ptr(last_bias),
+                                  int(add_residual), _ptr(out), _ptr(wsp.mask_bits),
+                                  _ptr(wsp.token_idx), _ptr(wsp.offsets), N, d, R, E, H, ACT[act],
+                                  _dt(x2d), _ptr(wsp.ws), wsp.ws.numel(), _ptr(wsp.status), st),
+              "d2d_moe_forward")
 
 
 def prepack_experts(w1, b1, w2, w_up=None):
@@ -193,8 +227,9 @@ def prepack_experts(w1, b1, w2, w_up=None):
     buf = torch.empty(n.value + 1024, dtype=torch.uint8, device=w1.device)
     off = (-buf.data_ptr()) % 1024
     packed = buf[off:off + n.value]
-    check(lib.d2d_prepack_experts(_ptr(w1), _ptr(b1), _ptr(w_up), _ptr(w2), _ptr(packed), d, E, H,
-                                  _dt(w1), _stream()), "d2d_prepack_experts")
+    with _on(w1) as st:
+        check(lib.d2d_prepack_experts(_ptr(w1), _ptr(b1), _ptr(w_up), _ptr(w2), _ptr(packed), d, E,
+                                      H, _dt(w1), st), "d2d_prepack_experts")
     return packed
 
 
@@ -209,6 +244,7 @@ def prepack_router(wa, wb):
     buf = torch.empty(n.value + 1024, dtype=torch.uint8, device=wa.device)
     off = (-buf.data_ptr()) % 1024
     packed = buf[off:off + n.value]
-    check(lib.d2d_prepack_router(_ptr(wa), _ptr(wb), _ptr(packed), d, R, E, _dt(wa), _stream()),
-          "d2d_prepack_router")
+    with _on(wa) as st:
+        check(lib.d2d_prepack_router(_ptr(wa), _ptr(wb), _ptr(packed), d, R, E, _dt(wa), st),
+              "d2d_prepack_router")
     return packed

@@ -182,15 +182,26 @@ int d2d_moe_forward(const void* x, const void* wa, const void* wb, const void* r
                     int64_t N, int d, int R, int E, int H, int act, int dtype,
                     void* ws, size_t ws_bytes, int* dev_status, d2d_stream_t stream);
 
+/* Number of kernels the calling thread's last d2d_moe_forward issued (4 on the tensor-core
+ * path: router + rule, compaction scan, compaction scatter, expert FFN; more on the
+ * general-shape paths).  Introspection for benchmarks; no upstream counterpart. */
+int d2d_last_forward_launches(void);
+
+/* Test hook, no upstream counterpart.  Every wait inside the tensor-core kernels is bounded;
+ * when one runs out the kernel writes D2D_ERR_TIMEOUT to *dev_status, frees its tensor
+ * memory and returns.  wait_limit_log2 in 4..22 sets the bound to 2^n polls for later
+ * launches of this process (anything else restores the default of 2^22, about a second);
+ * withhold_weight_tile != 0 makes CTA 0 of later launches skip its first weight tile, so
+ * that exactly this path can be exercised without faulting the GPU.  Call
+ * d2d_debug_configure(0, 0) to return to normal operation. */
+int d2d_debug_configure(int wait_limit_log2, int withhold_weight_tile);
+
 /* One-time re-layout of the weights into the shared-memory tile images the
  * tensor-core kernels copy in bulk (bf16 only).  The upstream kernels read the
  * parameters in place (architectures/moe/moe_impls.py:137-146,276-284); here the
  * module owns a packed copy and refreshes it when the parameters change.
- * *_bytes returns 0 bytes when the shape has no tensor-core path. */
-/* Number of kernels the calling thread's last d2d_moe_forward issued (3 on the tensor-core
- * path: router + rule, compaction scatter, expert FFN; more on the general-shape paths).  Introspection for benchmarks; no upstream counterpart. */
-int d2d_last_forward_launches(void);
-
+ * *_bytes returns 0 bytes when the shape has no tensor-core path.  `packed` must be
+ * 1024-byte aligned. */
 int d2d_prepack_experts_bytes(int d, int E, int H, int glu, int dtype, size_t* bytes /* host */);
 int d2d_prepack_experts(const void* w1, const void* b1_opt, const void* w_up_opt, const void* w2,
                         void* packed, int d, int E, int H, int dtype, d2d_stream_t stream);

@@ -291,3 +291,49 @@ def cpu_layer_forward_naive(x, p: dict, tau: float, act="relu", scores=None):
     if p.get("last_bias") is not None:
         out = out + p["last_bias"]
     return out.view(x.shape), rt
+
+
+def glu_module_weights(w_gate, w_up, w_down):
+    """Per-expert ``nn.Linear`` weights of the upstream 'module' experts, from the stacked
+    GLU parameters: gate.weight = layers.0.w[e]^T, up_scale.weight = layers.2.w[e]^T,
+    down_scale.weight = layers.1.w[e]^T (nn.Linear stores [out, in];
+    architectures/moe/moe_layers.py:104-110).  Made once, like a module's parameters."""
+    tr = lambda w: [w[e].t().contiguous() for e in range(w.shape[0])]       # noqa: E731
+    return {"gate": tr(w_gate), "up": tr(w_up), "down": tr(w_down)}
+
+
+@torch.inference_mode()
+def experts_glu_module(x2d, rt, lin: dict, act="gelu"):
+    """ModuleBatchedExperts.forward with GLUExpert experts, no biases
+    (architectures/moe/moe_layers.py:104-113,310-324): for every expert i the rows with a
+    non-zero routing entry are gathered, down(act(gate(x)) * up(x)) is evaluated with three
+    nn.Linear calls, multiplied by the routing entries and added to the output rows."""
+    F = torch.nn.functional
+    fn = {"relu": torch.relu, "gelu": F.gelu, "tanh": torch.tanh, "leaky_relu": F.leaky_relu,
+          "gelu_tanh": lambda v: F.gelu(v, approximate="tanh")}[act]
+    out = torch.zeros_like(x2d)
+    for i in range(len(lin["gate"])):
+        col = rt[:, i]
+        m = col != 0.0
+        sc = col[m].unsqueeze(1)
+        xe = x2d[m]
+        y = F.linear(fn(F.linear(xe, lin["gate"][i])) * F.linear(xe, lin["up"][i]), lin["down"][i])
+        out[m] += y * sc
+    return out
+
+
+@torch.inference_mode()
+def cpu_layer_forward_module_glu(x, p: dict, tau: float, act="gelu"):
+    """The upstream CPU path of a gated (GeGLU) layer: router and dynk_max gate as in
+    cpu_layer_forward_naive (moefication.py:328-330, :80-85), experts_class='module' with
+    add_intermediate_gating (moefication.py:39-45 -> ModuleBatchedExperts + GLUExpert), no
+    last_bias (bias=False).  p: wa, wb and ``lin`` from glu_module_weights."""
+    F = torch.nn.functional
+    x2d = x.reshape(-1, x.shape[-1])
+    s = F.linear(torch.relu(F.linear(x2d, p["wa"])), p["wb"]).abs()
+    mx = s.max(dim=-1, keepdim=True).values
+    thr = mx * (1.0 - tau)
+    rt = torch.zeros_like(s)
+    rt[s >= thr] = 1.0
+    out = experts_glu_module(x2d, rt, p["lin"], act)
+    return out.view(x.shape), rt

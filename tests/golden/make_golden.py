@@ -3,7 +3,7 @@
 Usage:  python tests/golden/make_golden.py            (needs an upstream checkout;
         see oracle/ref_shim.py for where it is looked up)
 
-For every case of oracle/cases.py (parity grid, config 0, a small GeGLU case)
+For every case of oracle/cases.py (parity grid, config 0, small GeGLU cases, the Gemma-size layer shape)
 this builds the upstream MoeficationMoE + MoeficationRouter, loads the seeded
 tensors into it, runs forward in 'dynk_max' mode with the experts in 'masked'
 (dense) and 'naive' (sparse loop) modes, and stores what the upstream code
@@ -54,8 +54,27 @@ def glu_case_bf16() -> C.LayerCase:
                        norm="rms", dtype="bf16")
 
 
+def gemma_shape_cases() -> list[C.LayerCase]:
+    """The Gemma-2B-size layer's own shape (d 2048, 128 experts x 128, router 2048->256->128,
+    GeGLU with erf GELU, RMS-normed input, bf16) at a ragged token count: the two-half router,
+    16 output chunks per tile, E = 128 with H = 128.  The second case keeps more experts per
+    token, so that some experts own more than one 128-row tile."""
+    return [
+        C.LayerCase("gemma_shape", 3, 701, 2048, 128, 128, R=256, tau=0.1, dtype="bf16",
+                    act="gelu", glu=True, norm="rms", seed=4),
+        C.LayerCase("gemma_shape_k", 3, 701, 2048, 128, 128, R=256, tau=0.45, dtype="bf16",
+                    act="gelu", glu=True, norm="rms", seed=5),
+    ]
+
+
+# cases whose saved output rows are capped at this many (others: MAX_OUT_ELEMS elements)
+ROWS_SAVED = {"gemma_shape": 96, "gemma_shape_k": 96}
+# upstream's dense gated experts materialise [E, N, d]: such cases run in token chunks
+TOKEN_CHUNK = {"gemma_shape": 192, "gemma_shape_k": 192}
+
+
 def all_cases():
-    return C.parity_grid() + [C.config0(), glu_case(), glu_case_bf16()]
+    return C.parity_grid() + [C.config0(), glu_case(), glu_case_bf16()] + gemma_shape_cases()
 
 
 def build_reference_module(ref, c: C.LayerCase, t: dict):
@@ -95,15 +114,53 @@ def run_case(ref, c: C.LayerCase) -> dict:
            "scores": scores.float().reshape(c.N, c.E).numpy()}
     outs = {}
     modes = ["execute_all"] if c.glu else ["masked", "naive"]
+    chunk = TOKEN_CHUNK.get(c.name)
     for mode in modes:
         if not c.glu:
             moe.experts.forward_mode = mode
-        out, gd = moe(t["x"])
-        rt = gd[c.name][0]
+        if chunk is None:
+            out, gd = moe(t["x"])
+            rt = gd[c.name][0]
+        else:
+            # tokens are independent: the module run on slices of the token axis gives the
+            # rows of a run on the whole batch
+            # (the scores are those of the whole-batch router run above, fed back through the
+            # fixed-score router, so that no slice depends on how a CPU GEMM blocks its rows)
+            xs = t["x"].reshape(1, c.N, c.d)
+            ss = scores.reshape(1, c.N, c.E)
+            router = moe.router
+            o_parts, r_parts = [], []
+            for lo in range(0, c.N, chunk):
+                moe.router = _FixedScores(ss[:, lo:lo + chunk])
+                o, gd = moe(xs[:, lo:lo + chunk])
+                o_parts.append(o)
+                r_parts.append(gd[c.name][0])
+            moe.router = router
+            out = torch.cat(o_parts, 1).reshape(c.B, c.S, c.d)
+            rt = torch.cat(r_parts, 1).reshape(c.B, c.S, c.E)
         assert rt.dtype == scores.dtype and rt.shape == (c.B, c.S, c.E)
         outs[mode] = out.float().reshape(c.N, c.d)
         rec["mask_bits"] = O.pack_mask(rt.reshape(c.N, c.E) > 0)
-    stride = max(1, -(-c.N * c.d // MAX_OUT_ELEMS))
+    if c.glu:
+        # the sparse CPU form of the same layer: experts_class='module' (one GLUExpert of
+        # three nn.Linear per expert), fed the same parameters
+        sp = ref.MoeficationMoE(c.name, c.d, c.E, False, c.H, ACT[c.act], experts_class="module",
+                                add_intermediate_gating=True).to(c.torch_dtype)
+        for e in range(c.E):
+            sp.experts.e[e].gate.weight.copy_(t["w1"][e].t())
+            sp.experts.e[e].up_scale.weight.copy_(t["w_up"][e].t())
+            sp.experts.e[e].down_scale.weight.copy_(t["w2"][e].t())
+        sp.router = _FixedScores(scores)
+        sp.forward_mode, sp.tau = "dynk_max", c.tau
+        sp.eval()
+        out, gd = sp(t["x"])
+        assert torch.equal(gd[c.name][0].reshape(c.N, c.E) > 0,
+                           O.unpack_mask(rec["mask_bits"], c.E))
+        outs["module"] = out.float().reshape(c.N, c.d)
+    if c.name in ROWS_SAVED:
+        stride = max(1, c.N // ROWS_SAVED[c.name])
+    else:
+        stride = max(1, -(-c.N * c.d // MAX_OUT_ELEMS))
     rows = np.arange(0, c.N, stride, dtype=np.int64)
     rec["rows"] = rows
     for mode, o in outs.items():
@@ -118,7 +175,10 @@ def main():
         raise SystemExit("no upstream checkout found (set D2DMOE_REFERENCE_ROOT)")
     torch.set_num_threads(8)
     outdir = Path(__file__).resolve().parent
+    only = set(sys.argv[1:])          # optional: names of the cases to (re)generate
     for c in all_cases():
+        if only and c.name not in only:
+            continue
         rec = run_case(ref, c)
         np.savez_compressed(outdir / f"{c.name}.npz", **rec)
         k = O.unpack_mask(rec["mask_bits"], c.E).sum().item() / c.N

@@ -40,3 +40,27 @@ def test_host_only_entry_points():
     # null pointers are rejected on the host before anything is launched
     assert _capi.lib.d2d_compact(None, None, None, 10, 4, None, 0, None, None) == 1
     assert _capi.lib.d2d_mask_from_scores(None, 0.5, None, 10, 4, 0, None, None) == 1
+
+
+def test_misaligned_buffers_are_rejected_before_any_launch():
+    """x / out that do not start on a 16-byte boundary (a view with a storage offset) must be
+    refused on the host with BAD_ARG: the checks of every stage run before the first launch,
+    so nothing is enqueued.  The pointers are never dereferenced on the host."""
+    import ctypes as C
+    from d2dmoe_b200 import _capi
+    lib = _capi.lib
+    a = lambda v: C.c_void_p(v)                                             # noqa: E731
+    base, ws = 0x7f0000000000, 0x7f0000100000
+    good = dict(x=a(base), out=a(base + 0x10000))
+    for bad in ("x", "out"):
+        ptrs = dict(good)
+        ptrs[bad] = a(ptrs[bad].value + 2)
+        rc = lib.d2d_moe_forward(ptrs["x"], a(base), a(base), a(ws), None, 0.9, a(base), a(base),
+                                 None, a(base), a(ws), None, 0, ptrs["out"], a(base), a(base),
+                                 a(base), 256, 768, 128, 24, 128, 0, 1, a(ws), 1 << 20, None, None)
+        assert rc == 1, (bad, rc)
+    # experts entry point alone
+    rc = lib.d2d_experts_ffn(a(base + 2), a(base), a(base), a(base), None, None, a(base), None,
+                             None, 0, 1, a(base), 256, 768, 24, 128, 0, 1, None, None)
+    assert rc == 1
+    assert lib.d2d_debug_configure(0, 0) == 0

@@ -130,3 +130,91 @@ def test_sampled_rows_against_oracle(layer):
     ex = O.experts_ffn_exact(xs, m, p["experts.w1"], p["experts.b1"], p["experts.w2"]) \
         + p["last_bias"].double()
     assert O.rel_err(out.reshape(N, D)[idx.cuda()].float().cpu(), ex) <= 2e-2
+
+
+# ---------------------------------------------------------------------------------------
+# The other configurations at their full layer size: sampled rows against the CPU oracle.
+# ---------------------------------------------------------------------------------------
+FULL = {
+    # name: (B, S, d, H, E, R, glu, act, norm, scores given)
+    "gpt2_scores_32768": (32, 1024, 768, 128, 24, 128, False, "relu", "layer", True),
+    "bert_96x32_65536": (512, 128, 768, 32, 96, 128, False, "relu", "layer", False),
+    "gemma_geglu_131072": (64, 2048, 2048, 128, 128, 256, True, "gelu", "rms", False),
+}
+
+
+@pytest.mark.parametrize("name", list(FULL), ids=list(FULL))
+def test_full_size_configs_sampled_rows(name):
+    """One layer of the GPT-2 (log-normal score override), BERT (96 experts x 32) and
+    Gemma-size (GeGLU, d 2048, 128 experts, 256-wide router) configurations at full token
+    count through the module: the routing tensor must be the rule on the scores (all tokens
+    for given scores; sampled tokens, outside the tie window, for the fused router), the token
+    lists must be the routing tensor's columns, and sampled output rows must match the fp64
+    evaluation of the experts the layer selected."""
+    import d2dmoe_b200 as Dm
+    Bn, Sn, d, Hn, En, Rn, glu, act, norm, given = FULL[name]
+    n = Bn * Sn
+    g = torch.Generator(device="cuda").manual_seed(len(name))
+    rn = lambda *s: torch.randn(*s, generator=g, device="cuda")           # noqa: E731
+    x = rn(Bn, Sn, d)
+    if norm == "layer":
+        x = torch.nn.functional.layer_norm(x, (d,))
+    else:
+        x = x * torch.rsqrt(x.pow(2).mean(-1, keepdim=True) + 1e-6)
+    x = x.bfloat16()
+    actm = {"relu": torch.nn.ReLU, "gelu": torch.nn.GELU}[act]
+    if glu:
+        moe = Dm.MoeficationMoE("moe", d, En, False, Hn, actm, experts_class="execute_all",
+                                add_intermediate_gating=True)
+    else:
+        moe = Dm.MoeficationMoE("moe", d, En, True, Hn, actm, experts_class="custom_kernel")
+    moe.router = Dm.MoeficationRouter(d, En, width=Rn, depth=2, bias=False, activation="relu",
+                                      output_activation="abs")
+    moe = moe.to(torch.bfloat16).cuda()
+    with torch.no_grad():
+        for p in moe.parameters():
+            p.copy_((rn(*p.shape) * 0.02).to(p.dtype))
+    scores = None
+    if given:
+        scores = torch.exp(1.5 * rn(Bn, Sn, En)).bfloat16()
+
+        class Fixed(torch.nn.Module):
+            def forward(self, x):
+                return scores
+        moe.router = Fixed()
+    moe.forward_mode, moe.tau = "dynk_max", 0.1
+    out, gd = moe(x)
+    torch.cuda.synchronize()
+    rt = gd["moe"][0].reshape(n, En)
+    w = moe.last_workspace(n, x.device)
+    w.check_status()
+    # token lists = columns of the routing tensor, ascending
+    off = w.offsets.clone()
+    counts = (rt > 0).sum(0).to(torch.int32)
+    assert int(off[0]) == 0 and torch.equal(off[1:] - off[:-1], counts)
+    for e in (0, En // 3, En - 1):
+        seg = w.token_idx[int(off[e]):int(off[e + 1])]
+        assert torch.equal(seg, torch.nonzero(rt[:, e] > 0).flatten().to(torch.int32))
+    assert (rt.sum(1) >= 1).all()
+    idx = torch.arange(0, n, n // 64)[:64]
+    xs = x.reshape(n, d)[idx.cuda()].cpu()
+    m = rt[idx.cuda()].cpu() > 0
+    sd = {k: v.detach().cpu() for k, v in moe.state_dict().items()}
+    if given:
+        s2 = scores.reshape(n, En)
+        mx = s2.float().max(-1, keepdim=True).values
+        thr = (mx * torch.tensor(np.float32(1.0 - 0.1), device="cuda")).bfloat16().float()
+        assert torch.equal(rt > 0, s2.float() >= thr)               # every token, bit-exact
+    else:
+        s = O.router_scores(xs, sd["router.layers.0.weight"], sd["router.layers.2.weight"])
+        near = O.near_threshold(s, moe.tau, 2.0 ** -7)
+        assert ((m != O.dynk_max_mask(s, moe.tau)) & ~near).sum().item() == 0
+    if glu:
+        ex = O.experts_ffn_exact(xs, m, sd["experts.layers.0.w"], None, sd["experts.layers.1.w"],
+                                 act, sd["experts.layers.2.w"])
+    else:
+        ex = O.experts_ffn_exact(xs, m, sd["experts.w1"], sd["experts.b1"], sd["experts.w2"], act) \
+            + sd["last_bias"].double()
+    assert O.rel_err(out.reshape(n, d)[idx.cuda()].float().cpu(), ex) <= 2e-2
+    # every row was written (no row left at its pre-call contents): all finite and no row of zeros
+    assert torch.isfinite(out.float()).all()

@@ -165,9 +165,9 @@ def test_experts_ffn(c):
 
 @pytest.mark.parametrize("c", all_cases(), ids=case_ids())
 def test_fused_forward_writes_every_row(c):
-    """The one-call layer on an output buffer pre-filled with NaN: the router skips the initial
-    value of rows the expert kernel stores itself (tokens kept by one expert), so a row missed
-    by both sides, or initialised and stored, would show."""
+    """The one-call layer on an output buffer pre-filled with NaN: the router kernel writes every
+    row's initial value (last_bias, plus x with a residual connection) and the expert kernel
+    adds to it, so a row that neither wrote would still hold NaN."""
     from d2dmoe_b200 import ops
     g, t = load_golden(c)
     x2d = dev(t["x"].reshape(c.N, c.d))
@@ -419,3 +419,171 @@ def test_forward_host_matches_forward():
     D.MoeficationMoE.host_synchronize()
     for o in (o1, o2, o3):
         assert O.rel_err(o.float(), ref.float().cpu()) <= TOL["bf16"]
+
+
+DIRECT = ["n197_vit_bf16", "n129_e64", "gelu_bias_res", "e96_h32_bert", "glu_small_bf16",
+          "gemma_shape"]
+
+
+@pytest.mark.parametrize("name", DIRECT)
+def test_experts_module_called_directly(name):
+    """``experts(x2d, routing_tensor)``, the ExpertsLayer interface
+    (architectures/moe/moe_layers.py:174-191), fed the upstream routing tensor: output against
+    the upstream experts output (out_naive has last_bias and the residual added, so they are
+    added here too) and against the fp64 evaluation."""
+    import d2dmoe_b200 as D
+    c = {k.name: k for k in all_cases()}[name]
+    g, t = load_golden(c)
+    act = {"relu": torch.nn.ReLU, "gelu": torch.nn.GELU}[c.act]
+    if c.glu:
+        ex = D.B200GluExperts(c.d, c.E, depth=2, expert_dim=c.H, bias=False, activation=act)
+        sd = {"layers.0.w": t["w1"], "layers.1.w": t["w2"], "layers.2.w": t["w_up"]}
+    else:
+        ex = D.B200KernelExperts(c.d, c.E, depth=2, expert_dim=c.H, bias="without_last",
+                                 activation=act)
+        sd = {"w1": t["w1"], "b1": t["b1"], "w2": t["w2"]}
+    ex = ex.to(c.torch_dtype)
+    ex.load_state_dict(sd, strict=True)
+    ex = ex.cuda()
+    mask = golden_mask(g, c)
+    rt = mask.to(c.torch_dtype).cuda()
+    x2d = t["x"].reshape(c.N, c.d).cuda()
+    out = ex(x2d, rt)
+    out2 = ex(x2d, rt)                                  # cached workspace and packed weights
+    o = out.float().cpu()
+    if not c.glu:
+        o = (o.to(c.torch_dtype) + t["last_bias"]).float()     # what MoeficationMoE.forward adds
+    if c.residual:
+        o = (o.to(c.torch_dtype) + x2d.cpu()).float()
+    rows = torch.from_numpy(g["rows"])
+    ref = torch.from_numpy(g["out_execute_all" if c.glu else "out_naive"])
+    assert O.rel_err(o[rows], ref) <= TOL[c.dtype]
+    assert O.rel_err(o, _exact(c, t, mask)) <= TOL[c.dtype]
+    assert O.rel_err(out2.float().cpu(), out.float().cpu()) <= TOL[c.dtype]
+    with pytest.raises(NotImplementedError):
+        ex.forward_mode = "naive"
+        ex(x2d, rt)
+
+
+@pytest.mark.parametrize("dtype", ["fp32", "bf16"])
+def test_gelu_tanh_activation(dtype):
+    """The tanh form of GELU (what Gemma's own act_fn uses) on both kernel families, against
+    the fp64 evaluation of the same formula."""
+    from d2dmoe_b200 import ops
+    c = C.LayerCase("gelu_tanh", 3, 67, 128, 64, 8, tau=0.4, dtype=dtype, act="gelu_tanh",
+                    glu=(dtype == "bf16"), norm="rms")
+    t = C.make_tensors(c)
+    x2d = t["x"].reshape(c.N, c.d)
+    s = O.router_scores(x2d, t["wa"], t["wb"])
+    mask = O.dynk_max_mask(s, c.tau)
+    wsp = ops.Workspace.allocate(c.N, c.E, "cuda")
+    load_mask(wsp, mask)
+    ops.compact(wsp, c.N, c.E)
+    b1 = None if c.glu else t["b1"]
+    exact = O.experts_ffn_exact(x2d, mask, t["w1"], b1, t["w2"], "gelu_tanh", t.get("w_up"))
+    w1, w2, w_up = dev(t["w1"]), dev(t["w2"]), dev(t.get("w_up"))
+    for packed in (None, ops.prepack_experts(w1, dev(b1), w2, w_up)):
+        out = torch.full((c.N, c.d), float("nan"), dtype=c.torch_dtype, device="cuda")
+        ops.experts_ffn(dev(x2d), wsp, w1, dev(b1), w2, "gelu_tanh", out, w_up=w_up, packed=packed)
+        assert O.rel_err(out.float().cpu(), exact) <= TOL[dtype]
+    wsp.check_status()
+
+
+def test_residual_summation_order_bound():
+    """bf16 layer with a residual connection and inputs of magnitude ~1 against small expert
+    outputs.  Upstream adds the expert sum, then last_bias, then x (one rounding at the
+    magnitude of x); here the output starts as bf16(last_bias + x) and every expert
+    contribution is added to it in bf16, i.e. k+1 roundings at the magnitude of the output.
+    Every element must stay inside that bound around the fp64 value."""
+    from d2dmoe_b200 import ops
+    c = C.LayerCase("res_order", 4, 97, 128, 64, 8, tau=0.6, dtype="bf16", norm="none",
+                    zero_last_bias=False, residual=True, seed=9)
+    t = C.make_tensors(c)
+    x2d = t["x"].reshape(c.N, c.d)
+    wa, wb = dev(t["wa"]), dev(t["wb"])
+    w1, b1, w2 = dev(t["w1"]), dev(t["b1"]), dev(t["w2"])
+    lb = dev(t["last_bias"].reshape(-1))
+    wsp = ops.Workspace.allocate(c.N, c.E, "cuda")
+    out = torch.empty(c.N, c.d, dtype=torch.bfloat16, device="cuda")
+    ops.moe_forward(dev(x2d), wa, wb, c.tau, w1, b1, w2, "relu", out, wsp, last_bias=lb,
+                    add_residual=True, router_packed=ops.prepack_router(wa, wb),
+                    experts_packed=ops.prepack_experts(w1, b1, w2))
+    wsp.check_status()
+    m = O.unpack_mask(bits_of(wsp, c.N), c.E)
+    k = m.sum(-1, keepdim=True).double()
+    assert k.max().item() >= 3                                  # the case must have multi-expert tokens
+    ex = O.experts_ffn_exact(x2d, m, t["w1"], t["b1"], t["w2"]) + t["last_bias"].double() \
+        + x2d.double()
+    err = (out.float().cpu().double() - ex).abs()
+    # unit roundoff of bf16 is 2^-8; partial sums stay within the larger of |x| and |result|
+    mag = torch.maximum(ex.abs(), x2d.double().abs()) + (ex - x2d.double()).abs()
+    bound = (k + 1.0) * 2.0 ** -8 * mag + 2.0 ** -8 * (ex - x2d.double()).abs()
+    assert (err <= bound * 1.5 + 2e-3).all(), float((err / (bound + 1e-12)).max())
+    # and the upstream order (one rounding at the end) is not better than this by more than
+    # the extra k roundings: compare the two max errors
+    up = ((O.experts_ffn_naive(x2d, m, t["w1"], t["b1"], t["w2"]).float()
+           + t["last_bias"].float()).bfloat16().float() + x2d.float()).bfloat16().double()
+    e_up = (up - ex).abs().max().item()
+    assert err.max().item() <= (k.max().item() + 1.0) * max(e_up, 2.0 ** -9)
+
+
+def test_compact_zero_tokens_through_the_c_abi():
+    """N = 0 through both compaction entry points, after a non-empty call that leaves the
+    counts table and the outputs dirty: offsets must come back all zero, status clean."""
+    import ctypes as CT
+    from d2dmoe_b200 import ops, _capi
+    E = 24
+    wsp = ops.Workspace.allocate(1000, E, "cuda")
+    m = torch.rand(1000, E) < 0.2
+    load_mask(wsp, m)
+    ops.compact(wsp, 1000, E)
+    assert int(wsp.offsets[E]) == int(m.sum())
+    p = lambda x: CT.c_void_p(x.data_ptr())                              # noqa: E731
+    st = CT.c_void_p(torch.cuda.current_stream().cuda_stream)
+    for fn in ("d2d_compact", "d2d_compact_noalloc"):
+        wsp.offsets.fill_(77)
+        if fn == "d2d_compact":
+            rc = _capi.lib.d2d_compact(p(wsp.mask_bits), p(wsp.token_idx), p(wsp.offsets), 0, E,
+                                       p(wsp.ws), wsp.ws.numel(), p(wsp.status), st)
+        else:
+            rc = _capi.lib.d2d_compact_noalloc(p(wsp.mask_bits), p(wsp.token_idx), p(wsp.offsets),
+                                               0, E, p(wsp.status), st)
+        assert rc == 0
+        assert torch.equal(wsp.offsets, torch.zeros_like(wsp.offsets)), fn
+        wsp.check_status()
+
+
+def test_bounded_wait_runs_out_and_the_next_launch_is_clean():
+    """A weight tile that never arrives (test hook) makes a bounded device wait run out: the
+    kernel must report D2D_ERR_TIMEOUT in the status word and return, with its tensor memory
+    freed, so that the same call right afterwards, hook off, gives the normal result."""
+    from d2dmoe_b200 import ops, _capi
+    c = C.LayerCase("timeout", 4, 197, 256, 64, 16, tau=0.2, dtype="bf16")
+    t = C.make_tensors(c)
+    x = dev(t["x"].reshape(c.N, c.d))
+    w1, b1, w2 = dev(t["w1"]), dev(t["b1"]), dev(t["w2"])
+    wa, wb, lb = dev(t["wa"]), dev(t["wb"]), dev(t["last_bias"].reshape(-1))
+    rp, ep = ops.prepack_router(wa, wb), ops.prepack_experts(w1, b1, w2)
+    wsp = ops.Workspace.allocate(c.N, c.E, "cuda")
+    out = torch.empty_like(x)
+
+    def call():
+        ops.moe_forward(x, wa, wb, c.tau, w1, b1, w2, c.act, out, wsp, last_bias=lb,
+                        router_packed=rp, experts_packed=ep)
+    call()
+    torch.cuda.synchronize()
+    wsp.check_status()
+    ref = out.clone()
+    try:
+        assert _capi.lib.d2d_debug_configure(12, 1) == 0
+        call()
+        torch.cuda.synchronize()                     # returns: nothing hangs
+        with pytest.raises(_capi.D2DError, match="TIMEOUT"):
+            wsp.check_status()
+    finally:
+        _capi.lib.d2d_debug_configure(0, 0)
+    out.fill_(float("nan"))
+    call()
+    torch.cuda.synchronize()
+    wsp.check_status()
+    assert O.rel_err(out.float().cpu(), ref.float().cpu()) <= TOL["bf16"]

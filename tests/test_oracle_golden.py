@@ -87,3 +87,31 @@ def test_topk_and_dynk_rules_match_upstream_gate(item):
     s = golden_scores(g, c).reshape(c.N, c.E)
     m = O.gate_topk(s, par) if rule == "topk" else O.gate_dynk_cumulative(s, par)
     assert torch.equal(m, O.unpack_mask(bits, c.E))
+
+
+GLU_CASES = [c for c in all_cases() if c.glu]
+
+
+@pytest.mark.parametrize("c", GLU_CASES, ids=[c.name for c in GLU_CASES])
+def test_glu_module_port_matches_upstream_module_experts(c):
+    """The restated sparse CPU path of a gated layer (experts_class='module': one GLUExpert of
+    three nn.Linear per expert) against what the upstream module returned for the same
+    parameters and routing tensor (fixture key out_module)."""
+    g, t = load_golden(c)
+    if "out_module" not in g:
+        pytest.skip("fixture predates the module-experts output")
+    m = golden_mask(g, c)
+    x2d = t["x"].reshape(c.N, c.d)
+    lin = O.glu_module_weights(t["w1"], t["w_up"], t["w2"])
+    out = O.experts_glu_module(x2d, m.to(x2d.dtype), lin, c.act).float()
+    rows = torch.from_numpy(g["rows"])
+    ref = torch.from_numpy(g["out_module"])
+    # same torch CPU calls in the same order on the same bits
+    assert O.rel_err(out[rows], ref) <= (2e-6 if c.dtype == "fp32" else 2.0 ** -7)
+    # and the sparse and dense upstream forms agree with each other within the tolerance
+    assert O.rel_err(ref, torch.from_numpy(g["out_execute_all"])) <= TOL[c.dtype]
+    # whole-layer form used as the timed CPU baseline of the gated configuration
+    p = {"wa": t["wa"], "wb": t["wb"], "lin": lin}
+    out2, rt = O.cpu_layer_forward_module_glu(t["x"], p, c.tau, c.act)
+    near = O.near_threshold(golden_scores(g, c), c.tau, WINDOW[c.dtype])
+    assert (((rt.reshape(c.N, c.E) > 0) != m) & ~near).sum().item() == 0

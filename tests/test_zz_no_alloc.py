@@ -55,6 +55,15 @@ def test_noalloc_matches_workspace_entry_point_twice():
         for e in (0, E // 2, E - 1):                         # and both are the true lists
             assert np.array_equal(idx_b[off_b[e]:off_b[e + 1]],
                                   torch.nonzero(m[:, e]).flatten().numpy())
+    # no tokens at all, right after calls that left the shared table full of counts:
+    # every list is empty, so all E+1 offsets are zero and nothing is reported
+    off = torch.full((E + 1,), 5, dtype=torch.int32, device="cuda")
+    idx = torch.zeros(1, dtype=torch.int32, device="cuda")
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    p = lambda t: C.c_void_p(t.data_ptr())                               # noqa: E731
+    rc = lib.d2d_compact_noalloc(p(bits), p(idx), p(off), 0, E, p(status),
+                                 C.c_void_p(torch.cuda.current_stream().cuda_stream))
+    assert rc == 0 and int(off.abs().sum()) == 0 and int(status.item()) == 0
 
 
 def test_noalloc_rejects_sizes_beyond_its_table():
