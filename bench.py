@@ -1,21 +1,25 @@
 #!/usr/bin/env python
-"""Benchmark of the D2DMoE MoE-FFN layer path: tokens/s vs tau, roofline, CPU baseline.
+"""Benchmark of the D2DMoE MoE-FFN layer path: tokens/s vs tau, roofline, CPU baselines.
 
   python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
 
-Workload (N=1 and every rank of N>1): the 12 converted FFN layers of ViT-B/16 at
-batch 256, bf16: per layer 256*197 = 50432 tokens x d=768, E=24 experts x H=128,
-router 768->128->24.  One "step" is one pass of the layer path over one batch:
-the 12 layers, each on its own input buffer (24 x 77 MB of x/out per step, so the
-inputs exceed the 126 MB L2 and every step streams from HBM).  Weights are
-random-init N(0, 0.02) and inputs are LayerNorm'd N(0,1), both seeded; they stand in
-for the ImageNet batches and trained checkpoints the upstream wall-clock script
+Headline workload: the 12 converted FFN layers of ViT-B/16 at GLOBAL batch 256, bf16:
+per layer 256*197 = 50432 tokens x d=768, E=24 experts x H=128, router 768->128->24.
+One "step" is one pass of the layer path over the batch: the 12 layers, each a
+``MoeficationMoE.forward`` on its own input buffer (12 x 77 MB of x plus as much of
+out per step, so the inputs exceed the 126 MB L2 and every step streams from HBM).
+With N GPUs the batch is split over the ranks (rank r takes images
+shard_bounds(256, N, r); replicated weights, no collective): strong scaling.
+Weights are random-init N(0, 0.02) and inputs are LayerNorm'd N(0,1), both seeded; they
+stand in for the ImageNet batches and trained checkpoints the upstream wall-clock script
 uses (scripts/d2dmoe_vit_wallclock.py:417-442), which are not available offline.
 
 Prints ONE JSON line (rank 0).  `value` is whole-job tokens/s at tau_cfg = 0.9 with
 inputs resident in HBM; `e2e` is the same metric through the module API with host
 buffers (H2D of x and D2H of out inside the timed region); `tau_sweep` repeats the
-device-resident measurement for every tau of the config.
+device-resident measurement for every tau of the config; `configs` (1 GPU only) holds
+the same measurement for all five model configurations, each with the upstream CPU
+path timed beside it.
 """
 from __future__ import annotations
 
@@ -34,14 +38,36 @@ import torch
 ROOT = Path(__file__).resolve().parent
 sys.path.insert(0, str(ROOT))
 
-TAUS = [0.5, 0.7, 0.8, 0.9, 0.95, 1.0]
+HEADLINE = "vit_b16"
 HEADLINE_TAU = 0.9
-LAYERS, BATCH, SEQ, D, H, E, R = 12, 256, 197, 768, 128, 24, 128
-# dram__bytes_read.sum + dram__bytes_write.sum of one expert-kernel launch of this workload at
-# tau_cfg 0.9 (177.2 + 30.9 MB), from the ncu capture summarised in
-# profiles/mlp_tiles_kernels_vit_b16_tau0.9.md
-NCU_EXPERTS_TRAFFIC_BYTES = 208.11e6
+# dram__bytes_read.sum + dram__bytes_write.sum of one expert-kernel launch of the headline
+# workload at tau_cfg 0.9, from an ncu capture of that launch (None = no capture of the
+# current kernel yet)
+NCU_EXPERTS_TRAFFIC_BYTES = None
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
+
+BF16, FP32 = torch.bfloat16, torch.float32
+# The five model configurations of the layer path (per MoE-FFN layer).  `scores`: the router
+# is replaced by a seeded log-normal(0, 1.5) score tensor.  `cpu_tokens`: tokens of the CPU
+# baseline's sample layer (None = the full layer).
+CONFIGS = {
+    "vit_layer_fp32": dict(layers=1, B=8, S=197, d=768, H=128, E=24, R=128, dtype=FP32,
+                           act="relu", glu=False, norm="layer", scores=False, taus=[0.9],
+                           cpu_tokens=None),
+    "vit_b16": dict(layers=12, B=256, S=197, d=768, H=128, E=24, R=128, dtype=BF16, act="relu",
+                    glu=False, norm="layer", scores=False,
+                    taus=[0.5, 0.7, 0.8, 0.9, 0.95, 1.0], cpu_tokens=None),
+    "gpt2_small": dict(layers=12, B=32, S=1024, d=768, H=128, E=24, R=128, dtype=BF16,
+                       act="relu", glu=False, norm="layer", scores=True, taus=[0.8, 0.9, 0.95],
+                       cpu_tokens=None),
+    "bert_base_96x32": dict(layers=12, B=512, S=128, d=768, H=32, E=96, R=128, dtype=BF16,
+                            act="relu", glu=False, norm="layer", scores=False, taus=[0.9],
+                            cpu_tokens=None),
+    "gemma_2b_geglu": dict(layers=18, B=64, S=2048, d=2048, H=128, E=128, R=256, dtype=BF16,
+                           act="gelu", glu=True, norm="rms", scores=False, taus=[0.9],
+                           cpu_tokens=8192),
+}
+ACT = {"relu": torch.nn.ReLU, "gelu": torch.nn.GELU}
 
 
 def peaks():
@@ -55,24 +81,24 @@ def peaks():
     return d
 
 
-# --------------------------------------------------------------------------- inputs
-def make_layer_tensors(layer: int, batch: int, device, dtype=torch.bfloat16):
-    """Seeded tensors of one layer, drawn on the device in fp32 and cast (the parity
-    tests use the CPU generator; the benchmark only needs the same distributions)."""
-    g = torch.Generator(device=device).manual_seed(1000 + layer)
-    rn = lambda *s: torch.randn(*s, generator=g, device=device)            # noqa: E731
-    x = torch.nn.functional.layer_norm(rn(batch, SEQ, D), (D,))
-    t = dict(x=x, w1=rn(E, D, H) * 0.02, b1=rn(E, H) * 0.02, w2=rn(E, H, D) * 0.02,
-             wa=rn(R, D) * 0.02, wb=rn(E, R) * 0.02, last_bias=torch.zeros(1, D, device=device))
-    return {k: v.to(dtype).contiguous() for k, v in t.items()}
+def algorithmic(c, n_tokens: int, sum_c: float):
+    """Algorithmic work of one layer call: selected-expert FLOPs and the bytes that must
+    move (x read once, out written once, every weight read once)."""
+    s = 4 if c["dtype"] == FP32 else 2
+    G = 2 if c["glu"] else 1
+    d, H, E, R = c["d"], c["H"], c["E"], c["R"]
+    flops = 2 * d * H * (G + 1) * sum_c
+    w = s * ((G + 1) * E * d * H + (0 if c["glu"] else E * H + d) + d * R + R * E)
+    return flops, 2 * n_tokens * d * s + w
 
 
-def algorithmic(n_tokens: int, sum_c: int, s: int = 2):
-    """Algorithmic work of one layer call: selected-expert FLOPs and the bytes that
-    must move (x read once, out written once, every weight read once)."""
-    flops = 2 * D * H * 2 * sum_c
-    w = s * (2 * E * D * H + E * H + D + D * R + R * E)
-    return flops, 2 * n_tokens * D * s + w
+def t_roof(c, n_tokens, sum_c, pk):
+    fl, by = algorithmic(c, n_tokens, sum_c)
+    t_hbm = by / (pk["hbm_gbs"] * 1e9)
+    if c["dtype"] == FP32:      # no fp32 tensor peak is measured: HBM bound only
+        return t_hbm, "hbm"
+    t_tc = fl / (pk["bf16_tflops_sustained"] * 1e12)
+    return (t_tc, "tensor") if t_tc >= t_hbm else (t_hbm, "hbm")
 
 
 # --------------------------------------------------------------------------- clocks
@@ -122,39 +148,150 @@ class ClockSampler:
 
 
 # --------------------------------------------------------------------------- ours
-class LayerState:
-    def __init__(self, layer, batch, device):
-        from d2dmoe_b200 import ops
-        self.t = make_layer_tensors(layer, batch, device)
-        self.x2d = self.t["x"].reshape(-1, D)
-        self.n = self.x2d.shape[0]
-        self.out = torch.empty_like(self.x2d)
-        self.wsp = ops.Workspace.allocate(self.n, E, device)
-        self.lb = self.t["last_bias"].reshape(-1)
-        self.rp = ops.prepack_router(self.t["wa"], self.t["wb"])
-        self.ep = ops.prepack_experts(self.t["w1"], self.t["b1"], self.t["w2"])
+class Stack:
+    """The MoE-FFN layers of one configuration on one device: a module per layer (seeded
+    weights) and the layer inputs.  Large configurations rotate through `nbuf` distinct
+    input buffers (every buffer set is larger than L2 in total)."""
 
-    def forward(self, tau):
-        from d2dmoe_b200 import ops
-        t = self.t
-        ops.moe_forward(self.x2d, t["wa"], t["wb"], tau, t["w1"], t["b1"], t["w2"], "relu",
-                        self.out, self.wsp, last_bias=self.lb, router_packed=self.rp,
-                        experts_packed=self.ep)
+    def __init__(self, name, batch, device, layers=None, seed0=1000):
+        import d2dmoe_b200 as Dm
+        c = CONFIGS[name]
+        self.c, self.name = c, name
+        self.layers = layers or c["layers"]
+        d, H, E, R, dt = c["d"], c["H"], c["E"], c["R"], c["dtype"]
+        self.n = batch * c["S"]
+        es = 4 if dt == FP32 else 2
+        per_x = self.n * d * es
+        nbuf = max(1, min(self.layers, max(4, int(2.0e9 // max(per_x, 1)))))
+        nbuf = min(nbuf, self.layers)
+        self.mods, self.x, self.scores = [], [], []
+        for l in range(self.layers):
+            g = torch.Generator(device=device).manual_seed(seed0 + l)
+            rn = lambda *s: torch.randn(*s, generator=g, device=device)        # noqa: E731
+            if l < nbuf:
+                x = rn(batch, c["S"], d)
+                if c["norm"] == "layer":
+                    x = torch.nn.functional.layer_norm(x, (d,))
+                else:
+                    x = x * torch.rsqrt(x.pow(2).mean(-1, keepdim=True) + 1e-6)
+                self.x.append(x.to(dt).contiguous())
+                if c["scores"]:
+                    self.scores.append(torch.exp(1.5 * rn(batch, c["S"], E)).to(dt))
+            if c["glu"]:
+                m = Dm.MoeficationMoE("moe", d, E, False, H, ACT[c["act"]],
+                                      experts_class="execute_all", add_intermediate_gating=True)
+            else:
+                m = Dm.MoeficationMoE("moe", d, E, True, H, ACT[c["act"]],
+                                      experts_class="custom_kernel")
+            m.router = Dm.MoeficationRouter(d, E, width=R, depth=2, bias=False, activation="relu",
+                                            output_activation="abs")
+            m = m.to(dt).to(device)
+            with torch.no_grad():
+                for nme, p in m.named_parameters():
+                    if nme == "last_bias":
+                        p.zero_()
+                    else:
+                        p.copy_((rn(*p.shape) * 0.02).to(dt))
+            if c["scores"]:
+                m.router = _FixedScores(self.scores[l % nbuf])
+            m.forward_mode = "dynk_max"
+            self.mods.append(m)
+        self.nbuf = nbuf
 
-    def staged(self, tau, ev):
-        """Same work as forward() through the per-stage entry points, with CUDA events
-        between the stages (per-kernel durations for the roofline object)."""
+    def set_tau(self, tau_cfg):
+        for m in self.mods:
+            m.tau = 1.0 - tau_cfg
+
+    def step(self):
+        for l, m in enumerate(self.mods):
+            m(self.x[l % self.nbuf])
+
+    def graphed(self):
+        """The step captured once in a CUDA graph (the module forwards issue no host
+        synchronisation and take their temporaries from the graph's pool); returns the
+        replay callable, or None when capture is not possible."""
+        try:
+            side = torch.cuda.Stream(self.x[0].device)
+            side.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(side):
+                self.step()
+                side.synchronize()
+                g = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(g, stream=side):
+                    self.step()
+            torch.cuda.current_stream().wait_stream(side)
+            torch.cuda.synchronize()
+            self._graph = g
+            return g.replay
+        except Exception as exc:      # noqa: BLE001
+            print(f"# CUDA graph capture failed, timing eager launches: {exc}", file=sys.stderr)
+            return None
+
+    def sum_c(self):
+        """Selected token-expert pairs per layer of the last step (from the offsets the
+        compaction left in each module's workspace)."""
+        E = self.c["E"]
+        dev = self.x[0].device
+        return [int(m.last_workspace(self.n, dev).offsets[E].item()) for m in self.mods]
+
+    def launches_per_layer(self):
+        from d2dmoe_b200 import _capi
+        return int(_capi.lib.d2d_last_forward_launches()) + 1     # + the routing-tensor expand
+
+    def staged(self, l, ev):
+        """Layer l through the per-stage entry points with CUDA events between the stages
+        (per-kernel durations)."""
         from d2dmoe_b200 import ops
-        t = self.t
+        c, m = self.c, self.mods[l]
+        x2d = self.x[l % self.nbuf].reshape(self.n, c["d"])
+        p = m.experts.kernel_params()
+        wsp = m.last_workspace(self.n, x2d.device)
+        lb = m.last_bias.view(-1) if m.bias else None
+        out = self._out
         ev[0].record()
-        ops.router_mask(self.x2d, t["wa"], t["wb"], tau, self.wsp, packed=self.rp,
-                        last_bias=self.lb, out_init=self.out)
+        if c["scores"]:
+            ops.mask_from_scores(self.scores[l % self.nbuf].reshape(self.n, c["E"]), m.tau, wsp)
+            ops.init_out(x2d, lb, False, out)
+        else:
+            ops.router_mask(x2d, m.router.layers[0].weight, m.router.layers[2].weight, m.tau, wsp,
+                            packed=m.router.packed(), last_bias=lb, out_init=out)
         ev[1].record()
-        ops.compact(self.wsp, self.n, E)
+        ops.compact(wsp, self.n, c["E"])
         ev[2].record()
-        ops.experts_ffn(self.x2d, self.wsp, t["w1"], t["b1"], t["w2"], "relu", self.out,
-                        packed=self.ep, accumulate=True)
+        ops.experts_ffn(x2d, wsp, p["w1"], p["b1"], p["w2"], p["act"], out, w_up=p["w_up"],
+                        packed=m.experts.packed(), accumulate=True)
         ev[3].record()
+
+    def stage_times(self, reps):
+        c = self.c
+        self._out = torch.empty(self.n, c["d"], dtype=c["dtype"], device=self.x[0].device)
+        evs = [[torch.cuda.Event(enable_timing=True) for _ in range(4)]
+               for _ in range(self.layers)]
+        tot = [0.0, 0.0, 0.0]
+        for r in range(reps + 2):
+            for l in range(self.layers):
+                self.staged(l, evs[l])
+            torch.cuda.synchronize()
+            if r >= 2:
+                for ev in evs:
+                    for i in range(3):
+                        tot[i] += ev[i].elapsed_time(ev[i + 1])
+        n = reps * self.layers
+        del self._out
+        return {"router_mask": tot[0] * 1e3 / n, "compact": tot[1] * 1e3 / n,
+                "experts_ffn": tot[2] * 1e3 / n}, n
+
+
+class _FixedScores(torch.nn.Module):
+    """Router stand-in that returns a given score tensor (the mechanism of upstream's own
+    override hook, architectures/moe/moefication.py:331-339)."""
+
+    def __init__(self, s):
+        super().__init__()
+        self.s = s
+
+    def forward(self, x):
+        return self.s
 
 
 def timed(fn, steps, warmup, dist=None, quantiles=None):
@@ -166,7 +303,8 @@ def timed(fn, steps, warmup, dist=None, quantiles=None):
     if dist is not None:
         dist.barrier()
     torch.cuda.synchronize()
-    ev = [torch.cuda.Event(enable_timing=True) for _ in range(steps + 1 if quantiles is not None else 2)]
+    ev = [torch.cuda.Event(enable_timing=True)
+          for _ in range(steps + 1 if quantiles is not None else 2)]
     ev[0].record()
     for i in range(steps):
         fn()
@@ -188,110 +326,142 @@ def timed(fn, steps, warmup, dist=None, quantiles=None):
     return ms
 
 
-def sample_check(layers, tau):
+def sample_check(stack, tau_cfg):
     """Sanity check of the timed path on a token sample of layer 0, in plain tensor
     arithmetic on the host: the rule applied to fp32-accumulated, bf16-rounded router
-    scores, and the output as an fp64 sum over the experts the kernel selected."""
+    scores, and the output as an fp64 sum over the experts the layer selected."""
     import numpy as np
-    L = layers[0]
-    L.forward(1.0 - tau)
+    c, m = stack.c, stack.mods[0]
+    d, E = c["d"], c["E"]
+    x = stack.x[0]
+    out, gd = m(x)
     torch.cuda.synchronize()
-    idx = torch.arange(0, L.n, max(1, L.n // 96))[:96]
-    t = {k: v.cpu() for k, v in L.t.items()}
-    x = t["x"].reshape(-1, D)[idx]
+    n = stack.n
+    idx = torch.arange(0, n, max(1, n // 96))[:96]
+    sd = {k: v.detach().float().cpu() for k, v in m.state_dict().items()}
+    xs = x.reshape(n, d)[idx.cuda()].cpu()
     bf = lambda v: v.to(torch.bfloat16).float()                              # noqa: E731
-    h = torch.relu(bf(x.float() @ t["wa"].float().t()))
-    s = bf(h @ t["wb"].float().t()).abs()
+    h = torch.relu(bf(xs.float() @ sd["router.layers.0.weight"].t()))
+    s = bf(h @ sd["router.layers.2.weight"].t()).abs()
     mx = s.max(-1, keepdim=True).values
-    mult = torch.tensor(np.float32(1.0 - (1.0 - tau)))
+    mult = torch.tensor(np.float32(1.0 - (1.0 - tau_cfg)))
     thr = bf(mx * mult)
-    m = s >= thr
+    mref = s >= thr
     near = (s - mx * mult).abs() <= 2.0 ** -7 * mx
-    words = L.wsp.mask_bits[: L.n].cpu()[idx, 0].to(torch.int64) & 0xFFFFFFFF
-    mg = ((words.unsqueeze(1) >> torch.arange(E)) & 1).bool()
-    ex = torch.zeros(len(idx), D, dtype=torch.float64)
+    mg = gd["moe"][0].reshape(n, E)[idx.cuda()].cpu() > 0
+    ex = torch.zeros(len(idx), d, dtype=torch.float64)
     for e in range(E):
         r = mg[:, e].nonzero().flatten()
         if len(r):
-            hh = torch.relu(x[r].double() @ t["w1"][e].double() + t["b1"][e].double())
-            ex[r] += hh @ t["w2"][e].double()
-    ex += t["last_bias"].double()
-    got = L.out.cpu()[idx].double()
+            hh = torch.relu(xs[r].double() @ sd["experts.w1"][e].double()
+                            + sd["experts.b1"][e].double())
+            ex[r] += hh @ sd["experts.w2"][e].double()
+    ex += sd["last_bias"].double()
+    got = out.reshape(n, d)[idx.cuda()].cpu().double()
     err = float((got - ex).abs().max() / ex.abs().max())
-    return {"tokens": int(len(idx)), "mask_mismatch_outside_window": int(((m != mg) & ~near).sum()),
+    return {"tokens": int(len(idx)),
+            "mask_mismatch_outside_window": int(((mref != mg) & ~near).sum()),
             "out_rel_err": err, "tol": 2e-2}
 
 
-def cpu_baseline_layer(reps=5, warmup=2):
-    """The upstream CPU path ('naive' experts, all host threads) on ONE full-size
-    layer (50432 tokens, 1 of the 12), fp32 and bf16; the faster one is reported."""
-    from oracle import d2d_oracle as O
-    torch.set_num_threads(os.cpu_count() or 1)
-    g = torch.Generator().manual_seed(0)
+# --------------------------------------------------------------------------- CPU baselines
+def _cpu_tensors(c, n_tokens, seed=0):
+    g = torch.Generator().manual_seed(seed)
     rn = lambda *s: torch.randn(*s, generator=g)                           # noqa: E731
-    x = torch.nn.functional.layer_norm(rn(BATCH, SEQ, D), (D,))
-    p = dict(w1=rn(E, D, H) * 0.02, b1=rn(E, H) * 0.02, w2=rn(E, H, D) * 0.02,
-             wa=rn(R, D) * 0.02, wb=rn(E, R) * 0.02, last_bias=torch.zeros(1, D))
+    d, H, E, R = c["d"], c["H"], c["E"], c["R"]
+    x = rn(n_tokens, d)
+    if c["norm"] == "layer":
+        x = torch.nn.functional.layer_norm(x, (d,))
+    else:
+        x = x * torch.rsqrt(x.pow(2).mean(-1, keepdim=True) + 1e-6)
+    p = dict(w1=rn(E, d, H) * 0.02, w2=rn(E, H, d) * 0.02, wa=rn(R, d) * 0.02,
+             wb=rn(E, R) * 0.02)
+    if c["glu"]:
+        p["w_up"] = rn(E, d, H) * 0.02
+    else:
+        p["b1"] = rn(E, H) * 0.02
+        p["last_bias"] = torch.zeros(1, d)
+    sc = torch.exp(1.5 * rn(n_tokens, E)) if c["scores"] else None
+    return x, p, sc
+
+
+def cpu_baseline(name, tau_cfg, budget_s=6.0, reps=5, warmup=1):
+    """The upstream CPU path on ONE layer of the configuration with every host thread:
+    'naive' experts (moe_layers.py:200-211) for the two-layer configurations, the 'module'
+    experts with GLUExpert (moe_layers.py:104-113,310-324) for the gated one; fp32 and the
+    configuration's own dtype, the faster one reported."""
+    from oracle import d2d_oracle as O
+    c = CONFIGS[name]
+    torch.set_num_threads(os.cpu_count() or 1)
+    n_full = c["B"] * c["S"]
+    n = c["cpu_tokens"] or n_full
+    x, p, sc = _cpu_tensors(c, n)
+    tau = 1.0 - tau_cfg
     best = None
-    for dt, name in ((torch.float32, "fp32"), (torch.bfloat16, "bf16")):
+    dts = [(FP32, "fp32")] + ([(BF16, "bf16")] if c["dtype"] == BF16 else [])
+    for dt, nm in dts:
         xx = x.to(dt)
         pp = {k: v.to(dt) for k, v in p.items()}
-        ts = []
+        ss = None if sc is None else sc.to(dt)
+        if c["glu"]:
+            pp["lin"] = O.glu_module_weights(pp["w1"], pp["w_up"], pp["w2"])
+            run = lambda: O.cpu_layer_forward_module_glu(xx, pp, tau, c["act"])     # noqa: E731
+        else:
+            run = lambda: O.cpu_layer_forward_naive(xx, pp, tau, c["act"], scores=ss)  # noqa: E731
+        ts, t_start = [], time.perf_counter()
         for i in range(warmup + reps):
             t0 = time.perf_counter()
-            O.cpu_layer_forward_naive(xx, pp, 1.0 - HEADLINE_TAU)
+            run()
             if i >= warmup:
                 ts.append(time.perf_counter() - t0)
-            if sum(ts) > 12:
+            if time.perf_counter() - t_start > budget_s and ts:
                 break
         med = statistics.median(ts)
         if best is None or med < best[0]:
-            best = (med, name)
-    n = BATCH * SEQ
+            best = (med, nm, len(ts))
+    scaled = "" if n == n_full else f" (a {n}-token sample of the {n_full}-token layer; tokens/s scales linearly in tokens)"
     return {"value": n / best[0], "unit": "tokens/s", "cores": torch.get_num_threads(),
             "kind": "port",
-            "sample": f"1 of 12 layers at full size ({n} tokens), tau_cfg {HEADLINE_TAU}, "
-                      f"{best[1]} (faster of fp32/bf16), median of runs, torch CPU ops in the "
-                      f"upstream 'naive' order"}
+            "sample": f"1 of {c['layers']} layers, {n} tokens{scaled}, tau_cfg {tau_cfg}, "
+                      f"{best[1]} (faster of fp32/{'bf16' if c['dtype'] == BF16 else 'fp32'}), "
+                      f"median of {best[2]} runs, torch CPU ops in the upstream "
+                      f"{'module (GLUExpert)' if c['glu'] else 'naive'} order"}
 
 
 def run_reference(args):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
-    steps, warmup = max(1, args.steps), max(1, min(args.warmup, 3))
+    steps, warmup = max(1, min(args.steps, 20)), max(1, min(args.warmup, 3))
     from oracle import d2d_oracle as O
+    c = CONFIGS[HEADLINE]
     torch.set_num_threads(os.cpu_count() or 1)
-    g = torch.Generator().manual_seed(0)
-    rn = lambda *s: torch.randn(*s, generator=g)                           # noqa: E731
-    x = torch.nn.functional.layer_norm(rn(BATCH, SEQ, D), (D,))
-    p = dict(w1=rn(E, D, H) * 0.02, b1=rn(E, H) * 0.02, w2=rn(E, H, D) * 0.02,
-             wa=rn(R, D) * 0.02, wb=rn(E, R) * 0.02, last_bias=torch.zeros(1, D))
-    steps = min(steps, 20)
+    n = c["B"] * c["S"]
+    x, p, _ = _cpu_tensors(c, n)
+    tau = 1.0 - HEADLINE_TAU
     # upstream runs its CPU path in the model's dtype; take the faster of fp32 and bf16 here
     probe = {}
-    for dtp, nm in ((torch.float32, "fp32"), (torch.bfloat16, "bf16")):
+    for dtp, nm in ((FP32, "fp32"), (BF16, "bf16")):
         xx, pp = x.to(dtp), {k: v.to(dtp) for k, v in p.items()}
-        O.cpu_layer_forward_naive(xx, pp, 1.0 - HEADLINE_TAU)
+        O.cpu_layer_forward_naive(xx, pp, tau)
         t0 = time.perf_counter()
-        O.cpu_layer_forward_naive(xx, pp, 1.0 - HEADLINE_TAU)
+        O.cpu_layer_forward_naive(xx, pp, tau)
         probe[nm] = (time.perf_counter() - t0, xx, pp)
     ref_dtype = min(probe, key=lambda k: probe[k][0])
     _, x, p = probe[ref_dtype]
     for _ in range(warmup):
-        O.cpu_layer_forward_naive(x, p, 1.0 - HEADLINE_TAU)
+        O.cpu_layer_forward_naive(x, p, tau)
     t0 = time.perf_counter()
     for _ in range(steps):
-        O.cpu_layer_forward_naive(x, p, 1.0 - HEADLINE_TAU)
+        O.cpu_layer_forward_naive(x, p, tau)
     dt = time.perf_counter() - t0
-    n = BATCH * SEQ
     v = n * steps / dt
     sample = (f"each step = 1 of the 12 layers at full size ({n} tokens), {ref_dtype}, tau_cfg "
               f"{HEADLINE_TAU}; upstream CPU path ('naive' experts) restated in torch CPU ops")
     print(json.dumps({
         "impl": "reference", "metric": "moe_ffn_layer_tokens_per_s", "value": v, "unit": "tokens/s",
         "n_gpus": args.gpus, "steps": steps, "warmup": warmup, "ms_per_step": 1e3 * dt / steps,
-        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": ref_dtype,
+        "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": ref_dtype,
         "data": "synthetic", "config": workload_config(args.gpus),
         "cpu_baseline": {"value": v, "unit": "tokens/s", "cores": torch.get_num_threads(),
                          "kind": "port", "sample": sample},
@@ -300,42 +470,91 @@ def run_reference(args):
 
 
 def workload_config(n_gpus):
-    return {"workload": "vit_b16_moe_ffn_12layers_batch256_bf16", "layers": LAYERS,
-            "tokens_per_layer_per_gpu": BATCH * SEQ, "global_batch": BATCH * n_gpus,
-            "seq_len": SEQ, "d": D, "experts": E, "expert_dim": H, "router_width": R,
-            "tau_cfg": HEADLINE_TAU, "parallelism": f"batch-sharded x{n_gpus}, no collective",
-            "l2": "inputs larger than L2 (24 x 77 MB of x/out per step)"}
+    c = CONFIGS[HEADLINE]
+    return {"workload": "vit_b16_moe_ffn_12layers_batch256_bf16", "layers": c["layers"],
+            "global_batch": c["B"], "tokens_per_layer": c["B"] * c["S"],
+            "seq_len": c["S"], "d": c["d"], "experts": c["E"], "expert_dim": c["H"],
+            "router_width": c["R"], "tau_cfg": HEADLINE_TAU,
+            "parallelism": f"batch 256 split over {n_gpus} GPU(s), replicated weights, no collective",
+            "l2": "inputs larger than L2 (12 distinct 77 MB inputs and as much output per step)"}
+
+
+def copy_ceiling(stack, steps, dist):
+    """Plain pinned H2D + D2H of the bytes one e2e step moves (x of every layer in, out of
+    every layer out), one cudaMemcpyAsync per layer and direction on two streams, no
+    kernels: what the host links allow on this box with every rank copying at once."""
+    dev = stack.x[0].device
+    hx = stack.x[0].cpu().pin_memory()
+    ho = torch.empty_like(hx).pin_memory()
+    dx = [torch.empty_like(stack.x[0]) for _ in range(2)]
+    s_in, s_out = torch.cuda.Stream(dev), torch.cuda.Stream(dev)
+
+    def step():
+        for l in range(stack.layers):
+            with torch.cuda.stream(s_in):
+                dx[l & 1].copy_(hx, non_blocking=True)
+            with torch.cuda.stream(s_out):
+                ho.copy_(dx[(l + 1) & 1], non_blocking=True)
+        s_in.synchronize()
+        s_out.synchronize()
+
+    for _ in range(2):
+        step()
+    if dist is not None:
+        dist.barrier()
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        step()
+    dt = time.perf_counter() - t0
+    if dist is not None:
+        t = torch.tensor([dt], device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        dt = float(t.item())
+    return dt / steps
 
 
 def run_ours(args):
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
     local = int(os.environ.get("LOCAL_RANK", "0"))
+    # each rank stays on the cores nearest in index to its GPU's share of the host, so that
+    # its pinned buffers are first touched (and later copied) from there
+    try:
+        ncpu = os.cpu_count() or 1
+        if world > 1 and ncpu >= 2 * world:
+            per = ncpu // world
+            os.sched_setaffinity(0, set(range(local * per, (local + 1) * per)))
+    except (AttributeError, OSError):
+        pass
     torch.cuda.set_device(local)
     dist = None
     if world > 1:
         import torch.distributed as dist_mod
         dist_mod.init_process_group("nccl", device_id=torch.device("cuda", local))
         dist = dist_mod
-    import d2dmoe_b200  # noqa: F401  (raises if the CUDA library is missing)
+    import d2dmoe_b200 as Dm
+    from d2dmoe_b200.sharding import shard_bounds
     dev = torch.device("cuda", local)
-    layers = [LayerState(l, BATCH, dev) for l in range(LAYERS)]
-    n_layer = layers[0].n
-    tokens_step = n_layer * LAYERS
+    c = CONFIGS[HEADLINE]
+    lo, hi = shard_bounds(c["B"], world, rank)
+    stack = Stack(HEADLINE, hi - lo, dev, layers=args.layers)
+    stack.set_tau(HEADLINE_TAU)
+    n_layer_global = c["B"] * c["S"]
+    tokens_step_global = n_layer_global * stack.layers
     pk = peaks()
     steps, warmup = args.steps, max(3, args.warmup)
 
-    def step(tau_mod):
-        for L in layers:
-            L.forward(tau_mod)
-
-    # ---- headline: tau_cfg 0.9, device-resident ---------------------------------
+    # ---- headline: tau_cfg 0.9, device-resident, module forward -------------------
     sampler = ClockSampler(local) if rank == 0 else None
     step_q = {}
-    ms = timed(lambda: step(1.0 - HEADLINE_TAU), steps, warmup, dist, quantiles=step_q)
-    value = world * tokens_step * steps / (ms * 1e-3)
-    from d2dmoe_b200 import _capi
-    launches_per_call = int(_capi.lib.d2d_last_forward_launches())   # as the library counted
+    stack.step()
+    launches_per_layer = stack.launches_per_layer()
+    ms_eager = timed(stack.step, max(2, min(steps, 20)), warmup, dist) / max(2, min(steps, 20))
+    replay = None if args.eager else stack.graphed()
+    run_step = replay or stack.step
+    ms = timed(run_step, steps, warmup, dist, quantiles=step_q)
+    value = tokens_step_global * steps / (ms * 1e-3)
     if args.quick:
         clocks = sampler.stop() if sampler else None
         if dist is not None:
@@ -343,46 +562,40 @@ def run_ours(args):
         if rank == 0:
             print(json.dumps({"metric": "moe_ffn_layer_tokens_per_s", "value": value,
                               "unit": "tokens/s", "ms_per_step": ms / steps, "quick": True,
-                              "layers": LAYERS, "tau_cfg": HEADLINE_TAU, "clocks": clocks}))
+                              "eager_ms_per_step": ms_eager, "graph": replay is not None,
+                              "layers": stack.layers, "tau_cfg": HEADLINE_TAU, "clocks": clocks}))
         return
 
     # ---- tau sweep ----------------------------------------------------------------
     sweep = []
     sw_steps = max(2, min(steps, 5))
-    for tau in TAUS:
-        tm = timed(lambda: step(1.0 - tau), sw_steps, 3, dist)
-        sum_c = [int(L.wsp.offsets[E].item()) for L in layers]
-        t_roof = 0.0
-        for sc in sum_c:
-            fl, by = algorithmic(n_layer, sc)
-            t_roof += max(fl / (pk["bf16_tflops_sustained"] * 1e12), by / (pk["hbm_gbs"] * 1e9))
+    for tau in c["taus"]:
+        stack.set_tau(tau)
+        fn = (None if args.eager else stack.graphed()) or stack.step
+        tm = timed(fn, sw_steps, 3, dist)
+        sum_c = stack.sum_c()
+        if dist is not None:      # pairs over all ranks
+            t = torch.tensor(sum_c, dtype=torch.float64, device="cuda")
+            dist.all_reduce(t)
+            sum_c = t.tolist()
+        troof = sum(t_roof(c, n_layer_global, sc, pk)[0] for sc in sum_c) / world
         per_step = tm * 1e-3 / sw_steps
-        sweep.append({"tau_cfg": tau, "mean_k": sum(sum_c) / (LAYERS * n_layer),
-                      "tokens_per_s": world * tokens_step / per_step,
-                      "ms_per_step": per_step * 1e3, "roofline_ms_per_step": t_roof * 1e3,
-                      "roofline_frac": t_roof / per_step})
+        sweep.append({"tau_cfg": tau, "mean_k": sum(sum_c) / (stack.layers * n_layer_global),
+                      "tokens_per_s": tokens_step_global / per_step,
+                      "ms_per_step": per_step * 1e3, "roofline_ms_per_step": troof * 1e3,
+                      "roofline_frac": troof / per_step,
+                      "bound": t_roof(c, n_layer_global, sum_c[0], pk)[1]})
+    stack.set_tau(HEADLINE_TAU)
+    stack.step()
+    head = next(s for s in sweep if s["tau_cfg"] == HEADLINE_TAU)
 
     # ---- per-kernel durations at the headline tau (CUDA events between stages) ----
-    tau_mod = 1.0 - HEADLINE_TAU
-    evs = [[torch.cuda.Event(enable_timing=True) for _ in range(4)] for _ in layers]
-    stage_ms = [0.0, 0.0, 0.0]
-    reps = max(2, min(steps, 5))
-    for _ in range(2):
-        for L, ev in zip(layers, evs):
-            L.staged(tau_mod, ev)
-    torch.cuda.synchronize()
-    for _ in range(reps):
-        for L, ev in zip(layers, evs):
-            L.staged(tau_mod, ev)
-        torch.cuda.synchronize()
-        for ev in evs:
-            for i in range(3):
-                stage_ms[i] += ev[i].elapsed_time(ev[i + 1])
-    launches = reps * LAYERS
-    ffn_s = stage_ms[2] * 1e-3 / launches
-    sum_c = sum(int(L.wsp.offsets[E].item()) for L in layers) / LAYERS
-    fl, _ = algorithmic(n_layer, int(sum_c))
-    ffn_bytes = 2 * n_layer * D * 2 + 2 * (2 * E * D * H + E * H)
+    stage_us, launches = stack.stage_times(max(2, min(steps, 5)))
+    ffn_s = stage_us["experts_ffn"] * 1e-6
+    sum_c_local = sum(stack.sum_c()) / stack.layers
+    n_local = stack.n
+    fl, _ = algorithmic(c, n_local, sum_c_local)
+    ffn_bytes = 2 * n_local * c["d"] * 2 + 2 * (2 * c["E"] * c["d"] * c["H"] + c["E"] * c["H"])
     t_tensor = fl / (pk["bf16_tflops_sustained"] * 1e12)
     t_hbm = ffn_bytes / (pk["hbm_gbs"] * 1e9)
     if t_tensor >= t_hbm:
@@ -392,52 +605,83 @@ def run_ours(args):
         roof = {"bound": "hbm", "achieved": ffn_bytes / ffn_s / 1e9, "peak": pk["hbm_gbs"],
                 "unit": "GB/s"}
     roof["frac"] = roof["achieved"] / roof["peak"]
-    roof.update({"kernel": "experts_ffn (mlp_tiles_kernel<EXPERTS>)",
-                 "traffic": NCU_EXPERTS_TRAFFIC_BYTES
-                 if (LAYERS == 12 and HEADLINE_TAU == 0.9 and BATCH == 256) else None, "peak_source": pk["source"],
-                 "avg_launch_us": ffn_s * 1e6, "launches_timed": launches,
+    roof.update({"kernel": "experts_ffn (expert FFN tile kernel)",
+                 "traffic": NCU_EXPERTS_TRAFFIC_BYTES if (world == 1 and stack.layers == 12) else None,
+                 "peak_source": pk["source"], "avg_launch_us": ffn_s * 1e6,
+                 "launches_timed": launches, "tokens_per_launch": n_local,
                  "algorithmic_bytes_per_launch": ffn_bytes, "algorithmic_flops_per_launch": fl,
-                 "stage_us_per_layer": {"router_mask": stage_ms[0] * 1e3 / launches,
-                                        "compact": stage_ms[1] * 1e3 / launches,
-                                        "experts_ffn": stage_ms[2] * 1e3 / launches}})
-    # the sampler covered the headline region, the sweep and the stage timing: the same
-    # kernels on the same buffers, all of it timed device work
+                 "stage_us_per_layer": stage_us})
     clocks = sampler.stop() if sampler else None
-    head = next(s for s in sweep if s["tau_cfg"] == HEADLINE_TAU)
+
+    # ---- replicas (weak scaling): every rank on the whole batch of 256 --------------
+    replica = None
+    if world > 1:
+        rep = Stack(HEADLINE, c["B"], dev, layers=stack.layers)
+        rep.set_tau(HEADLINE_TAU)
+        rm = timed((None if args.eager else rep.graphed()) or rep.step, max(2, min(steps, 10)), 3,
+                   dist)
+        replica = world * tokens_step_global * max(2, min(steps, 10)) / (rm * 1e-3)
+        del rep
+        torch.cuda.empty_cache()
 
     # ---- e2e: module API, host buffers ------------------------------------------
-    import d2dmoe_b200 as Dm
-    mods = []
-    for L in layers:
-        m = Dm.MoeficationMoE("moe", D, E, True, H, torch.nn.ReLU, experts_class="custom_kernel")
-        m.router = Dm.MoeficationRouter(D, E, width=R, depth=2, bias=False, activation="relu",
-                                        output_activation="abs")
-        m = m.to(torch.bfloat16).to(dev)
-        m.load_state_dict({"experts.w1": L.t["w1"], "experts.b1": L.t["b1"],
-                           "experts.w2": L.t["w2"], "last_bias": L.t["last_bias"],
-                           "router.layers.0.weight": L.t["wa"],
-                           "router.layers.2.weight": L.t["wb"]})
-        m.forward_mode, m.tau = "dynk_max", 1.0 - HEADLINE_TAU
-        mods.append(m)
-    hx = [L.t["x"].cpu().pin_memory() for L in layers[:4]]
+    nh = min(4, stack.nbuf)
+    hx = [stack.x[i].cpu().pin_memory() for i in range(nh)]
     ho = [torch.empty_like(h).pin_memory() for h in hx]
 
     def e2e_step():
-        # host x -> layer -> host out through the module's host-buffer entry point
-        # (copies and kernels of consecutive batch slices overlap inside it)
-        # the 12 layer calls queue back to back on the shared copy/compute streams; the step
+        # host x -> layer -> host out through the module's host-buffer entry point; the 12
+        # layer calls queue back to back on the shared copy/compute streams and the step
         # ends when every layer's output has arrived in host memory
-        for i, m in enumerate(mods):
-            m.forward_host(hx[i % 4], ho[i % 4], chunks=4, sync=False)
+        for i, m in enumerate(stack.mods):
+            m.forward_host(hx[i % nh], ho[i % nh], chunks=4, sync=False)
         Dm.MoeficationMoE.host_synchronize(dev)
 
     e2e_steps = max(2, min(steps, 5))
     ms_e2e = timed(e2e_step, e2e_steps, 2, dist)
-    e2e_val = world * tokens_step * e2e_steps / (ms_e2e * 1e-3)
-    bytes_x = n_layer * D * 2 * LAYERS
+    e2e_val = tokens_step_global * e2e_steps / (ms_e2e * 1e-3)
+    bytes_x = stack.n * c["d"] * 2 * stack.layers
+    ceil_s = copy_ceiling(stack, e2e_steps, dist)
+    e2e_ceiling = tokens_step_global / ceil_s
 
-    check = sample_check(layers, HEADLINE_TAU) if rank == 0 else None
-    cpu = cpu_baseline_layer() if (rank == 0 and world == 1 and not args.no_cpu) else None
+    check = sample_check(stack, HEADLINE_TAU) if rank == 0 else None
+
+    # ---- all five configurations with their CPU baselines (1 GPU) -------------------
+    configs = None
+    cpu_head = None
+    if world == 1 and rank == 0 and not args.no_configs:
+        configs = []
+        for name, cc in CONFIGS.items():
+            st = stack if name == HEADLINE else Stack(name, cc["B"], dev, seed0=3000)
+            k_steps = max(2, min(steps, 10 if cc["layers"] * cc["B"] * cc["S"] < 2e6 else 4))
+            for tau in cc["taus"]:
+                st.set_tau(tau)
+                fn = (None if args.eager else st.graphed()) or st.step
+                tm = timed(fn, k_steps, 3)
+                sum_c = st.sum_c()
+                n = st.n
+                troof = sum(t_roof(cc, n, sc, pk)[0] for sc in sum_c)
+                per_step = tm * 1e-3 / k_steps
+                row = {"config": name, "tau_cfg": tau, "layers": st.layers,
+                       "tokens_per_layer": n, "dtype": "fp32" if cc["dtype"] == FP32 else "bf16",
+                       "mean_k": sum(sum_c) / (st.layers * n),
+                       "tokens_per_s": n * st.layers / per_step,
+                       "us_per_layer": per_step * 1e6 / st.layers,
+                       "roofline_us_per_layer": troof * 1e6 / st.layers,
+                       "roofline_frac": troof / per_step,
+                       "bound": t_roof(cc, n, sum_c[0], pk)[1]}
+                if tau == cc["taus"][-1] or tau == HEADLINE_TAU:
+                    st.set_tau(tau)
+                    row["stage_us_per_layer"] = st.stage_times(2)[0]
+                if not args.no_cpu and (tau == HEADLINE_TAU or len(cc["taus"]) == 1):
+                    row["cpu_baseline"] = cpu_baseline(name, tau)
+                    if name == HEADLINE:
+                        cpu_head = row["cpu_baseline"]
+                configs.append(row)
+            if st is not stack:
+                del st
+                torch.cuda.empty_cache()
+        stack.set_tau(HEADLINE_TAU)
 
     if dist is not None:
         dist.barrier()
@@ -447,39 +691,58 @@ def run_ours(args):
     line = {
         "metric": "moe_ffn_layer_tokens_per_s", "value": value, "unit": "tokens/s",
         "n_gpus": world, "steps": steps, "warmup": warmup, "ms_per_step": ms / steps,
-        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
+        "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16",
         "data": "synthetic", "config": workload_config(world),
+        "api": "MoeficationMoE.forward per layer (device-resident x)",
+        "launch": "the 12 module forwards captured once in a CUDA graph and replayed per step"
+                  if replay else "eager launches",
+        "eager_ms_per_step": ms_eager,
         "ms_per_step_quantiles": step_q,
         "mean_k": head["mean_k"], "roofline_frac_layer_path": head["roofline_frac"],
         "tau_sweep": sweep, "roofline": roof,
         "e2e": {"value": e2e_val, "unit": "tokens/s", "h2d_bytes_per_step": bytes_x,
-                "d2h_bytes_per_step": bytes_x, "api": "MoeficationMoE.forward_host (pinned host x -> pinned host out, 4 slices per layer, layers pipelined)"},
-        # kernels per layer call as the library counted them for the last call: router+mask
-        # (+ token lists), [compaction scatter], expert FFN
-        "gpu_launches": steps * LAYERS * launches_per_call,
+                "d2h_bytes_per_step": bytes_x,
+                "copy_ceiling_tokens_per_s": e2e_ceiling,
+                "frac_of_copy_ceiling": e2e_val / e2e_ceiling,
+                "api": "MoeficationMoE.forward_host (pinned host x -> pinned host out, 4 slices "
+                       "per layer, layers pipelined); bytes are per rank"},
+        # kernels per layer call: what the library counted for the last d2d_moe_forward
+        # (router+rule, compaction scan, compaction scatter, expert FFN) + the routing-tensor
+        # expansion the module returns as gating data
+        "gpu_launches": steps * stack.layers * launches_per_layer,
         "clocks": clocks, "check": check,
     }
-    if cpu is not None:
-        line["cpu_baseline"] = cpu
+    if replica is not None:
+        line["replicas_weak_tokens_per_s"] = replica
+    if configs is not None:
+        line["configs"] = configs
+    if cpu_head is not None:
+        line["cpu_baseline"] = cpu_head
+    elif world == 1 and not args.no_cpu:
+        line["cpu_baseline"] = cpu_baseline(HEADLINE, HEADLINE_TAU)
     print(json.dumps(line))
 
 
 def main():
-    global LAYERS, HEADLINE_TAU
+    global HEADLINE_TAU
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=100)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
-    ap.add_argument("--layers", type=int, default=LAYERS,
+    ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline legs")
+    ap.add_argument("--no-configs", action="store_true",
+                    help="skip the per-configuration array (headline workload only)")
+    ap.add_argument("--layers", type=int, default=None,
                     help="profiling aid: run fewer than the 12 layers (not a bench value)")
     ap.add_argument("--tau", type=float, default=HEADLINE_TAU,
                     help="profiling aid: tau_cfg of the headline measurement")
+    ap.add_argument("--eager", action="store_true",
+                    help="time eager launches instead of CUDA-graph replays of the step")
     ap.add_argument("--quick", action="store_true",
-                    help="profiling aid: headline timing only (no sweep, stages, e2e, CPU leg)")
+                    help="profiling aid: headline timing only (no sweep, stages, e2e, CPU legs)")
     args = ap.parse_args()
-    LAYERS, HEADLINE_TAU = args.layers, args.tau
+    HEADLINE_TAU = args.tau
     if args.impl == "reference":
         run_reference(args)
     else:

@@ -28,6 +28,7 @@ SIGNATURES = {
     "d2d_mask_from_scores": (_i, [_p, _f, _p, _i64, _i, _i, _p, _p]),
     "d2d_last_forward_launches": (_i, []),
     "d2d_debug_configure": (_i, [_i, _i]),
+    "d2d_debug_select_experts_kernel": (_i, [_i]),
     "d2d_mask_rule_from_scores": (_i, [_p, _i, _i, _f, _p, _i64, _i, _i, _p, _p]),
     "d2d_init_out": (_i, [_p, _p, _i, _p, _i64, _i, _i, _p]),
     "d2d_expand_mask": (_i, [_p, _p, _i64, _i, _i, _p]),

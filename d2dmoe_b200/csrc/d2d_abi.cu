@@ -206,6 +206,11 @@ int d2d_moe_forward(const void* x, const void* wa, const void* wb, const void* r
 
 int d2d_last_forward_launches(void) { return g_last_forward_launches; }
 
+int d2d_debug_select_experts_kernel(int which) {
+  umma_debug_select_experts_kernel(which);
+  return D2D_OK;
+}
+
 int d2d_debug_configure(int wait_limit_log2, int withhold_weight_tile) {
   umma_debug_configure(wait_limit_log2, withhold_weight_tile);
   return D2D_OK;

@@ -56,50 +56,47 @@ compact_count_kernel(const uint32_t* __restrict__ mask_bits, int32_t* __restrict
   }
 }
 
-// CTA b owns experts 32b..32b+31.  Thread (seg, el) first adds up the counts of expert
-// 32b+el over its segment of the tile range (a warp reads 32 consecutive experts of one
-// tile: one 128-byte line), the 32 segment sums of each expert are scanned in shared
-// memory, and a second pass over the segment replaces every count by the number of
-// tokens of that expert in earlier tiles.  Row ntiles receives the totals.
-__global__ void __launch_bounds__(SCAN_NT)
+// CTA b owns experts 32b..32b+31.  Thread (seg, el) loads the counts of expert 32b+el over
+// its segment of the tile range into registers (a warp reads 32 consecutive experts of one
+// tile: one 128-byte line; all loads of a thread are in flight together), the 32 segment
+// sums of each expert are scanned in shared memory, and every count is replaced by the
+// number of tokens of that expert in earlier tiles.  Row ntiles receives the totals.
+// Tile ranges longer than 32 x SCAN_REG tiles are walked in several rounds with a carry.
+constexpr int SCAN_REG = 16;
+__global__ void __launch_bounds__(SCAN_NT, 1)
 compact_scan_kernel(int32_t* __restrict__ counts, int ntiles, int E) {
   __shared__ int seg_sum[32][33];
+  __shared__ int carry[32];
   const int el = threadIdx.x & 31, seg = threadIdx.x >> 5;
   const int e = blockIdx.x * 32 + el;
-  const int per = (ntiles + 31) / 32;
-  const int t0 = min(seg * per, ntiles), t1 = min(t0 + per, ntiles);
   grid_launch_dependents();
+  if (seg == 0) carry[el] = 0;
   grid_dependency_wait();      // the counts table comes from the previous kernel
-  int sum = 0;
-  if (e < E) {
-    int t = t0;
-    for (; t + 3 < t1; t += 4) {     // four independent loads in flight
-      const int a = counts[(int64_t)t * E + e], b = counts[(int64_t)(t + 1) * E + e];
-      const int c = counts[(int64_t)(t + 2) * E + e], d = counts[(int64_t)(t + 3) * E + e];
-      sum += a + b + c + d;
+  for (int base = 0; base < ntiles; base += 32 * SCAN_REG) {
+    const int span = min(ntiles - base, 32 * SCAN_REG);
+    const int per = (span + 31) / 32;
+    const int t0 = base + min(seg * per, span), t1 = base + min(seg * per + per, span);
+    int v[SCAN_REG], sum = 0;
+#pragma unroll
+    for (int i = 0; i < SCAN_REG; ++i) {
+      v[i] = (e < E && t0 + i < t1) ? counts[(int64_t)(t0 + i) * E + e] : 0;
+      sum += v[i];
     }
-    for (; t < t1; ++t) sum += counts[(int64_t)t * E + e];
+    __syncthreads();           // carry of the previous round is final, seg_sum is free
+    seg_sum[seg][el] = sum;
+    __syncthreads();
+    int run = carry[el];
+    for (int s = 0; s < seg; ++s) run += seg_sum[s][el];
+#pragma unroll
+    for (int i = 0; i < SCAN_REG; ++i) {
+      if (e < E && t0 + i < t1) counts[(int64_t)(t0 + i) * E + e] = run;
+      run += v[i];
+    }
+    __syncthreads();           // every thread has read carry and seg_sum
+    if (seg == SCAN_NT / 32 - 1) carry[el] = run;
   }
-  seg_sum[seg][el] = sum;
   __syncthreads();
-  if (seg == 0) {
-    int run = 0;
-    for (int s = 0; s < 32; ++s) {
-      const int v = seg_sum[s][el];
-      seg_sum[s][el] = run;
-      run += v;
-    }
-    if (e < E) counts[(int64_t)ntiles * E + e] = run;
-  }
-  __syncthreads();
-  if (e < E) {
-    int run = seg_sum[seg][el];
-    for (int t = t0; t < t1; ++t) {
-      const int v = counts[(int64_t)t * E + e];
-      counts[(int64_t)t * E + e] = run;
-      run += v;
-    }
-  }
+  if (seg == 0 && e < E) counts[(int64_t)ntiles * E + e] = carry[el];
 }
 
 __global__ void __launch_bounds__(NTS)

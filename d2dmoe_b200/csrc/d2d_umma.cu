@@ -40,12 +40,12 @@
 #include <mutex>
 
 #include "d2d_umma_api.cuh"
+#include "d2d_umma_ptx.cuh"
 
 namespace d2d {
+using namespace umma;
 namespace {
 
-constexpr int TILE_M = 128;
-constexpr int SLOT = TILE_M * 128;   // 16 KB: 128 rows x 64 bf16, also the weight slot size
 constexpr int NA_MAX = 6;            // ring A stages (upper bound)
 constexpr int NB_MAX = 6;            // ring B stages (upper bound)
 constexpr int SLOTS_TOTAL = 14;      // ring A + ring B + hidden tile + staging (224 KB)
@@ -53,8 +53,8 @@ constexpr int NTHREADS = 480;            // router form
 constexpr int NTHREADS_EXPERTS = 608;    // + four warps that write the output rows
 constexpr int WARP_MMA1 = 8, WARP_MMA2 = 9, WARP_BULK = 10, WARP_PROD0 = 11, WARP_WR0 = 15;
 constexpr int MAX_E = 128;
-constexpr uint32_t WAIT_LIMIT = 1u << 22;   // polls of one bounded wait (about a second)
 constexpr int MODE_EXPERTS = 0, MODE_ROUTER = 1;
+constexpr long long PAIR_MIN_TOKENS = 1LL << 62;   // pairs only on request until they win
 
 struct Geo {
   int kc1;       // d / 64
@@ -134,212 +134,6 @@ Geo router_geo(int d, int R, int E) {
   return g;
 }
 
-// byte offset of element (row n, k) inside a K-major tile of 64 bf16 per row with the
-// 128-byte swizzle: 16-byte piece index XOR (row mod 8), 8-row groups 1024 bytes apart
-__host__ __device__ __forceinline__ int swz(int n, int k) {
-  return (n >> 3) * 1024 + (n & 7) * 128 + ((((k >> 3) ^ (n & 7)) & 7) << 4) + (k & 7) * 2;
-}
-
-// ---------------------------------------------------------------------------
-// PTX wrappers
-// ---------------------------------------------------------------------------
-__device__ __forceinline__ uint32_t smem_u32(const void* p) {
-  return (uint32_t)__cvta_generic_to_shared(p);
-}
-__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
-  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
-}
-__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
-  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t bar, uint32_t bytes) {
-  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes)
-               : "memory");
-}
-__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
-  uint32_t ok;
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-      "selp.u32 %0, 1, 0, p;\n\t}"
-      : "=r"(ok)
-      : "r"(bar), "r"(parity)
-      : "memory");
-  return ok != 0;
-}
-// Non-blocking test (try_wait may suspend the thread for a while when the phase is not
-// complete; a loop that serves two rings must not sit in one of them).
-__device__ __forceinline__ bool mbar_test_wait(uint32_t bar, uint32_t parity) {
-  uint32_t ok;
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-      "selp.u32 %0, 1, 0, p;\n\t}"
-      : "=r"(ok)
-      : "r"(bar), "r"(parity)
-      : "memory");
-  return ok != 0;
-}
-// Bounded wait.  false = gave up (this thread's limit ran out, or another role did).
-// abort_flag[1] holds the poll limit of this launch (Ctl::wait_limit).
-__device__ __noinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag,
-                                       int* dev_status) {
-  const uint32_t limit = (uint32_t)abort_flag[1];
-  for (uint32_t i = 0; i < limit; ++i) {
-    if (mbar_try_wait(bar, parity)) return true;
-    if (i > 64) {
-      __nanosleep(i > 4096 ? 256 : 32);
-      if ((i & 63) == 0 && *abort_flag) return false;
-    }
-  }
-  *abort_flag = 1;
-  report(dev_status, D2D_ERR_TIMEOUT);
-  return false;
-}
-// Fast path inline (the barrier is usually complete already); the bounded polling loop
-// stays out of line.
-__device__ __forceinline__ bool mbar_wait_fast(uint32_t bar, uint32_t parity,
-                                               volatile int* abort_flag, int* dev_status) {
-  if (mbar_try_wait(bar, parity)) return true;
-  return mbar_wait(bar, parity, abort_flag, dev_status);
-}
-__device__ __forceinline__ void bulk_g2s(uint32_t dst, const void* src, uint32_t bytes,
-                                         uint32_t bar) {
-  asm volatile(
-      "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::
-          "r"(dst),
-      "l"(src), "r"(bytes), "r"(bar)
-      : "memory");
-}
-__device__ __forceinline__ void cp_async16(uint32_t dst, const void* src) {
-  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
-}
-// the mbarrier receives one arrival (already counted in its expected count) once every
-// cp.async this thread has issued so far has landed
-__device__ __forceinline__ void cp_async_arrive_noinc(uint32_t bar) {
-  asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ void cp_async_wait_all() {
-  asm volatile("cp.async.wait_all;" ::: "memory");
-}
-__device__ __forceinline__ void fence_proxy_async() {
-  asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-}
-__device__ __forceinline__ void tc_fence_before() {
-  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-}
-__device__ __forceinline__ void tc_fence_after() {
-  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-}
-__device__ __forceinline__ void tmem_alloc(uint32_t smem_dst, uint32_t ncols) {
-  asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_dst),
-               "r"(ncols)
-               : "memory");
-  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
-}
-__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t ncols) {
-  asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols)
-               : "memory");
-}
-// D[tmem] (+)= A[smem] * B[smem], bf16 inputs, fp32 accumulate, issued by one thread
-__device__ __forceinline__ void umma_bf16(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc,
-                                          uint32_t idesc, uint32_t accumulate) {
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "setp.ne.b32 p, %4, 0;\n\t"
-      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}" ::"r"(tmem_d),
-      "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
-      : "memory");
-}
-// mbarrier arrives once every MMA issued so far by this thread has completed
-__device__ __forceinline__ void umma_commit(uint32_t bar) {
-  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(
-                   bar)
-               : "memory");
-}
-__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t* v) {
-  asm volatile(
-      "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
-      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
-      : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]),
-        "=r"(v[7]), "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]),
-        "=r"(v[14]), "=r"(v[15])
-      : "r"(taddr)
-      : "memory");
-}
-__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t* v) {
-  asm volatile(
-      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
-      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
-      : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]),
-        "=r"(v[7]), "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]),
-        "=r"(v[14]), "=r"(v[15]), "=r"(v[16]), "=r"(v[17]), "=r"(v[18]), "=r"(v[19]),
-        "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]), "=r"(v[24]), "=r"(v[25]),
-        "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
-      : "r"(taddr)
-      : "memory");
-}
-__device__ __forceinline__ uint4 ld_shared_v4(uint32_t addr) {
-  uint4 r;
-  asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];"
-               : "=r"(r.x), "=r"(r.y), "=r"(r.z), "=r"(r.w)
-               : "r"(addr)
-               : "memory");
-  return r;
-}
-// TMA store of one contiguous run from shared to global memory (bulk group completion)
-__device__ __forceinline__ void bulk_s2g(void* gdst, uint32_t ssrc, uint32_t bytes) {
-  asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;" ::"l"(gdst),
-               "r"(ssrc), "r"(bytes)
-               : "memory");
-}
-__device__ __forceinline__ void bulk_commit() {
-  asm volatile("cp.async.bulk.commit_group;" ::: "memory");
-}
-__device__ __forceinline__ void bulk_wait_all() {
-  asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
-}
-__device__ __forceinline__ void tmem_wait_ld() {
-  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-}
-__device__ __forceinline__ void st_shared_v4(uint32_t addr, uint32_t a, uint32_t b, uint32_t c,
-                                             uint32_t d) {
-  asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(a), "r"(b), "r"(c),
-               "r"(d)
-               : "memory");
-}
-
-// One lane of a converged warp.  Unlike a test on the lane id, elect.sync tells the
-// compiler that exactly one thread runs the guarded code, so warp-uniform operands of
-// tcgen05.mma / tcgen05.commit need no per-lane handling.
-__device__ __forceinline__ bool elect_one() {
-  uint32_t pred;
-  asm volatile(
-      "{\n\t.reg .pred P;\n\t"
-      "elect.sync _|P, 0xffffffff;\n\t"
-      "selp.u32 %0, 1, 0, P;\n\t}"
-      : "=r"(pred));
-  return pred != 0;
-}
-
-// Shared-memory matrix descriptor: K-major tile, 128-byte swizzle, 8-row groups 1024
-// bytes apart (stride byte offset), descriptor version 1 (sm_100).
-__device__ __forceinline__ uint64_t smem_desc(uint32_t addr) {
-  return (uint64_t)((addr >> 4) & 0x3FFF) | ((uint64_t)1 << 16) | ((uint64_t)(1024 >> 4) << 32) |
-         ((uint64_t)1 << 46) | ((uint64_t)2 << 61);
-}
-// Instruction descriptor, kind::f16: D fp32, A/B bf16, both K-major, M x N tile.
-__device__ __forceinline__ uint32_t instr_desc(int M, int N) {
-  return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(N >> 3) << 17) |
-         ((uint32_t)(M >> 4) << 24);
-}
-
-__device__ __forceinline__ float bfr(float v) { return __bfloat162float(__float2bfloat16_rn(v)); }
-__device__ __forceinline__ float nanmax(float a, float b) {
-  return (a != a || b != b) ? __int_as_float(0x7fc00000) : fmaxf(a, b);
-}
-
 // ---------------------------------------------------------------------------
 // shared-memory bookkeeping
 // ---------------------------------------------------------------------------
@@ -394,19 +188,6 @@ __device__ __forceinline__ Tile tile_info(const Params& p, const Ctl* c, int til
   }
   return t;
 }
-
-// Ring position kept as (stage, phase) with wrap-around instead of a running counter:
-// no integer division, and every value stays provably warp-uniform, which lets the
-// compiler form the MMA operands in uniform registers.
-struct RingPos {
-  uint32_t s, ph;
-  __device__ __forceinline__ void next(uint32_t n) {
-    if (++s == n) {
-      s = 0;
-      ph ^= 1;
-    }
-  }
-};
 
 // With one weight subtile per k-chunk (nsub == 1) the first accumulator is double
 // buffered and GEMM1 of the next tile is issued before GEMM2 of the current one, so the
@@ -482,7 +263,7 @@ __device__ void role_bulk(const Params& p, Ctl* c, uint32_t ringB, uint32_t ring
   const uint8_t *pe1 = nullptr, *pe2 = nullptr;
   if (t1 < total) pe1 = pe2 = p.packed + (long long)tile_info<MODE>(p, c, t1).e * g.stride;
   uint32_t idle = 0;
-  bool withheld = p.withhold != 0 && blockIdx.x == 0;
+  bool withheld = (p.withhold & 1) != 0 && blockIdx.x == 0;
   while (t1 < total || t2 < total) {
     bool progress = false;
     if (t1 < total && mbar_test_wait(emptyB + 8 * r1.s, r1.ph ^ 1)) {
@@ -1212,6 +993,7 @@ std::mutex g_dev_lock;
 // test hooks (d2d_debug_configure): process-wide, read at launch
 std::atomic<uint32_t> g_wait_limit{WAIT_LIMIT};
 std::atomic<int> g_withhold{0};
+std::atomic<int> g_experts_kernel{0};     // 0 = chosen from the size, 1 = one CTA per tile, 2 = CTA pairs
 
 static_assert(1024 + (size_t)SLOTS_TOTAL * SLOT + sizeof(Ctl) + 64 <= 232448,
               "shared-memory plan exceeds the 227 KB a CTA may use");
@@ -1297,14 +1079,27 @@ int launch_experts_umma(const void* x, const int32_t* token_idx, const int32_t* 
   p.act = act;
   p.glu = glu ? 1 : 0;
   p.dev_status = dev_status;
+  // CTA pairs halve the weight bytes per row but work on 256-row units: they pay off once
+  // the token lists are long enough to keep every pair busy for several tiles
+  const int which = g_experts_kernel.load();
+  const bool pair = which == 2 || (which == 0 && N >= PAIR_MIN_TOKENS);
+  if (pair && pair_experts_supported(d, E, H, glu, D2D_BF16)) {
+    const int rc = launch_experts_pair(x, token_idx, offsets, packed, out, N, d, E, H, glu, act,
+                                       dev_status, g_wait_limit.load(), g_withhold.load(), s);
+    if (rc != D2D_ERR_UNSUPPORTED) return rc;      // no cluster launch on this device: one CTA per tile
+  }
   const long long max_tiles = (N * (long long)E + TILE_M - 1) / TILE_M + E;
   return launch<MODE_EXPERTS>(p, max_tiles, s);
+}
+
+void umma_debug_select_experts_kernel(int which) {
+  g_experts_kernel.store(which == 1 || which == 2 ? which : 0);
 }
 
 void umma_debug_configure(int wait_limit_log2, int withhold_weight_tile) {
   g_wait_limit.store(wait_limit_log2 >= 4 && wait_limit_log2 <= 22 ? 1u << wait_limit_log2
                                                                     : WAIT_LIMIT);
-  g_withhold.store(withhold_weight_tile ? 1 : 0);
+  g_withhold.store(withhold_weight_tile);
 }
 
 bool umma_router_supported(int d, int R, int E, int dtype) {

@@ -196,6 +196,12 @@ int d2d_last_forward_launches(void);
  * d2d_debug_configure(0, 0) to return to normal operation. */
 int d2d_debug_configure(int wait_limit_log2, int withhold_weight_tile);
 
+/* Test hook, no upstream counterpart.  The bf16 expert FFN exists in two tilings: one CTA
+ * per 128 rows of an expert's token list, and CTA pairs (tcgen05 cta_group::2) per 256 rows,
+ * each CTA loading half of every weight tile.  which = 0: chosen from the token count
+ * (default); 1: always one CTA per tile; 2: always CTA pairs. */
+int d2d_debug_select_experts_kernel(int which);
+
 /* One-time re-layout of the weights into the shared-memory tile images the
  * tensor-core kernels copy in bulk (bf16 only).  The upstream kernels read the
  * parameters in place (architectures/moe/moe_impls.py:137-146,276-284); here the

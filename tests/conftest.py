@@ -20,3 +20,16 @@ def pytest_collection_modifyitems(config, items):
     for it in items:
         if "gpu" in it.keywords:
             it.add_marker(skip)
+
+
+@pytest.fixture(scope="session", autouse=True)
+def _experts_kernel_choice():
+    """D2D_TEST_EXPERTS_KERNEL=1|2 runs the whole suite with the bf16 expert FFN forced to
+    one tiling (1: one CTA per 128-row tile, 2: CTA pairs per 256 rows) instead of the choice
+    the library makes from the token count, so that every parity case reaches both."""
+    import os
+    which = int(os.environ.get("D2D_TEST_EXPERTS_KERNEL", "0"))
+    if which:
+        from d2dmoe_b200 import _capi
+        _capi.lib.d2d_debug_select_experts_kernel(which)
+    yield

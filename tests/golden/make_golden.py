@@ -62,7 +62,7 @@ def gemma_shape_cases() -> list[C.LayerCase]:
     return [
         C.LayerCase("gemma_shape", 3, 701, 2048, 128, 128, R=256, tau=0.1, dtype="bf16",
                     act="gelu", glu=True, norm="rms", seed=4),
-        C.LayerCase("gemma_shape_k", 3, 701, 2048, 128, 128, R=256, tau=0.45, dtype="bf16",
+        C.LayerCase("gemma_shape_k", 3, 701, 2048, 128, 128, R=256, tau=0.3, dtype="bf16",
                     act="gelu", glu=True, norm="rms", seed=5),
     ]
 
