@@ -38,7 +38,7 @@ SIGNATURES = {
     "d2d_experts_ffn": (_i, [_p, _p, _p, _p, _p, _p, _p, _p, _p, _i, _i, _p,
                              _i64, _i, _i, _i, _i, _i, _p, _p]),
     "d2d_moe_forward": (_i, [_p, _p, _p, _p, _p, _f, _p, _p, _p, _p, _p, _p, _i, _p,
-                             _p, _p, _p, _i64, _i, _i, _i, _i, _i, _i, _p, _sz, _p, _p]),
+                             _p, _p, _p, _i64, _i, _i, _i, _i, _i, _i, _p, _sz, _p, _p, _p]),
     "d2d_prepack_experts_bytes": (_i, [_i, _i, _i, _i, _i, C.POINTER(_sz)]),
     "d2d_prepack_experts": (_i, [_p, _p, _p, _p, _p, _i, _i, _i, _i, _p]),
     "d2d_prepack_router_bytes": (_i, [_i, _i, _i, _i, C.POINTER(_sz)]),
@@ -67,7 +67,7 @@ def _load() -> C.CDLL:
 
 
 lib = _load()
-if lib.d2d_abi_version() != 1:
+if lib.d2d_abi_version() != 2:
     raise ImportError("libd2dmoe_b200.so: ABI version mismatch")
 
 

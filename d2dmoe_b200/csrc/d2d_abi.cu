@@ -58,7 +58,7 @@ int d2d_router_mask(const void* x, const void* wa, const void* wb, const void* r
   if (router_packed_opt && umma_router_supported(d, R, E, dtype) && aligned(x, 16) &&
       aligned(last_bias_opt, 16) && aligned(out_init_opt, 16) && aligned(router_packed_opt, 1024))
     return launch_router_mask_umma(x, router_packed_opt, thresh_mult, mask_bits, scores_opt,
-                                   last_bias_opt, add_residual, out_init_opt, nullptr, N, d, R, E,
+                                   nullptr, last_bias_opt, add_residual, out_init_opt, nullptr, N, d, R, E,
                                    dev_status, s);
   return launch_router_mask_simt(x, wa, wb, thresh_mult, mask_bits, scores_opt, last_bias_opt,
                                  add_residual, out_init_opt, N, d, R, E, dtype, dev_status, s);
@@ -149,9 +149,10 @@ int d2d_moe_forward(const void* x, const void* wa, const void* wb, const void* r
                     const void* experts_packed_opt, const void* last_bias_opt, int add_residual,
                     void* out, uint32_t* mask_bits, int32_t* token_idx, int32_t* offsets,
                     int64_t N, int d, int R, int E, int H, int act, int dtype, void* ws,
-                    size_t ws_bytes, int* dev_status, d2d_stream_t stream) {
+                    size_t ws_bytes, int* dev_status, void* routing_tensor_opt,
+                    d2d_stream_t stream) {
   int rc, nl = 0;
-  bool counts_ready = false;
+  bool counts_ready = false, rt_done = routing_tensor_opt == nullptr;
   g_last_forward_launches = 0;
   if (!wa && !scores_in_opt) return D2D_ERR_BAD_ARG;
   if (!mask_bits || !token_idx || !offsets || !ws || !aligned(ws, 16)) return D2D_ERR_BAD_ARG;
@@ -166,12 +167,14 @@ int d2d_moe_forward(const void* x, const void* wa, const void* wb, const void* r
   if (scores_in_opt) {
     // rule + counts table + output init in one launch when the shape allows it
     rc = (dtype_ok(dtype) && out && d >= 1 && E >= 1 && (!add_residual || x))
-             ? launch_gate_scores_fused(scores_in_opt, thresh_mult, mask_bits, (int32_t*)ws, x,
+             ? launch_gate_scores_fused(scores_in_opt, thresh_mult, mask_bits, routing_tensor_opt,
+                                        (int32_t*)ws, x,
                                         last_bias_opt, add_residual, out, N, d, E, dtype,
                                         (cudaStream_t)stream)
              : D2D_ERR_UNSUPPORTED;
     if (rc == D2D_OK) {
       counts_ready = true;
+      rt_done = true;
       nl += 1;
     } else if (rc == D2D_ERR_UNSUPPORTED) {
       rc = d2d_mask_from_scores(scores_in_opt, thresh_mult, mask_bits, N, E, dtype, dev_status,
@@ -184,9 +187,10 @@ int d2d_moe_forward(const void* x, const void* wa, const void* wb, const void* r
              aligned(last_bias_opt, 16) && aligned(router_packed_opt, 1024)) {
     // the tensor-core router also fills the compaction's counts table
     rc = launch_router_mask_umma(x, router_packed_opt, thresh_mult, mask_bits, nullptr,
-                                 last_bias_opt, add_residual, out, (int32_t*)ws, N, d, R, E,
-                                 dev_status, (cudaStream_t)stream);
+                                 routing_tensor_opt, last_bias_opt, add_residual, out,
+                                 (int32_t*)ws, N, d, R, E, dev_status, (cudaStream_t)stream);
     counts_ready = true;
+    rt_done = true;
     nl += 1;
   } else {
     rc = d2d_router_mask(x, wa, wb, router_packed_opt, thresh_mult, mask_bits, nullptr,
@@ -198,6 +202,11 @@ int d2d_moe_forward(const void* x, const void* wa, const void* wb, const void* r
                       (cudaStream_t)stream, counts_ready);
   if (rc != D2D_OK) return rc;
   nl += counts_ready ? 2 : 3;      // [count,] scan, scatter
+  if (!rt_done) {                  // paths whose first kernel does not write the routing tensor
+    rc = launch_expand_mask(mask_bits, routing_tensor_opt, N, E, dtype, (cudaStream_t)stream);
+    if (rc != D2D_OK) return rc;
+    nl += 1;
+  }
   g_last_forward_launches = nl + 1;
   return d2d_experts_ffn(x, token_idx, offsets, w1, b1_opt, w_up_opt, w2, experts_packed_opt,
                          nullptr, 0, /*accumulate=*/1, out, N, d, E, H, act, dtype, dev_status,

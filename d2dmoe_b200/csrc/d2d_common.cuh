@@ -130,7 +130,7 @@ int launch_gate_rule(const void* scores, int rule, int k, float tau, uint32_t* m
                      int64_t N, int E, int dtype, cudaStream_t s);
 int launch_mask_from_scores(const void* scores, float mult, uint32_t* mask_bits, int64_t N, int E,
                             int dtype, int* dev_status, cudaStream_t s);
-int launch_gate_scores_fused(const void* scores, float mult, uint32_t* mask_bits,
+int launch_gate_scores_fused(const void* scores, float mult, uint32_t* mask_bits, void* rt,
                              int32_t* tile_counts, const void* x, const void* last_bias,
                              int add_residual, void* out, int64_t N, int d, int E, int dtype,
                              cudaStream_t s);

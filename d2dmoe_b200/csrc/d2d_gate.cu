@@ -291,7 +291,8 @@ gate_rule_kernel(const T* __restrict__ scores, int rule, int k, float tau,
 template <typename T>
 __global__ void __launch_bounds__(NT)
 gate_scores_fused_kernel(const T* __restrict__ scores, float mult,
-                         uint32_t* __restrict__ mask_bits, int32_t* __restrict__ tile_counts,
+                         uint32_t* __restrict__ mask_bits, T* __restrict__ rt,
+                         int32_t* __restrict__ tile_counts,
                          const T* __restrict__ x, const T* __restrict__ last_bias,
                          int add_residual, T* __restrict__ out, int64_t N, int d, int E) {
   __shared__ int cnt[256];
@@ -320,6 +321,7 @@ gate_scores_fused_kernel(const T* __restrict__ scores, float mult,
       const bool keep = (lane + 32 * j < E) && (s[j] >= thr);
       const uint32_t word = __ballot_sync(0xffffffffu, keep);
       if (lane == 0) mask_bits[t * nw + j] = word;
+      if (rt && lane + 32 * j < E) rt[t * E + lane + 32 * j] = DT<T>::from_f(keep ? 1.0f : 0.0f);
       mine[j] += keep ? 1 : 0;
     }
   }
@@ -476,7 +478,7 @@ int launch_gate_rule(const void* scores, int rule, int k, float tau, uint32_t* m
 
 // returns D2D_ERR_UNSUPPORTED when the shape does not allow the fused form (caller then uses
 // the separate kernels)
-int launch_gate_scores_fused(const void* scores, float mult, uint32_t* mask_bits,
+int launch_gate_scores_fused(const void* scores, float mult, uint32_t* mask_bits, void* rt,
                              int32_t* tile_counts, const void* x, const void* last_bias,
                              int add_residual, void* out, int64_t N, int d, int E, int dtype,
                              cudaStream_t s) {
@@ -488,11 +490,11 @@ int launch_gate_scores_fused(const void* scores, float mult, uint32_t* mask_bits
   if (grid > 0x7fffffffLL) return D2D_ERR_UNSUPPORTED;
   if (dtype == D2D_F32)
     gate_scores_fused_kernel<float><<<(unsigned)grid, NT, 0, s>>>(
-        (const float*)scores, mult, mask_bits, tile_counts, (const float*)x,
+        (const float*)scores, mult, mask_bits, (float*)rt, tile_counts, (const float*)x,
         (const float*)last_bias, add_residual, (float*)out, N, d, E);
   else
     gate_scores_fused_kernel<bf16><<<(unsigned)grid, NT, 0, s>>>(
-        (const bf16*)scores, mult, mask_bits, tile_counts, (const bf16*)x,
+        (const bf16*)scores, mult, mask_bits, (bf16*)rt, tile_counts, (const bf16*)x,
         (const bf16*)last_bias, add_residual, (bf16*)out, N, d, E);
   return cudaGetLastError() == cudaSuccess ? D2D_OK : D2D_ERR_LAUNCH;
 }

@@ -39,6 +39,7 @@
 #include <atomic>
 #include <mutex>
 
+#include "d2d_tmap.cuh"
 #include "d2d_umma_api.cuh"
 #include "d2d_umma_ptx.cuh"
 
@@ -87,6 +88,7 @@ struct Params {
   float mult;
   uint32_t* mask_bits;
   bf16* scores;
+  bf16* rt_out;             // optional: 0/1 routing tensor [N, E]
   const bf16* last_bias;
   int add_residual;
   bf16* out_init;
@@ -94,6 +96,7 @@ struct Params {
   int* dev_status;
   uint32_t wait_limit;      // polls per bounded wait
   int withhold;             // test hook: CTA 0 never loads its first weight tile
+  int tma_gather;           // experts: rows by TMA tile::gather4 instead of cp.async
 };
 
 Geo experts_geo(int d, int H, bool glu) {
@@ -197,8 +200,13 @@ __device__ __forceinline__ bool lookahead(const Geo& g) { return g.nsub == 1; }
 // ---------------------------------------------------------------------------
 // roles
 // ---------------------------------------------------------------------------
-template <int MODE>
-__device__ void role_producer(const Params& p, Ctl* c, uint32_t ringA, int pt) {
+// Ring A producer of the expert form, default path (four warps): the rows of the tile's
+// token list by 16-byte cp.async (4 rows x 128 bytes per warp instruction, software
+// swizzle); the stage barrier is signalled by cp.async.mbarrier.arrive.  Measured against
+// the TMA gather below on the ViT-B/16 layer: 61 vs 101 us per launch, so this is the path
+// that runs.
+__device__ void role_producer_cpasync(const Params& p, Ctl* c, uint32_t ringA, int pt) {
+  constexpr int MODE = MODE_EXPERTS;
   const int lane = pt & 31, pw = pt >> 5;
   const int j = lane & 7;
   uint32_t dstoff[8];
@@ -216,15 +224,10 @@ __device__ void role_producer(const Params& p, Ctl* c, uint32_t ringA, int pt) {
     for (int i = 0; i < 8; ++i) {
       int row = pw * 32 + i * 4 + (lane >> 3);
       row = min(row, t.nrows - 1);      // rows past the tail repeat the last row; masked later
-      long long tok;
-      if (MODE == MODE_ROUTER) {
-        tok = (long long)t.r0 + row;
-      } else {
-        tok = p.token_idx[t.r0 + row];
-        if (tok < 0 || tok >= p.N) {
-          report(p.dev_status, D2D_ERR_INDEX_RANGE);
-          tok = 0;
-        }
+      long long tok = p.token_idx[t.r0 + row];
+      if (tok < 0 || tok >= p.N) {
+        report(p.dev_status, D2D_ERR_INDEX_RANGE);
+        tok = 0;
       }
       src[i] = p.x + tok * p.d + j * 8;
     }
@@ -234,6 +237,51 @@ __device__ void role_producer(const Params& p, Ctl* c, uint32_t ringA, int pt) {
 #pragma unroll
       for (int i = 0; i < 8; ++i) cp_async16(base + dstoff[i], src[i] + kc * 64);
       cp_async_arrive_noinc(smem_u32(&c->fullA[s]));
+      if (++s == (uint32_t)p.g.na) {
+        s = 0;
+        ph ^= 1;
+      }
+    }
+  }
+}
+
+// Ring A producer by TMA (one warp): the tile's rows of x into the 128-byte-swizzled K-major
+// stage the MMA descriptor describes, 64 columns (128 bytes per row) per stage.
+//   router:  rows are consecutive: one lane issues one 128-row box per stage; rows past the
+//            last token arrive as zeros.
+//   experts: (selectable, slower than the cp.async gather: the TMA unit spends a request per
+//            128-byte row) lane l gathers rows 4l..4l+3 of the tile with one tile::gather4
+//            copy (four token indices -> four consecutive 128-byte rows, 512 bytes per lane).
+// Lane 0 posts the stage's 16 KB on its barrier; the copies complete on it.
+template <int MODE>
+__device__ void role_producer(const Params& p, Ctl* c, const CUtensorMap* tmx, uint32_t ringA,
+                              int lane) {
+  volatile int* af = &c->abort_flag;
+  uint32_t s = 0, ph = 0;
+  for (int tile = blockIdx.x; tile < c->total_tiles; tile += gridDim.x) {
+    const Tile t = tile_info<MODE>(p, c, tile);
+    int tok[4] = {0, 0, 0, 0};
+    if (MODE == MODE_EXPERTS) {
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const int row = min(4 * lane + i, t.nrows - 1);   // rows past the tail repeat the last row
+        tok[i] = p.token_idx[t.r0 + row];
+        if (tok[i] < 0 || tok[i] >= p.N) {
+          report(p.dev_status, D2D_ERR_INDEX_RANGE);
+          tok[i] = 0;
+        }
+      }
+    }
+    for (int kc = 0; kc < p.g.kc1; ++kc) {
+      if (!mbar_wait_fast(smem_u32(&c->emptyA[s]), ph ^ 1, af, p.dev_status)) return;
+      const uint32_t bar = smem_u32(&c->fullA[s]);
+      if (lane == 0) mbar_arrive_expect_tx(bar, SLOT);
+      if (MODE == MODE_EXPERTS) {
+        tma_gather4(ringA + s * SLOT + lane * 512, tmx, kc * 64, tok[0], tok[1], tok[2], tok[3],
+                    bar);
+      } else if (lane == 0) {
+        tma_load_2d(ringA + s * SLOT, tmx, kc * 64, t.r0, bar);
+      }
       if (++s == (uint32_t)p.g.na) {
         s = 0;
         ph ^= 1;
@@ -535,15 +583,34 @@ __device__ void role_epilogue_router(const Params& p, Ctl* c, uint32_t hs, uint3
       const int nw = (E + 31) >> 5;
       uint32_t word = 0, mw[4] = {0u, 0u, 0u, 0u};
       for (int c0 = 0; c0 < g.nd; c0 += 16) {
-        uint32_t v[16];
+        uint32_t v[16], blk = 0;
         tmem_ld16(tmem + lane_base + 256 + c0, v);
         tmem_wait_ld();
 #pragma unroll
         for (int q = 0; q < 16; ++q) {
           const float sc = fabsf(bfr(__uint_as_float(v[q])));
           if (c0 + q < E) {
-            if (sc >= thr) word |= 1u << ((c0 + q) & 31);
+            if (sc >= thr) {
+              word |= 1u << ((c0 + q) & 31);
+              blk |= 1u << q;
+            }
             if (p.scores && r < t.nrows) p.scores[trow * E + c0 + q] = __float2bfloat16_rn(sc);
+          }
+        }
+        if (p.rt_out && r < t.nrows && c0 < E) {
+          // this row's 0/1 routing entries of the block (bf16 1.0 = 0x3F80)
+          bf16* dst = p.rt_out + trow * E + c0;
+          if ((E & 7) == 0) {
+            uint32_t w8[8];
+#pragma unroll
+            for (int q = 0; q < 8; ++q)
+              w8[q] = ((blk >> (2 * q)) & 1u ? 0x3F80u : 0u) |
+                      ((blk >> (2 * q + 1)) & 1u ? 0x3F800000u : 0u);
+            *reinterpret_cast<uint4*>(dst) = make_uint4(w8[0], w8[1], w8[2], w8[3]);
+            if (c0 + 16 <= E) *reinterpret_cast<uint4*>(dst + 8) = make_uint4(w8[4], w8[5], w8[6], w8[7]);
+          } else {
+            for (int q = 0; q < 16 && c0 + q < E; ++q)
+              dst[q] = __float2bfloat16_rn((blk >> q) & 1u ? 1.0f : 0.0f);
           }
         }
         if (((c0 + 16) & 31) == 0 || c0 + 16 >= g.nd) {
@@ -775,7 +842,7 @@ __device__ void role_writer(const Params& p, Ctl* c, uint32_t stg, int wt) {
 // ---------------------------------------------------------------------------
 template <int MODE>
 __global__ void __launch_bounds__(MODE == MODE_EXPERTS ? NTHREADS_EXPERTS : NTHREADS, 1)
-mlp_tiles_kernel(const Params p) {
+mlp_tiles_kernel(const Params p, const __grid_constant__ CUtensorMap tmx) {
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw = smem_u32(smem_raw);
   const uint32_t base = (raw + 1023u) & ~1023u;
@@ -796,7 +863,7 @@ mlp_tiles_kernel(const Params p) {
 
   if (tid == 0) {
     for (int i = 0; i < NA_MAX; ++i) {
-      mbar_init(smem_u32(&c->fullA[i]), 128);
+      mbar_init(smem_u32(&c->fullA[i]), (MODE == MODE_EXPERTS && !p.tma_gather) ? 128 : 1);
       mbar_init(smem_u32(&c->emptyA[i]), 1);
     }
     for (int i = 0; i < NB_MAX; ++i) {
@@ -893,8 +960,12 @@ mlp_tiles_kernel(const Params p) {
     if (elect_one()) role_bulk<MODE>(p, c, ringB, ringB2);
     __syncwarp();
   } else if (warp < WARP_WR0) {
-    role_producer<MODE>(p, c, ringA, tid - WARP_PROD0 * 32);
-    cp_async_wait_all();
+    if (MODE == MODE_EXPERTS && !p.tma_gather) {
+      role_producer_cpasync(p, c, ringA, tid - WARP_PROD0 * 32);
+      cp_async_wait_all();
+    } else if (warp == WARP_PROD0) {
+      role_producer<MODE>(p, c, &tmx, ringA, tid & 31);
+    }
   } else if (MODE == MODE_EXPERTS) {
     role_writer(p, c, stg, tid - WARP_WR0 * 32);
   }
@@ -993,7 +1064,9 @@ std::mutex g_dev_lock;
 // test hooks (d2d_debug_configure): process-wide, read at launch
 std::atomic<uint32_t> g_wait_limit{WAIT_LIMIT};
 std::atomic<int> g_withhold{0};
-std::atomic<int> g_experts_kernel{0};     // 0 = chosen from the size, 1 = one CTA per tile, 2 = CTA pairs
+// 0 = chosen from the size, 1 = one CTA per tile, 2 = CTA pairs, 3 = one CTA per tile with
+// the rows gathered by TMA
+std::atomic<int> g_experts_kernel{0};
 
 static_assert(1024 + (size_t)SLOTS_TOTAL * SLOT + sizeof(Ctl) + 64 <= 232448,
               "shared-memory plan exceeds the 227 KB a CTA may use");
@@ -1033,10 +1106,16 @@ int launch(Params& p, long long max_tiles, cudaStream_t s) {
   }
   p.wait_limit = g_wait_limit.load();
   p.withhold = g_withhold.load();
+  // x as a tensor map: boxes of 64 columns x 1 row (gathered by fours) for the expert lists,
+  // 64 columns x 128 consecutive rows for the router
+  alignas(64) CUtensorMap tmx;
+  const int rc = encode_tmap_2d_b16(&tmx, p.x, (uint64_t)p.d, (uint64_t)p.N, (uint64_t)p.d * 2, 64,
+                                    MODE == MODE_EXPERTS ? 1 : TILE_M, true);
+  if (rc != D2D_OK) return rc == D2D_ERR_BAD_ARG ? D2D_ERR_LAUNCH : rc;
   long long grid = max_tiles < sms ? max_tiles : sms;
   if (grid < 1) grid = 1;
   return launch_pdl(k, dim3((unsigned)grid), dim3(MODE == MODE_EXPERTS ? NTHREADS_EXPERTS : NTHREADS),
-                    smem, s, p);
+                    smem, s, p, tmx);
 }
 
 }  // namespace
@@ -1082,6 +1161,7 @@ int launch_experts_umma(const void* x, const int32_t* token_idx, const int32_t* 
   // CTA pairs halve the weight bytes per row but work on 256-row units: they pay off once
   // the token lists are long enough to keep every pair busy for several tiles
   const int which = g_experts_kernel.load();
+  p.tma_gather = which == 3 ? 1 : 0;
   const bool pair = which == 2 || (which == 0 && N >= PAIR_MIN_TOKENS);
   if (pair && pair_experts_supported(d, E, H, glu, D2D_BF16)) {
     const int rc = launch_experts_pair(x, token_idx, offsets, packed, out, N, d, E, H, glu, act,
@@ -1093,7 +1173,7 @@ int launch_experts_umma(const void* x, const int32_t* token_idx, const int32_t* 
 }
 
 void umma_debug_select_experts_kernel(int which) {
-  g_experts_kernel.store(which == 1 || which == 2 ? which : 0);
+  g_experts_kernel.store(which >= 1 && which <= 3 ? which : 0);
 }
 
 void umma_debug_configure(int wait_limit_log2, int withhold_weight_tile) {
@@ -1118,9 +1198,9 @@ int launch_prepack_router(const void* wa, const void* wb, void* packed, int d, i
 }
 
 int launch_router_mask_umma(const void* x, const void* packed, float mult, uint32_t* mask_bits,
-                            void* scores, const void* last_bias, int add_residual, void* out_init,
-                            int32_t* tile_counts, int64_t N, int d, int R, int E, int* dev_status,
-                            cudaStream_t s) {
+                            void* scores, void* rt_out, const void* last_bias, int add_residual,
+                            void* out_init, int32_t* tile_counts, int64_t N, int d, int R, int E,
+                            int* dev_status, cudaStream_t s) {
   Params p = {};
   p.x = (const bf16*)x;
   p.N = N;
@@ -1131,6 +1211,7 @@ int launch_router_mask_umma(const void* x, const void* packed, float mult, uint3
   p.mult = mult;
   p.mask_bits = mask_bits;
   p.scores = (bf16*)scores;
+  p.rt_out = (bf16*)rt_out;
   p.last_bias = (const bf16*)last_bias;
   p.add_residual = add_residual;
   p.out_init = (bf16*)out_init;

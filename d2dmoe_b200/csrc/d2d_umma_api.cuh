@@ -17,9 +17,9 @@ size_t umma_router_packed_bytes(int d, int R, int E);
 int launch_prepack_router(const void* wa, const void* wb, void* packed, int d, int R, int E,
                           cudaStream_t s);
 int launch_router_mask_umma(const void* x, const void* packed, float mult, uint32_t* mask_bits,
-                            void* scores, const void* last_bias, int add_residual, void* out_init,
-                            int32_t* tile_counts, int64_t N, int d, int R, int E, int* dev_status,
-                            cudaStream_t s);
+                            void* scores, void* rt_out, const void* last_bias, int add_residual,
+                            void* out_init, int32_t* tile_counts, int64_t N, int d, int R, int E,
+                            int* dev_status, cudaStream_t s);
 
 // expert FFN on CTA pairs (tcgen05 cta_group::2, d2d_umma_pair.cu); same packed weights.
 // D2D_ERR_UNSUPPORTED when the device cannot co-schedule a 2-CTA cluster of this kernel.

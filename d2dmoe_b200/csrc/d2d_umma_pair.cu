@@ -366,6 +366,7 @@ __device__ void role_mma1(const Params& p, Ctl* c, uint32_t ringA, uint32_t ring
       if (!mbar_wait_fast(fullA + 8 * sa, pha, af, p.dev_status)) return;
       if (!mbar_wait_fast(fullB + 8 * sb, phb, af, p.dev_status)) return;
       tc_fence_after();
+      if (!(p.withhold & 16))
 #pragma unroll
       for (uint32_t k = 0; k < 4; ++k)
         umma2_bf16(acc, ((uint64_t)hi << 32) | (alo + 2 * k), ((uint64_t)hi << 32) | (blo + 2 * k),
@@ -444,6 +445,7 @@ __device__ void role_mma2(const Params& p, Ctl* c, uint32_t ringB2, uint32_t hs,
         }
         tc_fence_after();
         const int ksteps = min(4, (g.K2 - k2 * 64) >> 4);
+        if (!(p.withhold & 16))
 #pragma unroll
         for (int k = 0; k < 4; ++k)
           if (k < ksteps)

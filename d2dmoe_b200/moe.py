@@ -400,22 +400,24 @@ class MoeficationMoE(MoELayer):
             return out.view(orig_size), {self.name: (rt,)}
         if fused:
             wa, wb = self.router.layers[0].weight, self.router.layers[2].weight
+            rt = torch.empty(N, E, dtype=x.dtype, device=x.device)
             ops.moe_forward(x2d, wa, wb, self.tau, p["w1"], p["b1"], p["w2"], p["act"], out, wsp,
                             w_up=p["w_up"], last_bias=last_bias,
                             add_residual=self.add_residual_connection,
                             router_packed=self.router.packed(),
-                            experts_packed=self.experts.packed())
-            rt = ops.expand_mask(wsp, N, E, x.dtype).view(*orig_size[:-1], E)
+                            experts_packed=self.experts.packed(), routing_out=rt)
+            rt = rt.view(*orig_size[:-1], E)
         elif self.forward_mode == "dynk_max":
             # any other router: its scores come from device tensor ops, the rule and the
             # rest of the layer from the library
             s = self.router(x)
             s2 = s.reshape(N, E).contiguous()
+            rt = torch.empty(N, E, dtype=s.dtype, device=x.device)
             ops.moe_forward(x2d, None, None, self.tau, p["w1"], p["b1"], p["w2"], p["act"], out,
                             wsp, w_up=p["w_up"], scores=s2, last_bias=last_bias,
                             add_residual=self.add_residual_connection,
-                            experts_packed=self.experts.packed())
-            rt = ops.expand_mask(wsp, N, E, s.dtype).view(*orig_size[:-1], E)
+                            experts_packed=self.experts.packed(), routing_out=rt)
+            rt = rt.view(*orig_size[:-1], E)
         elif self.forward_mode in ("topk", "dynk"):
             s = self.router(x)
             self._rule_mask(s.reshape(N, E).contiguous(), wsp)

@@ -196,11 +196,12 @@ def experts_ffn(x2d, wsp: Workspace, w1, b1, w2, act: str, out, *, w_up=None, pa
 
 def moe_forward(x2d, wa, wb, tau, w1, b1, w2, act: str, out, wsp: Workspace, *, w_up=None,
                 scores=None, last_bias=None, add_residual=False, router_packed=None,
-                experts_packed=None):
+                experts_packed=None, routing_out=None):
     """Whole layer in one library call: router+mask (or mask from ``scores``) ->
-    compaction -> expert FFN with scatter-add into ``out``."""
+    compaction -> expert FFN with scatter-add into ``out``.  ``routing_out`` [N, E]
+    (optional) receives the 0/1 routing tensor."""
     _cu(x2d, wa, wb, w1, b1, w2, w_up, scores, last_bias, out, router_packed, experts_packed,
-        wsp.mask_bits)
+        wsp.mask_bits, routing_out)
     N, d = x2d.shape
     E, _, H = w1.shape
     R = wa.shape[0] if wa is not None else 0
@@ -210,7 +211,8 @@ def moe_forward(x2d, wa, wb, tau, w1, b1, w2, act: str, out, wsp: Workspace, *, 
                                   _ptr(w2), _ptr(experts_packed), _ptr(last_bias),
                                   int(add_residual), _ptr(out), _ptr(wsp.mask_bits),
                                   _ptr(wsp.token_idx), _ptr(wsp.offsets), N, d, R, E, H, ACT[act],
-                                  _dt(x2d), _ptr(wsp.ws), wsp.ws.numel(), _ptr(wsp.status), st),
+                                  _dt(x2d), _ptr(wsp.ws), wsp.ws.numel(), _ptr(wsp.status),
+                                  _ptr(routing_out), st),
               "d2d_moe_forward")
 
 

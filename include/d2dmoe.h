@@ -40,7 +40,7 @@
 extern "C" {
 #endif
 
-#define D2D_ABI_VERSION 1
+#define D2D_ABI_VERSION 2
 
 typedef void* d2d_stream_t; /* a cudaStream_t */
 
@@ -172,7 +172,10 @@ int d2d_experts_ffn(const void* x, const int32_t* token_idx, const int32_t* offs
 /* The whole layer, MoeficationMoE.forward in 'dynk_max' mode
  * (architectures/moe/moefication.py:90-101): router+mask (or mask from
  * scores_in_opt when wa is NULL) -> compaction -> expert FFN.  mask_bits,
- * token_idx, offsets are outputs the caller may inspect. */
+ * token_idx, offsets are outputs the caller may inspect.  routing_tensor_opt
+ * [N, E] in T, or NULL: the 0/1 routing tensor the upstream forward returns as
+ * gating data (architectures/moe/moefication.py:84-85,101), written by the same
+ * kernel that applies the rule. */
 int d2d_moe_forward(const void* x, const void* wa, const void* wb, const void* router_packed_opt,
                     const void* scores_in_opt, float thresh_mult,
                     const void* w1, const void* b1_opt, const void* w_up_opt, const void* w2,
@@ -180,7 +183,8 @@ int d2d_moe_forward(const void* x, const void* wa, const void* wb, const void* r
                     const void* last_bias_opt, int add_residual, void* out,
                     uint32_t* mask_bits, int32_t* token_idx, int32_t* offsets,
                     int64_t N, int d, int R, int E, int H, int act, int dtype,
-                    void* ws, size_t ws_bytes, int* dev_status, d2d_stream_t stream);
+                    void* ws, size_t ws_bytes, int* dev_status,
+                    void* routing_tensor_opt, d2d_stream_t stream);
 
 /* Number of kernels the calling thread's last d2d_moe_forward issued (4 on the tensor-core
  * path: router + rule, compaction scan, compaction scatter, expert FFN; more on the
@@ -199,7 +203,8 @@ int d2d_debug_configure(int wait_limit_log2, int withhold_weight_tile);
 /* Test hook, no upstream counterpart.  The bf16 expert FFN exists in two tilings: one CTA
  * per 128 rows of an expert's token list, and CTA pairs (tcgen05 cta_group::2) per 256 rows,
  * each CTA loading half of every weight tile.  which = 0: chosen from the token count
- * (default); 1: always one CTA per tile; 2: always CTA pairs. */
+ * (default); 1: always one CTA per tile; 2: always CTA pairs; 3: one CTA per tile with the token
+ * rows gathered by TMA (cp.async.bulk.tensor tile::gather4) instead of 16-byte cp.async. */
 int d2d_debug_select_experts_kernel(int which);
 
 /* One-time re-layout of the weights into the shared-memory tile images the

@@ -30,7 +30,7 @@ def test_library_exports_every_declared_symbol():
 
 def test_host_only_entry_points():
     from d2dmoe_b200 import _capi
-    assert _capi.lib.d2d_abi_version() == 1
+    assert _capi.lib.d2d_abi_version() == 2
     assert _capi.lib.d2d_strerror(0) == b"ok"
     assert b"workspace" in _capi.lib.d2d_strerror(4)
     n = ctypes.c_size_t(0)
@@ -57,7 +57,7 @@ def test_misaligned_buffers_are_rejected_before_any_launch():
         ptrs[bad] = a(ptrs[bad].value + 2)
         rc = lib.d2d_moe_forward(ptrs["x"], a(base), a(base), a(ws), None, 0.9, a(base), a(base),
                                  None, a(base), a(ws), None, 0, ptrs["out"], a(base), a(base),
-                                 a(base), 256, 768, 128, 24, 128, 0, 1, a(ws), 1 << 20, None, None)
+                                 a(base), 256, 768, 128, 24, 128, 0, 1, a(ws), 1 << 20, None, None, None)
         assert rc == 1, (bad, rc)
     # experts entry point alone
     rc = lib.d2d_experts_ffn(a(base + 2), a(base), a(base), a(base), None, None, a(base), None,
