@@ -538,9 +538,11 @@ def run_ours(args):
     dev = torch.device("cuda", local)
     c = CONFIGS[HEADLINE]
     lo, hi = shard_bounds(c["B"], world, rank)
+    if args.batch:                      # profiling aid: a rank's share of a larger job
+        lo, hi = 0, args.batch
     stack = Stack(HEADLINE, hi - lo, dev, layers=args.layers)
     stack.set_tau(HEADLINE_TAU)
-    n_layer_global = c["B"] * c["S"]
+    n_layer_global = (args.batch * world if args.batch else c["B"]) * c["S"]
     tokens_step_global = n_layer_global * stack.layers
     pk = peaks()
     steps, warmup = args.steps, max(3, args.warmup)
@@ -735,6 +737,9 @@ def main():
                     help="skip the per-configuration array (headline workload only)")
     ap.add_argument("--layers", type=int, default=None,
                     help="profiling aid: run fewer than the 12 layers (not a bench value)")
+    ap.add_argument("--batch", type=int, default=0,
+                    help="profiling aid: images per rank instead of this rank's share of 256 "
+                         "(e.g. 32 = one rank's share at 8 GPUs; not a bench value)")
     ap.add_argument("--tau", type=float, default=HEADLINE_TAU,
                     help="profiling aid: tau_cfg of the headline measurement")
     ap.add_argument("--eager", action="store_true",

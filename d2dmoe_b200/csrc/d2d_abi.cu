@@ -201,7 +201,7 @@ int d2d_moe_forward(const void* x, const void* wa, const void* wb, const void* r
   rc = launch_compact(mask_bits, token_idx, offsets, N, E, (int32_t*)ws, dev_status,
                       (cudaStream_t)stream, counts_ready);
   if (rc != D2D_OK) return rc;
-  nl += counts_ready ? 2 : 3;      // [count,] scan, scatter
+  nl += counts_ready ? 1 : 2;      // [count,] scatter
   if (!rt_done) {                  // paths whose first kernel does not write the routing tensor
     rc = launch_expand_mask(mask_bits, routing_tensor_opt, N, E, dtype, (cudaStream_t)stream);
     if (rc != D2D_OK) return rc;

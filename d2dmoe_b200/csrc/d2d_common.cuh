@@ -141,8 +141,9 @@ int launch_expand_mask(const uint32_t* mask_bits, void* rt, int64_t N, int E, in
 int launch_pack_mask(const void* rt, uint32_t* mask_bits, int64_t N, int E, int dtype,
                      cudaStream_t s);
 size_t compact_workspace_bytes(int64_t n_max, int E);
-// counts_ready: the table counts_ws[tile of 128 tokens][E] is already filled (by the
-// router kernel); otherwise a count kernel fills it first
+int compact_row_cells(int E);      // cells (bytes) per row of the compaction's counts table
+// counts_ready: the byte table counts_ws[tile of 128 tokens][compact_row_cells(E)] is already
+// filled (by the router kernel); otherwise a count kernel fills it first
 int launch_compact(const uint32_t* mask_bits, int32_t* token_idx, int32_t* offsets, int64_t N,
                    int E, int32_t* counts_ws, int* dev_status, cudaStream_t s,
                    bool counts_ready);

@@ -5,14 +5,15 @@
 // The sort only serves to bring each expert's tokens to the front of its column;
 // a compaction gives the same set per expert, here in ascending token order.
 //
-// Three launches:
-//   count   : counts[tile][e] = tokens of the 128-token tile that keep expert e
+// Two launches:
+//   count   : counts[tile][e] = tokens of the 128-token tile that keep expert e, one BYTE
+//             per cell (a tile holds at most 128 tokens), rows padded to EP cells
 //             (skipped when the router kernel already wrote the table)
-//   scan    : per expert, exclusive prefix of the counts along the tiles, in place;
-//             the expert totals go to the extra row counts[ntiles][.]
-//   scatter : one CTA per 256 tokens reads the prefix row of its first tile and the
-//             totals row (E values each), scans the totals over the experts and
-//             writes its token indices.
+//   scatter : one CTA per 256 tokens sweeps the byte table with 16-byte loads (sum over all
+//             tiles = the expert totals, sum over earlier tiles = its own base), scans the
+//             totals over the experts and writes its token indices.
+// Every CTA reads the whole table, but at one byte per cell that is 12 KB for a ViT-B/16
+// layer (394 tiles x 32) and 128 KB for 131072 tokens x 128 experts, out of L2.
 // Integer work, bit-exact by construction; HBM traffic is the mask (read twice)
 // plus 4 bytes per kept token-expert pair.
 #include "d2d_common.cuh"
@@ -27,85 +28,42 @@ constexpr int CHUNK = ROWS * 32;
 constexpr int CTILE = 128;               // granularity of the counts table
 constexpr int TILES_PER_CHUNK = CHUNK / CTILE;
 constexpr int MAX_E = 256;
-constexpr int SCAN_NT = 1024;            // scan CTA: 32 experts x 32 segments of the tile range
 
 // one warp = one 128-token tile; lane b ends up with the count of expert 32j+b
 __global__ void __launch_bounds__(NT)
-compact_count_kernel(const uint32_t* __restrict__ mask_bits, int32_t* __restrict__ counts,
-                     int64_t N, int E) {
+compact_count_kernel(const uint32_t* __restrict__ mask_bits, uint8_t* __restrict__ counts,
+                     int64_t N, int E, int EP) {
   const int lane = threadIdx.x & 31;
   const int64_t tile = (int64_t)blockIdx.x * (NT / 32) + (threadIdx.x >> 5);
   if (tile * CTILE >= N) return;
   const int nw = (E + 31) / 32;
-  for (int j = 0; j < nw; ++j) {
+  for (int j = 0; j * 32 < EP; ++j) {
     uint32_t w[4];
 #pragma unroll
     for (int r = 0; r < 4; ++r) {
       const int64_t t = tile * CTILE + r * 32 + lane;
-      w[r] = t < N ? mask_bits[t * nw + j] : 0u;
+      w[r] = (t < N && j < nw) ? mask_bits[t * nw + j] : 0u;
     }
     int mine = 0;
-    const int nb = min(32, E - 32 * j);
+    const int nb = max(0, min(32, E - 32 * j));
     for (int b = 0; b < nb; ++b) {
       int cb = 0;
 #pragma unroll
       for (int r = 0; r < 4; ++r) cb += __popc(__ballot_sync(0xffffffffu, (w[r] >> b) & 1u));
       if (lane == b) mine = cb;
     }
-    if (lane < nb) counts[tile * E + 32 * j + lane] = mine;
+    if (32 * j + lane < EP) counts[tile * EP + 32 * j + lane] = (uint8_t)mine;   // pads are 0
   }
-}
-
-// CTA b owns experts 32b..32b+31.  Thread (seg, el) loads the counts of expert 32b+el over
-// its segment of the tile range into registers (a warp reads 32 consecutive experts of one
-// tile: one 128-byte line; all loads of a thread are in flight together), the 32 segment
-// sums of each expert are scanned in shared memory, and every count is replaced by the
-// number of tokens of that expert in earlier tiles.  Row ntiles receives the totals.
-// Tile ranges longer than 32 x SCAN_REG tiles are walked in several rounds with a carry.
-constexpr int SCAN_REG = 16;
-__global__ void __launch_bounds__(SCAN_NT, 1)
-compact_scan_kernel(int32_t* __restrict__ counts, int ntiles, int E) {
-  __shared__ int seg_sum[32][33];
-  __shared__ int carry[32];
-  const int el = threadIdx.x & 31, seg = threadIdx.x >> 5;
-  const int e = blockIdx.x * 32 + el;
-  grid_launch_dependents();
-  if (seg == 0) carry[el] = 0;
-  grid_dependency_wait();      // the counts table comes from the previous kernel
-  for (int base = 0; base < ntiles; base += 32 * SCAN_REG) {
-    const int span = min(ntiles - base, 32 * SCAN_REG);
-    const int per = (span + 31) / 32;
-    const int t0 = base + min(seg * per, span), t1 = base + min(seg * per + per, span);
-    int v[SCAN_REG], sum = 0;
-#pragma unroll
-    for (int i = 0; i < SCAN_REG; ++i) {
-      v[i] = (e < E && t0 + i < t1) ? counts[(int64_t)(t0 + i) * E + e] : 0;
-      sum += v[i];
-    }
-    __syncthreads();           // carry of the previous round is final, seg_sum is free
-    seg_sum[seg][el] = sum;
-    __syncthreads();
-    int run = carry[el];
-    for (int s = 0; s < seg; ++s) run += seg_sum[s][el];
-#pragma unroll
-    for (int i = 0; i < SCAN_REG; ++i) {
-      if (e < E && t0 + i < t1) counts[(int64_t)(t0 + i) * E + e] = run;
-      run += v[i];
-    }
-    __syncthreads();           // every thread has read carry and seg_sum
-    if (seg == SCAN_NT / 32 - 1) carry[el] = run;
-  }
-  __syncthreads();
-  if (seg == 0 && e < E) counts[(int64_t)ntiles * E + e] = carry[el];
 }
 
 __global__ void __launch_bounds__(NTS)
-compact_scatter_kernel(const uint32_t* __restrict__ mask_bits, const int32_t* __restrict__ prefix,
+compact_scatter_kernel(const uint32_t* __restrict__ mask_bits, const uint8_t* __restrict__ counts,
                        int32_t* __restrict__ token_idx, int32_t* __restrict__ offsets, int64_t N,
-                       int E, int ntiles, int* dev_status) {
+                       int E, int EP, int ntiles, int* dev_status) {
   extern __shared__ int sm[];
   int* cnt = sm;                 // [ROWS][E] -> becomes each row's write base
-  int* tot = cnt + ROWS * E;     // [E]   total per expert, then exclusive offsets
+  int* tot = cnt + ROWS * E;     // [EP]  total per expert, then exclusive offsets
+  int* pre = tot + EP;           // [EP]  tokens of expert e in earlier chunks
   const int tid = threadIdx.x, lane = tid & 31, w = tid >> 5;
   const int nw = (E + 31) / 32;
   const int chunk = blockIdx.x;
@@ -113,16 +71,65 @@ compact_scatter_kernel(const uint32_t* __restrict__ mask_bits, const int32_t* __
 
   grid_launch_dependents();
   for (int i = tid; i < ROWS * E; i += NTS) cnt[i] = 0;
+  for (int e = tid; e < 2 * EP; e += NTS) tot[e] = 0;      // tot and pre are adjacent
   __syncthreads();
-  grid_dependency_wait();      // mask and prefix table come from the previous kernels
-  for (int e = tid; e < E; e += NTS) tot[e] = prefix[(int64_t)ntiles * E + e];
-  // per-row popcounts of this chunk; the words stay in registers for the second pass
+  grid_dependency_wait();      // mask and counts table come from the previous kernel
+  // this thread's mask words (warps 0..ROWS-1: one row of 32 tokens each); the loads are in
+  // flight during the table sweep and the words stay in registers for both passes
   uint32_t word[MAX_E / 32];
 #pragma unroll
-  for (int j = 0; j < MAX_E / 32; ++j) word[j] = (j < nw && t < N) ? mask_bits[t * nw + j] : 0u;
+  for (int j = 0; j < MAX_E / 32; ++j)
+    word[j] = (w < ROWS && j < nw && t < N) ? mask_bits[t * nw + j] : 0u;
+  // sweep of the byte table: thread (tsub, g) adds up the 16 cells of group g over the tiles
+  // tsub, tsub + stride, ...; sums over all tiles and over the tiles before this chunk
+  {
+    const int G = EP >> 4;                      // 16-cell groups per table row (power of two)
+    const int g = tid & (G - 1), tsub = tid / G, stride = NTS / G;
+    const int first_tile = chunk * TILES_PER_CHUNK;
+    int a[16], b[16];
+#pragma unroll
+    for (int q = 0; q < 16; ++q) a[q] = b[q] = 0;
+    for (int t0 = tsub; t0 < ntiles; t0 += 4 * stride) {
+      uint4 v[4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {      // four independent loads in flight
+        const int tt = t0 + u * stride;
+        v[u] = tt < ntiles ? __ldg(reinterpret_cast<const uint4*>(counts + (int64_t)tt * EP) + g)
+                           : make_uint4(0u, 0u, 0u, 0u);
+      }
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const uint32_t ww[4] = {v[u].x, v[u].y, v[u].z, v[u].w};
+        const bool before = t0 + u * stride < first_tile;
+#pragma unroll
+        for (int q = 0; q < 16; ++q) {
+          const int c = (ww[q >> 2] >> (8 * (q & 3))) & 0xff;
+          a[q] += c;
+          if (before) b[q] += c;
+        }
+      }
+    }
+    // lanes that hold the same group (lane mod G equal) are added up by shuffles, then one
+    // lane per group and warp adds into shared memory
+    for (int o = 16; o >= G; o >>= 1) {
+#pragma unroll
+      for (int q = 0; q < 16; ++q) {
+        a[q] += __shfl_xor_sync(0xffffffffu, a[q], o);
+        b[q] += __shfl_xor_sync(0xffffffffu, b[q], o);
+      }
+    }
+    if (lane < G && lane < 32) {
+#pragma unroll
+      for (int q = 0; q < 16; ++q) {
+        if (a[q]) atomicAdd(&tot[16 * g + q], a[q]);
+        if (b[q]) atomicAdd(&pre[16 * g + q], b[q]);
+      }
+    }
+  }
+  // per-row popcounts of this chunk
 #pragma unroll
   for (int j = 0; j < MAX_E / 32; ++j) {
-    if (j >= nw) break;
+    if (j >= nw || w >= ROWS) break;
     if (__ballot_sync(0xffffffffu, word[j] != 0u) == 0u) continue;
     const int nb = min(32, E - 32 * j);
     int mine = 0;
@@ -160,7 +167,7 @@ compact_scatter_kernel(const uint32_t* __restrict__ mask_bits, const int32_t* __
   __syncthreads();
   for (int e = tid; e < E; e += NTS) {
     if (chunk == 0) offsets[e] = tot[e];
-    int run = tot[e] + prefix[(int64_t)chunk * TILES_PER_CHUNK * E + e];
+    int run = tot[e] + pre[e];
     for (int row = 0; row < ROWS; ++row) {
       const int c = cnt[row * E + e];
       cnt[row * E + e] = run;
@@ -170,7 +177,7 @@ compact_scatter_kernel(const uint32_t* __restrict__ mask_bits, const int32_t* __
   __syncthreads();
 #pragma unroll
   for (int j = 0; j < MAX_E / 32; ++j) {
-    if (j >= nw) break;
+    if (j >= nw || w >= ROWS) break;
     if (__ballot_sync(0xffffffffu, word[j] != 0u) == 0u) continue;
     const int nb = min(32, E - 32 * j);
     for (int b = 0; b < nb; ++b) {
@@ -186,7 +193,16 @@ compact_scatter_kernel(const uint32_t* __restrict__ mask_bits, const int32_t* __
 
 }  // namespace
 
-// counts table: one row of E cells per 128-token tile, plus the totals row
+// cells per row of the byte table: the next power of two >= E, at least 16 (rows are read
+// in 16-byte groups; a power of two lets one warp's lanes split into equal groups)
+int compact_row_cells(int E) {
+  int ep = 16;
+  while (ep < E) ep <<= 1;
+  return ep;
+}
+
+// the byte table needs ntiles * EP bytes; this (four bytes per tile and expert) is what
+// d2d_workspace_bytes has always reported and covers it for every E
 size_t compact_workspace_bytes(int64_t n_max, int E) {
   const int64_t ntiles = ceil_div64(n_max > 0 ? n_max : 1, CTILE);
   return (size_t)(ntiles + 1) * (size_t)E * sizeof(int32_t);
@@ -203,19 +219,18 @@ int launch_compact(const uint32_t* mask_bits, int32_t* token_idx, int32_t* offse
                ? D2D_OK
                : D2D_ERR_LAUNCH;
   }
+  const int EP = compact_row_cells(E);
   const int64_t ntiles = ceil_div64(N, CTILE);
   const int64_t nchunks = ceil_div64(N, CHUNK);
+  uint8_t* counts = reinterpret_cast<uint8_t*>(counts_ws);
   if (!counts_ready) {
-    compact_count_kernel<<<(unsigned)ceil_div64(ntiles, NT / 32), NT, 0, s>>>(mask_bits, counts_ws,
-                                                                             N, E);
+    compact_count_kernel<<<(unsigned)ceil_div64(ntiles, NT / 32), NT, 0, s>>>(mask_bits, counts, N,
+                                                                             E, EP);
     if (cudaGetLastError() != cudaSuccess) return D2D_ERR_LAUNCH;
   }
-  int rc = launch_pdl(compact_scan_kernel, dim3((unsigned)ceil_div(E, 32)), dim3(SCAN_NT), 0, s,
-                      counts_ws, (int)ntiles, E);
-  if (rc != D2D_OK) return rc;
-  const size_t smem = sizeof(int) * ((size_t)ROWS * E + (size_t)E);
+  const size_t smem = sizeof(int) * ((size_t)ROWS * E + 2 * (size_t)EP);
   return launch_pdl(compact_scatter_kernel, dim3((unsigned)nchunks), dim3(NTS), smem, s, mask_bits,
-                    (const int32_t*)counts_ws, token_idx, offsets, N, E, (int)ntiles, dev_status);
+                    (const uint8_t*)counts, token_idx, offsets, N, E, EP, (int)ntiles, dev_status);
 }
 
 }  // namespace d2d
@@ -235,17 +250,15 @@ int launch_compact(const uint32_t* mask_bits, int32_t* token_idx, int32_t* offse
 // D2D_ERR_SCRATCH_LIMIT before anything is launched.
 //
 // The table is shared by every call in the process and keeps the previous call's
-// contents.  Nothing in it needs clearing: for N > 0 the count kernel writes all E cells
-// of each of the ceil(N/128) tile rows, the scan kernel then writes the totals row, and
-// the scatter kernel reads nothing else; for N = 0 no kernel touches the table (the
-// offsets are simply set to zero).
+// contents.  Nothing in it needs clearing: for N > 0 the count kernel writes every cell
+// (padding included) of each of the ceil(N/128) tile rows and the scatter kernel reads
+// nothing else; for N = 0 no kernel touches the table (the offsets are simply set to zero).
 // Two calls that run concurrently on one GPU (different streams) would overwrite
 // each other's counts: keep such calls on one stream or order them with events.
 // ---------------------------------------------------------------------------
 #define D2D_NOALLOC_MAX_CELLS (2048 * 128)
 
-// + one row of up to 256 expert totals behind the tile rows
-static __device__ __align__(256) int32_t g_noalloc_counts[D2D_NOALLOC_MAX_CELLS + 256];
+static __device__ __align__(256) int32_t g_noalloc_counts[D2D_NOALLOC_MAX_CELLS];
 
 namespace {
 
@@ -279,7 +292,11 @@ extern "C" int d2d_compact_noalloc(const uint32_t* mask_bits, int32_t* token_idx
                                    int64_t N, int E, int* dev_status, d2d_stream_t stream) {
   if (!mask_bits || !token_idx || !offsets || N < 0 || E < 1) return D2D_ERR_BAD_ARG;
   const int64_t ntiles = d2d::ceil_div64(N > 0 ? N : 1, d2d::CTILE);
-  if (ntiles * (int64_t)E > D2D_NOALLOC_MAX_CELLS) return D2D_ERR_SCRATCH_LIMIT;
+  // documented limit, and the table's actual bytes (rows are padded to at least 16 cells)
+  if (ntiles * (int64_t)E > D2D_NOALLOC_MAX_CELLS ||
+      ntiles * (int64_t)d2d::compact_row_cells(E > 0 && E <= 256 ? E : 256) >
+          (int64_t)sizeof(int32_t) * D2D_NOALLOC_MAX_CELLS)
+    return D2D_ERR_SCRATCH_LIMIT;
   int32_t* counts = nullptr;
   const int rc = noalloc_scratch(&counts);   // first call on a device looks the address up
   if (rc != D2D_OK) return rc;

@@ -292,7 +292,7 @@ template <typename T>
 __global__ void __launch_bounds__(NT)
 gate_scores_fused_kernel(const T* __restrict__ scores, float mult,
                          uint32_t* __restrict__ mask_bits, T* __restrict__ rt,
-                         int32_t* __restrict__ tile_counts,
+                         uint8_t* __restrict__ tile_counts, int EP,
                          const T* __restrict__ x, const T* __restrict__ last_bias,
                          int add_residual, T* __restrict__ out, int64_t N, int d, int E) {
   __shared__ int cnt[256];
@@ -301,53 +301,75 @@ gate_scores_fused_kernel(const T* __restrict__ scores, float mult,
   const int nw = (E + 31) / 32;
   const int64_t t0 = (int64_t)blockIdx.x * 128;
   for (int e = tid; e < E; e += NT) cnt[e] = 0;
-  __syncthreads();
-  int mine[8] = {0, 0, 0, 0, 0, 0, 0, 0};       // kept-count of expert lane+32j over my tokens
-  for (int i = 0; i < 16; ++i) {
-    const int64_t t = t0 + w * 16 + i;
-    if (t >= N) break;                           // warp-uniform
-    float s[8];
-    for (int j = 0; j < nw; ++j) {
-      const int e = lane + 32 * j;
-      s[j] = e < E ? DT<T>::to_f(scores[t * E + e]) : 0.f;
-    }
-    float m = -INFINITY;
-    for (int j = 0; j < nw; ++j)
-      if (lane + 32 * j < E) m = nanmax(m, s[j]);
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) m = nanmax(m, __shfl_xor_sync(0xffffffffu, m, o));
-    const float thr = DT<T>::round(__fmul_rn(m, mult));
-    for (int j = 0; j < nw; ++j) {
-      const bool keep = (lane + 32 * j < E) && (s[j] >= thr);
-      const uint32_t word = __ballot_sync(0xffffffffu, keep);
-      if (lane == 0) mask_bits[t * nw + j] = word;
-      if (rt && lane + 32 * j < E) rt[t * E + lane + 32 * j] = DT<T>::from_f(keep ? 1.0f : 0.0f);
-      mine[j] += keep ? 1 : 0;
-    }
-  }
-  for (int j = 0; j < nw; ++j)
-    if (lane + 32 * j < E && mine[j]) atomicAdd(&cnt[lane + 32 * j], mine[j]);
-  __syncthreads();
-  for (int e = tid; e < E; e += NT) tile_counts[(int64_t)blockIdx.x * E + e] = cnt[e];
+  // the tile's initial output rows first: these stores depend on nothing the rule computes
+  // and drain while it runs.  Warp w writes rows w, w+8, ...; a lane keeps its 16-byte
+  // column pieces of last_bias in registers.
   if (out) {
     const int dv = d / V;
     const int rows = (int)min((int64_t)128, N - t0);
-    for (int i = tid; i < rows * dv; i += NT) {
-      const int r = i / dv, cv = i - r * dv;
-      uint4 o = make_uint4(0u, 0u, 0u, 0u);
-      if (last_bias) o = __ldg(reinterpret_cast<const uint4*>(last_bias) + cv);
-      if (add_residual) {
-        const uint4 xv = __ldg(reinterpret_cast<const uint4*>(x + (t0 + r) * d) + cv);
-        const T* a = reinterpret_cast<const T*>(&o);
-        const T* b = reinterpret_cast<const T*>(&xv);
-        T rr[V];
+    for (int cv = lane; cv < dv; cv += 32) {
+      uint4 bz = make_uint4(0u, 0u, 0u, 0u);
+      if (last_bias) bz = __ldg(reinterpret_cast<const uint4*>(last_bias) + cv);
+#pragma unroll 4
+      for (int r = w; r < rows; r += NT / 32) {
+        uint4 o = bz;
+        if (add_residual) {
+          const uint4 xv = __ldg(reinterpret_cast<const uint4*>(x + (t0 + r) * d) + cv);
+          const T* a = reinterpret_cast<const T*>(&bz);
+          const T* b = reinterpret_cast<const T*>(&xv);
+          T rr[V];
 #pragma unroll
-        for (int q = 0; q < V; ++q) rr[q] = DT<T>::from_f(DT<T>::to_f(a[q]) + DT<T>::to_f(b[q]));
-        o = *reinterpret_cast<const uint4*>(rr);
+          for (int q = 0; q < V; ++q)
+            rr[q] = DT<T>::from_f(DT<T>::to_f(a[q]) + DT<T>::to_f(b[q]));
+          o = *reinterpret_cast<const uint4*>(rr);
+        }
+        *(reinterpret_cast<uint4*>(out + (t0 + r) * d) + cv) = o;
       }
-      *(reinterpret_cast<uint4*>(out + (t0 + r) * d) + cv) = o;
     }
   }
+  __syncthreads();
+  int mine[8] = {0, 0, 0, 0, 0, 0, 0, 0};       // kept-count of expert lane+32j over my tokens
+  // warp w applies the rule to tokens 16w..16w+15 (lane = expert); the scores of four tokens
+  // are loaded before the first of them is reduced, so the loads overlap
+  for (int i0 = 0; i0 < 16; i0 += 4) {
+    float s[4][8];
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      const int64_t t = t0 + w * 16 + i0 + u;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const int e = lane + 32 * j;
+        s[u][j] = (j < nw && t < N && e < E) ? DT<T>::to_f(scores[t * E + e]) : 0.f;
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      const int64_t t = t0 + w * 16 + i0 + u;
+      if (t >= N) break;                           // warp-uniform
+      float m = -INFINITY;
+#pragma unroll
+      for (int j = 0; j < 8; ++j)
+        if (j < nw && lane + 32 * j < E) m = nanmax(m, s[u][j]);
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) m = nanmax(m, __shfl_xor_sync(0xffffffffu, m, o));
+      const float thr = DT<T>::round(__fmul_rn(m, mult));
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        if (j >= nw) break;
+        const bool keep = (lane + 32 * j < E) && (s[u][j] >= thr);
+        const uint32_t word = __ballot_sync(0xffffffffu, keep);
+        if (lane == 0) mask_bits[t * nw + j] = word;
+        if (rt && lane + 32 * j < E) rt[t * E + lane + 32 * j] = DT<T>::from_f(keep ? 1.0f : 0.0f);
+        mine[j] += keep ? 1 : 0;
+      }
+    }
+  }
+#pragma unroll
+  for (int j = 0; j < 8; ++j)
+    if (j < nw && lane + 32 * j < E && mine[j]) atomicAdd(&cnt[lane + 32 * j], mine[j]);
+  __syncthreads();
+  for (int e = tid; e < EP; e += NT)
+    tile_counts[(int64_t)blockIdx.x * EP + e] = (uint8_t)(e < E ? cnt[e] : 0);
 }
 
 template <typename T>
@@ -490,11 +512,13 @@ int launch_gate_scores_fused(const void* scores, float mult, uint32_t* mask_bits
   if (grid > 0x7fffffffLL) return D2D_ERR_UNSUPPORTED;
   if (dtype == D2D_F32)
     gate_scores_fused_kernel<float><<<(unsigned)grid, NT, 0, s>>>(
-        (const float*)scores, mult, mask_bits, (float*)rt, tile_counts, (const float*)x,
+        (const float*)scores, mult, mask_bits, (float*)rt, reinterpret_cast<uint8_t*>(tile_counts),
+        compact_row_cells(E), (const float*)x,
         (const float*)last_bias, add_residual, (float*)out, N, d, E);
   else
     gate_scores_fused_kernel<bf16><<<(unsigned)grid, NT, 0, s>>>(
-        (const bf16*)scores, mult, mask_bits, (bf16*)rt, tile_counts, (const bf16*)x,
+        (const bf16*)scores, mult, mask_bits, (bf16*)rt, reinterpret_cast<uint8_t*>(tile_counts),
+        compact_row_cells(E), (const bf16*)x,
         (const bf16*)last_bias, add_residual, (bf16*)out, N, d, E);
   return cudaGetLastError() == cudaSuccess ? D2D_OK : D2D_ERR_LAUNCH;
 }

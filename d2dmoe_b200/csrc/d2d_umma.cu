@@ -55,7 +55,6 @@ constexpr int NTHREADS_EXPERTS = 608;    // + four warps that write the output r
 constexpr int WARP_MMA1 = 8, WARP_MMA2 = 9, WARP_BULK = 10, WARP_PROD0 = 11, WARP_WR0 = 15;
 constexpr int MAX_E = 128;
 constexpr int MODE_EXPERTS = 0, MODE_ROUTER = 1;
-constexpr long long PAIR_MIN_TOKENS = 1LL << 62;   // pairs only on request until they win
 
 struct Geo {
   int kc1;       // d / 64
@@ -92,7 +91,8 @@ struct Params {
   const bf16* last_bias;
   int add_residual;
   bf16* out_init;
-  int32_t* tile_counts;     // [tiles][E]: per-expert kept-token counts of each 128-token tile
+  uint8_t* tile_counts;     // [tiles][EP] bytes: per-expert kept-token counts of each 128-token tile
+  int EP;                   // cells per table row (compact_row_cells(E))
   int* dev_status;
   uint32_t wait_limit;      // polls per bounded wait
   int withhold;             // test hook: CTA 0 never loads its first weight tile
@@ -639,7 +639,7 @@ __device__ void role_epilogue_router(const Params& p, Ctl* c, uint32_t hs, uint3
           if (lane < nb && mine) atomicAdd(&c->tile_cnt[32 * jw + lane], mine);
         }
         asm volatile("bar.sync 1, 128;" ::: "memory");
-        if (r < E) p.tile_counts[(long long)tile * E + r] = c->tile_cnt[r];
+        if (r < p.EP) p.tile_counts[(long long)tile * p.EP + r] = (uint8_t)(r < E ? c->tile_cnt[r] : 0);
       }
     }
   }
@@ -1064,8 +1064,7 @@ std::mutex g_dev_lock;
 // test hooks (d2d_debug_configure): process-wide, read at launch
 std::atomic<uint32_t> g_wait_limit{WAIT_LIMIT};
 std::atomic<int> g_withhold{0};
-// 0 = chosen from the size, 1 = one CTA per tile, 2 = CTA pairs, 3 = one CTA per tile with
-// the rows gathered by TMA
+// expert rows: 0/1 = 16-byte cp.async gather (default), 2 = TMA tile::gather4
 std::atomic<int> g_experts_kernel{0};
 
 static_assert(1024 + (size_t)SLOTS_TOTAL * SLOT + sizeof(Ctl) + 64 <= 232448,
@@ -1158,28 +1157,19 @@ int launch_experts_umma(const void* x, const int32_t* token_idx, const int32_t* 
   p.act = act;
   p.glu = glu ? 1 : 0;
   p.dev_status = dev_status;
-  // CTA pairs halve the weight bytes per row but work on 256-row units: they pay off once
-  // the token lists are long enough to keep every pair busy for several tiles
-  const int which = g_experts_kernel.load();
-  p.tma_gather = which == 3 ? 1 : 0;
-  const bool pair = which == 2 || (which == 0 && N >= PAIR_MIN_TOKENS);
-  if (pair && pair_experts_supported(d, E, H, glu, D2D_BF16)) {
-    const int rc = launch_experts_pair(x, token_idx, offsets, packed, out, N, d, E, H, glu, act,
-                                       dev_status, g_wait_limit.load(), g_withhold.load(), s);
-    if (rc != D2D_ERR_UNSUPPORTED) return rc;      // no cluster launch on this device: one CTA per tile
-  }
+  p.tma_gather = g_experts_kernel.load() == 2 ? 1 : 0;
   const long long max_tiles = (N * (long long)E + TILE_M - 1) / TILE_M + E;
   return launch<MODE_EXPERTS>(p, max_tiles, s);
 }
 
 void umma_debug_select_experts_kernel(int which) {
-  g_experts_kernel.store(which >= 1 && which <= 3 ? which : 0);
+  g_experts_kernel.store(which == 2 ? 2 : 0);
 }
 
 void umma_debug_configure(int wait_limit_log2, int withhold_weight_tile) {
   g_wait_limit.store(wait_limit_log2 >= 4 && wait_limit_log2 <= 22 ? 1u << wait_limit_log2
                                                                     : WAIT_LIMIT);
-  g_withhold.store(withhold_weight_tile);
+  g_withhold.store(withhold_weight_tile ? 1 : 0);
 }
 
 bool umma_router_supported(int d, int R, int E, int dtype) {
@@ -1215,7 +1205,8 @@ int launch_router_mask_umma(const void* x, const void* packed, float mult, uint3
   p.last_bias = (const bf16*)last_bias;
   p.add_residual = add_residual;
   p.out_init = (bf16*)out_init;
-  p.tile_counts = tile_counts;
+  p.tile_counts = reinterpret_cast<uint8_t*>(tile_counts);
+  p.EP = compact_row_cells(E);
   p.dev_status = dev_status;
   return launch<MODE_ROUTER>(p, (N + TILE_M - 1) / TILE_M, s);
 }

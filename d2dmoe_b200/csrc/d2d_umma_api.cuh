@@ -21,14 +21,8 @@ int launch_router_mask_umma(const void* x, const void* packed, float mult, uint3
                             void* out_init, int32_t* tile_counts, int64_t N, int d, int R, int E,
                             int* dev_status, cudaStream_t s);
 
-// expert FFN on CTA pairs (tcgen05 cta_group::2, d2d_umma_pair.cu); same packed weights.
-// D2D_ERR_UNSUPPORTED when the device cannot co-schedule a 2-CTA cluster of this kernel.
-bool pair_experts_supported(int d, int E, int H, bool glu, int dtype);
-int launch_experts_pair(const void* x, const int32_t* token_idx, const int32_t* offsets,
-                        const void* packed, void* out, int64_t N, int d, int E, int H, bool glu,
-                        int act, int* dev_status, uint32_t wait_limit, int withhold,
-                        cudaStream_t s);
-// test hook: 0 = choose the expert kernel from the size, 1 = one CTA per tile, 2 = CTA pairs
+// test hook: how the expert kernel gathers its token rows: 0/1 = 16-byte cp.async
+// (default), 2 = TMA tile::gather4
 void umma_debug_select_experts_kernel(int which);
 
 // test hooks: poll limit of the bounded device waits (2^log2, out of range = default) and

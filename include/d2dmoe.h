@@ -186,9 +186,9 @@ int d2d_moe_forward(const void* x, const void* wa, const void* wb, const void* r
                     void* ws, size_t ws_bytes, int* dev_status,
                     void* routing_tensor_opt, d2d_stream_t stream);
 
-/* Number of kernels the calling thread's last d2d_moe_forward issued (4 on the tensor-core
- * path: router + rule, compaction scan, compaction scatter, expert FFN; more on the
- * general-shape paths).  Introspection for benchmarks; no upstream counterpart. */
+/* Number of kernels the calling thread's last d2d_moe_forward issued (3 on the tensor-core
+ * path: router + rule, compaction scatter, expert FFN; more on the general-shape
+ * paths).  Introspection for benchmarks; no upstream counterpart. */
 int d2d_last_forward_launches(void);
 
 /* Test hook, no upstream counterpart.  Every wait inside the tensor-core kernels is bounded;
@@ -200,11 +200,10 @@ int d2d_last_forward_launches(void);
  * d2d_debug_configure(0, 0) to return to normal operation. */
 int d2d_debug_configure(int wait_limit_log2, int withhold_weight_tile);
 
-/* Test hook, no upstream counterpart.  The bf16 expert FFN exists in two tilings: one CTA
- * per 128 rows of an expert's token list, and CTA pairs (tcgen05 cta_group::2) per 256 rows,
- * each CTA loading half of every weight tile.  which = 0: chosen from the token count
- * (default); 1: always one CTA per tile; 2: always CTA pairs; 3: one CTA per tile with the token
- * rows gathered by TMA (cp.async.bulk.tensor tile::gather4) instead of 16-byte cp.async. */
+/* Test hook, no upstream counterpart.  How the bf16 expert kernel brings the rows of an
+ * expert's token list into shared memory: which = 0 or 1: 16-byte cp.async per row piece
+ * (default, the faster one on B200); 2: TMA gathers (cp.async.bulk.tensor tile::gather4, four
+ * rows per copy), kept so that the two can be compared on any workload. */
 int d2d_debug_select_experts_kernel(int which);
 
 /* One-time re-layout of the weights into the shared-memory tile images the

@@ -24,9 +24,9 @@ def pytest_collection_modifyitems(config, items):
 
 @pytest.fixture(scope="session", autouse=True)
 def _experts_kernel_choice():
-    """D2D_TEST_EXPERTS_KERNEL=1|2 runs the whole suite with the bf16 expert FFN forced to
-    one tiling (1: one CTA per 128-row tile, 2: CTA pairs per 256 rows) instead of the choice
-    the library makes from the token count, so that every parity case reaches both."""
+    """D2D_TEST_EXPERTS_KERNEL=2 runs the whole suite with the bf16 expert kernel gathering
+    its token rows by TMA (tile::gather4) instead of the default 16-byte cp.async, so that
+    every parity case reaches both row paths."""
     import os
     which = int(os.environ.get("D2D_TEST_EXPERTS_KERNEL", "0"))
     if which:
