@@ -726,7 +726,7 @@ def run_ours(args):
 
 
 def main():
-    global HEADLINE_TAU
+    global HEADLINE_TAU, HEADLINE
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=100)
@@ -746,8 +746,12 @@ def main():
                     help="time eager launches instead of CUDA-graph replays of the step")
     ap.add_argument("--quick", action="store_true",
                     help="profiling aid: headline timing only (no sweep, stages, e2e, CPU legs)")
+    ap.add_argument("--config", default=HEADLINE, choices=list(CONFIGS),
+                    help="profiling aid: time another configuration as the quick workload "
+                         "(use with --quick; not a bench value)")
     args = ap.parse_args()
     HEADLINE_TAU = args.tau
+    HEADLINE = args.config
     if args.impl == "reference":
         run_reference(args)
     else:

@@ -372,6 +372,92 @@ gate_scores_fused_kernel(const T* __restrict__ scores, float mult,
     tile_counts[(int64_t)blockIdx.x * EP + e] = (uint8_t)(e < E ? cnt[e] : 0);
 }
 
+// The same kernel for rows of at most 8 sixteen-byte vectors (E <= 64 in bf16, E <= 32 in
+// fp32, E * sizeof(T) a multiple of 16): one LANE per token.  A lane loads its token's
+// whole score row with vector loads and finds the row maximum, the threshold and the mask
+// word(s) in its own registers, with no cross-lane traffic, so a warp settles 32 tokens in
+// the time the warp-per-token form needs for one; warps 0-3 take the tile's 128 tokens.
+// The per-expert counts of the tile come from one ballot per expert and warp.
+template <typename T, int NV>
+__global__ void __launch_bounds__(NT)
+gate_scores_fused_rows_kernel(const T* __restrict__ scores, float mult,
+                              uint32_t* __restrict__ mask_bits, T* __restrict__ rt,
+                              uint8_t* __restrict__ tile_counts, int EP,
+                              const T* __restrict__ x, const T* __restrict__ last_bias,
+                              int add_residual, T* __restrict__ out, int64_t N, int d, int E) {
+  __shared__ int cnt[64];
+  constexpr int V = 16 / sizeof(T);
+  constexpr int EMAX = NV * V;
+  const int tid = threadIdx.x, lane = tid & 31, w = tid >> 5;
+  const int nw = (E + 31) / 32;
+  const int64_t t0 = (int64_t)blockIdx.x * 128;
+  if (tid < 64) cnt[tid] = 0;
+  // this lane's score row first: the loads fly while the initial output rows are issued
+  const int64_t t = t0 + w * 32 + lane;
+  uint4 raw[NV];
+  if (w < 4) {
+#pragma unroll
+    for (int v = 0; v < NV; ++v)
+      raw[v] = t < N ? __ldg(reinterpret_cast<const uint4*>(scores + t * E) + v)
+                     : make_uint4(0u, 0u, 0u, 0u);
+  }
+  if (out) {
+    const int dv = d / V;
+    const int rows = (int)min((int64_t)128, N - t0);
+    for (int cv = lane; cv < dv; cv += 32) {
+      uint4 bz = make_uint4(0u, 0u, 0u, 0u);
+      if (last_bias) bz = __ldg(reinterpret_cast<const uint4*>(last_bias) + cv);
+#pragma unroll 4
+      for (int r = w; r < rows; r += NT / 32) {
+        uint4 o = bz;
+        if (add_residual) {
+          const uint4 xv = __ldg(reinterpret_cast<const uint4*>(x + (t0 + r) * d) + cv);
+          const T* a = reinterpret_cast<const T*>(&bz);
+          const T* b = reinterpret_cast<const T*>(&xv);
+          T rr[V];
+#pragma unroll
+          for (int q = 0; q < V; ++q)
+            rr[q] = DT<T>::from_f(DT<T>::to_f(a[q]) + DT<T>::to_f(b[q]));
+          o = *reinterpret_cast<const uint4*>(rr);
+        }
+        *(reinterpret_cast<uint4*>(out + (t0 + r) * d) + cv) = o;
+      }
+    }
+  }
+  __syncthreads();
+  if (w < 4) {
+    const T* sv = reinterpret_cast<const T*>(raw);
+    float m = -INFINITY;
+#pragma unroll
+    for (int e = 0; e < EMAX; ++e)
+      if (e < E) m = nanmax(m, DT<T>::to_f(sv[e]));
+    const float thr = DT<T>::round(__fmul_rn(m, mult));
+    uint32_t word[2] = {0u, 0u};
+    uint4 one[NV];
+    T* ov = reinterpret_cast<T*>(one);
+#pragma unroll
+    for (int e = 0; e < EMAX; ++e) {
+      const bool keep = e < E && DT<T>::to_f(sv[e]) >= thr;
+      if (keep) word[e >> 5] |= 1u << (e & 31);
+      ov[e] = DT<T>::from_f(keep ? 1.0f : 0.0f);
+    }
+    if (t < N) {
+      for (int j = 0; j < nw; ++j) mask_bits[t * nw + j] = word[j];
+      if (rt) {
+#pragma unroll
+        for (int v = 0; v < NV; ++v) *(reinterpret_cast<uint4*>(rt + t * E) + v) = one[v];
+      }
+    }
+    for (int e = 0; e < E; ++e) {
+      const int c = __popc(__ballot_sync(0xffffffffu, t < N && ((word[e >> 5] >> (e & 31)) & 1u)));
+      if (lane == 0 && c) atomicAdd(&cnt[e], c);
+    }
+  }
+  __syncthreads();
+  for (int e = tid; e < EP; e += NT)
+    tile_counts[(int64_t)blockIdx.x * EP + e] = (uint8_t)(e < E ? cnt[e] : 0);
+}
+
 template <typename T>
 __global__ void __launch_bounds__(NT)
 init_out_kernel(const T* __restrict__ x, const T* __restrict__ last_bias, int add_residual,
@@ -510,6 +596,34 @@ int launch_gate_scores_fused(const void* scores, float mult, uint32_t* mask_bits
     return D2D_ERR_UNSUPPORTED;
   const int64_t grid = ceil_div64(N, 128);
   if (grid > 0x7fffffffLL) return D2D_ERR_UNSUPPORTED;
+  // score rows of whole 16-byte vectors, at most 8 of them: one lane per token
+  const int row_bytes = E * (dtype == D2D_F32 ? 4 : 2);
+  const bool rows_form = row_bytes % 16 == 0 && row_bytes <= 128 && al16(scores) &&
+                         (rt == nullptr || al16(rt));
+#define D2D_ROWS_CASE(T, NVV)                                                                 \
+  case NVV:                                                                                   \
+    gate_scores_fused_rows_kernel<T, NVV><<<(unsigned)grid, NT, 0, s>>>(                      \
+        (const T*)scores, mult, mask_bits, (T*)rt, reinterpret_cast<uint8_t*>(tile_counts),   \
+        compact_row_cells(E), (const T*)x, (const T*)last_bias, add_residual, (T*)out, N, d,  \
+        E);                                                                                   \
+    break;
+  if (rows_form) {
+    if (dtype == D2D_F32) {
+      switch (row_bytes / 16) {
+        D2D_ROWS_CASE(float, 1) D2D_ROWS_CASE(float, 2) D2D_ROWS_CASE(float, 3)
+        D2D_ROWS_CASE(float, 4) D2D_ROWS_CASE(float, 5) D2D_ROWS_CASE(float, 6)
+        D2D_ROWS_CASE(float, 7) D2D_ROWS_CASE(float, 8)
+      }
+    } else {
+      switch (row_bytes / 16) {
+        D2D_ROWS_CASE(bf16, 1) D2D_ROWS_CASE(bf16, 2) D2D_ROWS_CASE(bf16, 3)
+        D2D_ROWS_CASE(bf16, 4) D2D_ROWS_CASE(bf16, 5) D2D_ROWS_CASE(bf16, 6)
+        D2D_ROWS_CASE(bf16, 7) D2D_ROWS_CASE(bf16, 8)
+      }
+    }
+    return cudaGetLastError() == cudaSuccess ? D2D_OK : D2D_ERR_LAUNCH;
+  }
+#undef D2D_ROWS_CASE
   if (dtype == D2D_F32)
     gate_scores_fused_kernel<float><<<(unsigned)grid, NT, 0, s>>>(
         (const float*)scores, mult, mask_bits, (float*)rt, reinterpret_cast<uint8_t*>(tile_counts),
