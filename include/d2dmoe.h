@@ -161,6 +161,14 @@ int d2d_compact_noalloc(const uint32_t* mask_bits, int32_t* token_idx, int32_t* 
  * accumulate = 0: out is first set to last_bias_opt (+ x);  accumulate = 1: out
  * already holds its initial value (d2d_router_mask's out_init_opt) and
  * last_bias_opt / add_residual are ignored.
+ * Summation order (bf16): the contributions are added to the initial value one by one in
+ * the activation dtype, like upstream's atomic kernel (architectures/moe/moe_impls.py:300-301)
+ * and unlike upstream's CPU path, which sums the experts first and adds last_bias and x
+ * last (architectures/moe/moefication.py:96-99): a token kept by k experts sees k + 1
+ * roundings at the magnitude of its output instead of one, and the order of the adds is
+ * not fixed, so outputs are reproducible to that rounding, not bit for bit.  The first
+ * layer rounds to T after the product, after + b1 and after the activation, as the
+ * upstream CPU path does.
  * experts_packed_opt: buffer made by d2d_prepack_experts, or NULL. */
 int d2d_experts_ffn(const void* x, const int32_t* token_idx, const int32_t* offsets,
                     const void* w1, const void* b1_opt, const void* w_up_opt, const void* w2,

@@ -587,3 +587,34 @@ def test_bounded_wait_runs_out_and_the_next_launch_is_clean():
     torch.cuda.synchronize()
     wsp.check_status()
     assert O.rel_err(out.float().cpu(), ref.float().cpu()) <= TOL["bf16"]
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs in one process")
+def test_two_devices_driven_by_one_process():
+    """One process, two GPUs, neither made current by the caller beforehand: the library keeps
+    its launch facts (shared-memory opt-in, SM count) per device and the wrappers make the
+    tensors' device current, so the same layer gives the same bits for mask and lists, and the
+    same output within tolerance, on both."""
+    import d2dmoe_b200 as D
+    c = C.LayerCase("twodev", 4, 197, 256, 64, 16, tau=0.2, dtype="bf16")
+    t = C.make_tensors(c)
+    outs = []
+    for dev_i in (1, 0, 1):                       # second device first
+        dev_ = torch.device("cuda", dev_i)
+        moe = D.MoeficationMoE(c.name, c.d, c.E, True, c.H, torch.nn.ReLU)
+        moe.router = D.MoeficationRouter(c.d, c.E, width=c.R, depth=2, bias=False,
+                                         activation="relu", output_activation="abs")
+        moe = moe.to(torch.bfloat16)
+        moe.load_state_dict({"experts.w1": t["w1"], "experts.b1": t["b1"], "experts.w2": t["w2"],
+                             "last_bias": t["last_bias"], "router.layers.0.weight": t["wa"],
+                             "router.layers.2.weight": t["wb"]})
+        moe = moe.to(dev_)
+        moe.forward_mode, moe.tau = "dynk_max", c.tau
+        out, gd = moe(t["x"].to(dev_))            # current device stays cuda:0 throughout
+        torch.cuda.synchronize(dev_)
+        moe.last_workspace(c.N, dev_).check_status()
+        outs.append((out.float().cpu(), gd[c.name][0].cpu()))
+    assert torch.cuda.current_device() == 0
+    for o, rt in outs[1:]:
+        assert torch.equal(rt, outs[0][1])
+        assert O.rel_err(o, outs[0][0]) <= TOL["bf16"]
