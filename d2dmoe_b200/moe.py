@@ -256,7 +256,7 @@ _HOST_STREAMS: dict = {}
 
 class MoELayer(nn.Module):
     def __init__(self, name, num_experts):
-        super().__init__()
+        nn.Module.__init__(self)      # not super(): bind_upstream() may re-base this class
         self.name = name
         self.num_experts = num_experts
 
@@ -519,6 +519,36 @@ class MoeficationMoE(MoELayer):
         return self._wsp.get(n, self.num_experts, device)
 
 
+def bind_upstream(moe_layers=None) -> bool:
+    """Make these classes first-class citizens of the upstream code base when this package is
+    used inside it.  The upstream block and attention forwards decide with
+    ``isinstance(module, MoELayer)`` whether a sub-module returns ``(out, gating_data)``
+    (architectures/moe/moe_models.py:20-46,71,93,150), and ``replace_with_moes`` builds experts
+    from ``MOE_IMPL_MAP[experts_class]`` (architectures/moe/moefication.py:39,157-167).  This
+    re-bases ``MoELayer`` / ``ExpertsLayer`` here onto the upstream classes of the same name and
+    registers ``'b200_kernel'`` / ``'b200_glu'`` in the upstream map, so that a layer of this
+    package dropped into an upstream model is dispatched exactly like an upstream one (FFN
+    blocks and MoE-fied q/k/v/o attention projections alike).
+
+    ``moe_layers``: the upstream module ``architectures.moe.moe_layers`` (imported here when
+    None).  Returns False when the upstream package cannot be imported.  Called automatically at
+    import when the upstream module is already loaded."""
+    if moe_layers is None:
+        try:
+            import importlib
+            moe_layers = importlib.import_module("architectures.moe.moe_layers")
+        except Exception:      # noqa: BLE001  (not inside the upstream tree)
+            return False
+    up_moe, up_experts = moe_layers.MoELayer, moe_layers.ExpertsLayer
+    if up_moe not in MoELayer.__mro__:
+        MoELayer.__bases__ = (up_moe,)
+    if up_experts not in ExpertsLayer.__mro__:
+        ExpertsLayer.__bases__ = (up_experts,)
+    moe_layers.MOE_IMPL_MAP.setdefault("b200_kernel", B200KernelExperts)
+    moe_layers.MOE_IMPL_MAP.setdefault("b200_glu", B200GluExperts)
+    return True
+
+
 def add_routers(model: nn.Module, router_args: dict) -> dict:
     """Attach a MoeficationRouter to every MoeficationMoE of ``model``
     (architectures/moe/moefication.py:342-354)."""
@@ -529,3 +559,9 @@ def add_routers(model: nn.Module, router_args: dict) -> dict:
             found[name] = m
     assert len(found) > 0
     return found
+
+
+import sys as _sys      # noqa: E402
+
+if "architectures.moe.moe_layers" in _sys.modules:
+    bind_upstream(_sys.modules["architectures.moe.moe_layers"])

@@ -73,8 +73,18 @@ ROWS_SAVED = {"gemma_shape": 96, "gemma_shape_k": 96}
 TOKEN_CHUNK = {"gemma_shape": 192, "gemma_shape_k": 192}
 
 
+def attention_projection_case() -> C.LayerCase:
+    """A MoE-fied attention projection of ViT-B/16 (architectures/moe/dsti.py:88-138 with
+    flops_factor 1: attention_dim = round((d*d + d) / (2d + 1)) = 384, split into 12 experts of
+    32; architectures/moe/moe_models.py:13-52 calls it like any MoE layer): GELU, last bias,
+    residual connection, bf16."""
+    return C.LayerCase("attn_proj_residual", 2, 197, 768, 32, 12, tau=0.2, dtype="bf16",
+                       act="gelu", zero_last_bias=False, residual=True, seed=7)
+
+
 def all_cases():
-    return C.parity_grid() + [C.config0(), glu_case(), glu_case_bf16()] + gemma_shape_cases()
+    return C.parity_grid() + [C.config0(), glu_case(), glu_case_bf16()] + gemma_shape_cases() + \
+        [attention_projection_case()]
 
 
 def build_reference_module(ref, c: C.LayerCase, t: dict):
