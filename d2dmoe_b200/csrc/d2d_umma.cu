@@ -8,29 +8,36 @@
 //   router  : per 128 consecutive tokens
 //               s = |bf16(relu(bf16(x Wa^T)) Wb^T)|, keep e iff s_e >= bf16(max s * mult)
 //             (architectures/moe/moefication.py:328-330 and :80-85), written as mask
-//             bits; the same CTA writes the layer output's initial value.
+//             bits (and, on request, as the 0/1 routing tensor); the same CTA writes the
+//             layer output's initial value and the compaction's counts table.
 //
-// Both are one persistent kernel (one CTA of 480 threads per SM, tile = 128 rows):
-// GEMM1 (K = d) into a double-buffered TMEM accumulator, an epilogue that turns it into
-// the bf16 A operand of GEMM2 in shared memory, GEMM2 (K = hidden width) per 128-column
-// chunk into a second double-buffered TMEM accumulator, and a second epilogue.
+// Both are one persistent kernel (one CTA per SM: 480 threads in the router form, 608 in
+// the experts form; tile = 128 rows): GEMM1 (K = d) into a double-buffered TMEM accumulator,
+// an epilogue that turns it into the bf16 A operand of GEMM2 in shared memory, GEMM2
+// (K = hidden width) per 128-column chunk into a second double-buffered TMEM accumulator,
+// and a second epilogue.
 //
 // Warp roles:
-//   warps 0-7   epilogues, two groups of four (warp w reads TMEM lanes 32*(w%4)..+31 =
-//               tile rows).  Group g takes every other 16-column block of epilogue 1 and
-//               the GEMM2 chunks that land in accumulator buffer g.  Experts: bf16 rows
-//               are staged per warp in shared memory and added to out[token] with
-//               row-contiguous red.global.add.noftz.v4.bf16x2 (4 cache lines per
-//               instruction).  Router: |.|, row max, threshold, mask word, per-tile
-//               expert counts for the compaction, and the layer output's initial value.
-//   warp  8     TMEM allocation; GEMM1 stream: waits (lanes poll the A and W1 stage
-//               barriers in parallel), one elected lane issues tcgen05.mma / commit
-//   warp  9     GEMM2 stream, same scheme, on its own weight ring
-//   warp 10     streams packed weight tiles with cp.async.bulk (TMA, 1-D) into the two
-//               weight rings, whichever has a free stage
-//   warps 11-14 gather token rows of x with 16-byte cp.async into ring A in the
-//               128-byte-swizzled K-major layout the MMA descriptors expect; stage
-//               barriers are signalled by cp.async.mbarrier.arrive
+//   experts form
+//     warps 0-3   epilogue 1: accumulator 1 -> + b1, activation (x up-projection) -> hidden tile
+//     warps 4-7   accumulator 2 -> bf16 -> two alternating 4 KB staging blocks per warp
+//     warps 15-18 read the blocks back row-contiguous and add them to out[token] with
+//                 red.global.add.noftz.v4.bf16x2 (4 cache lines per instruction)
+//     warps 11-14 gather the tile's token rows of x with 16-byte cp.async into ring A in the
+//                 128-byte-swizzled K-major layout the MMA descriptors expect; stage barriers
+//                 are signalled by cp.async.mbarrier.arrive.  (Selectable instead: warp 11
+//                 gathers them with TMA tile::gather4 copies, four rows per copy.)
+//   router form
+//     warps 0-7   two epilogue groups of four: epilogue 1 (ReLU hidden tile), then group 0:
+//                 |.|, row max, threshold, mask word, the row of the 0/1 routing tensor,
+//                 per-tile expert counts for the compaction; warp 7 issues the output's
+//                 initial rows as TMA row stores
+//     warp 11     one lane issues one tiled TMA box (128 rows x 64 columns of x) per stage
+//   both
+//     warp  8     TMEM allocation; one thread issues the GEMM1 stream (tcgen05.mma / commit)
+//     warp  9     one thread issues the GEMM2 stream on its own weight ring
+//     warp 10     one thread streams packed weight tiles with cp.async.bulk (TMA, 1-D) into
+//                 the two weight rings, whichever has a free stage
 // Weights are packed once (d2d_prepack_*) into exactly the shared-memory images the
 // MMA reads, so a weight tile is one contiguous bulk copy.  No multicast loads.
 //
