@@ -636,7 +636,7 @@ def run_ours(args):
         # layer calls queue back to back on the shared copy/compute streams and the step
         # ends when every layer's output has arrived in host memory
         for i, m in enumerate(stack.mods):
-            m.forward_host(hx[i % nh], ho[i % nh], chunks=4, sync=False)
+            m.forward_host(hx[i % nh], ho[i % nh], chunks=2, sync=False)
         Dm.MoeficationMoE.host_synchronize(dev)
 
     e2e_steps = max(2, min(steps, 5))
@@ -706,7 +706,7 @@ def run_ours(args):
                 "d2h_bytes_per_step": bytes_x,
                 "copy_ceiling_tokens_per_s": e2e_ceiling,
                 "frac_of_copy_ceiling": e2e_val / e2e_ceiling,
-                "api": "MoeficationMoE.forward_host (pinned host x -> pinned host out, 4 slices "
+                "api": "MoeficationMoE.forward_host (pinned host x -> pinned host out, 2 slices "
                        "per layer, layers pipelined); bytes are per rank"},
         # kernels per layer call: what the library counted for the last d2d_moe_forward
         # (router+rule, compaction scan, compaction scatter, expert FFN) + the routing-tensor
