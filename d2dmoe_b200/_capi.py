@@ -32,6 +32,7 @@ SIGNATURES = {
     "d2d_mask_rule_from_scores": (_i, [_p, _i, _i, _f, _p, _i64, _i, _i, _p, _p]),
     "d2d_init_out": (_i, [_p, _p, _i, _p, _i64, _i, _i, _p]),
     "d2d_expand_mask": (_i, [_p, _p, _i64, _i, _i, _p]),
+    "d2d_prenorm_init": (_i, [_p, _p, _p, _f, _i, _f, _p, _p, _p, _i64, _i, _i, _p]),
     "d2d_pack_mask": (_i, [_p, _p, _i64, _i, _i, _p]),
     "d2d_compact": (_i, [_p, _p, _p, _i64, _i, _p, _sz, _p, _p]),
     "d2d_compact_noalloc": (_i, [_p, _p, _p, _i64, _i, _p, _p]),

@@ -95,6 +95,17 @@ int d2d_init_out(const void* x, const void* last_bias_opt, int add_residual, voi
   return launch_init_out(x, last_bias_opt, add_residual, out, N, d, dtype, (cudaStream_t)stream);
 }
 
+int d2d_prenorm_init(const void* x, const void* gamma, const void* beta_opt, float eps, int kind,
+                     float gamma_offset, const void* last_bias_opt, void* xn, void* out_init_opt,
+                     int64_t N, int d, int dtype, d2d_stream_t stream) {
+  if (!x || !gamma || !xn || N < 0 || d < 1 || (kind != D2D_NORM_LAYER && kind != D2D_NORM_RMS))
+    return D2D_ERR_BAD_ARG;
+  if (!dtype_ok(dtype)) return D2D_ERR_UNSUPPORTED;
+  if (N == 0) return D2D_OK;
+  return launch_prenorm_init(x, gamma, beta_opt, eps, kind, gamma_offset, last_bias_opt, xn,
+                             out_init_opt, N, d, dtype, (cudaStream_t)stream);
+}
+
 int d2d_expand_mask(const uint32_t* mask_bits, void* routing_tensor, int64_t N, int E, int dtype,
                     d2d_stream_t stream) {
   if (!mask_bits || !routing_tensor || N < 0 || E < 1) return D2D_ERR_BAD_ARG;
@@ -163,15 +174,20 @@ int d2d_moe_forward(const void* x, const void* wa, const void* wb, const void* r
     return D2D_ERR_BAD_ARG;
   if (!dtype_ok(dtype) || act < D2D_RELU || act > D2D_GELU_TANH) return D2D_ERR_UNSUPPORTED;
   if (ws_bytes < compact_workspace_bytes(N, E)) return D2D_ERR_WORKSPACE;
+  if (add_residual < 0 || add_residual > D2D_OUT_PREINITIALISED) return D2D_ERR_BAD_ARG;
   if (N == 0) return D2D_OK;
+  // out already initialised by the caller (d2d_prenorm_init): the first kernel writes no rows
+  const bool pre = add_residual == D2D_OUT_PREINITIALISED;
+  void* out_init = pre ? nullptr : out;
+  if (pre) {
+    add_residual = 0;
+    last_bias_opt = nullptr;
+  }
   if (scores_in_opt) {
     // rule + counts table + output init in one launch when the shape allows it
-    rc = (dtype_ok(dtype) && out && d >= 1 && E >= 1 && (!add_residual || x))
-             ? launch_gate_scores_fused(scores_in_opt, thresh_mult, mask_bits, routing_tensor_opt,
-                                        (int32_t*)ws, x,
-                                        last_bias_opt, add_residual, out, N, d, E, dtype,
-                                        (cudaStream_t)stream)
-             : D2D_ERR_UNSUPPORTED;
+    rc = launch_gate_scores_fused(scores_in_opt, thresh_mult, mask_bits, routing_tensor_opt,
+                                  (int32_t*)ws, x, last_bias_opt, add_residual, out_init, N, d, E,
+                                  dtype, (cudaStream_t)stream);
     if (rc == D2D_OK) {
       counts_ready = true;
       rt_done = true;
@@ -180,21 +196,25 @@ int d2d_moe_forward(const void* x, const void* wa, const void* wb, const void* r
       rc = d2d_mask_from_scores(scores_in_opt, thresh_mult, mask_bits, N, E, dtype, dev_status,
                                 stream);
       if (rc != D2D_OK) return rc;
-      rc = d2d_init_out(x, last_bias_opt, add_residual, out, N, d, dtype, stream);
-      nl += 2;
+      nl += 1;
+      if (!pre) {
+        rc = d2d_init_out(x, last_bias_opt, add_residual, out, N, d, dtype, stream);
+        nl += 1;
+      }
     }
   } else if (router_packed_opt && wb && R >= 1 && umma_router_supported(d, R, E, dtype) &&
              aligned(last_bias_opt, 16) && aligned(router_packed_opt, 1024)) {
     // the tensor-core router also fills the compaction's counts table
     rc = launch_router_mask_umma(x, router_packed_opt, thresh_mult, mask_bits, nullptr,
-                                 routing_tensor_opt, last_bias_opt, add_residual, out,
+                                 routing_tensor_opt, last_bias_opt, add_residual, out_init,
                                  (int32_t*)ws, N, d, R, E, dev_status, (cudaStream_t)stream);
     counts_ready = true;
     rt_done = true;
     nl += 1;
   } else {
     rc = d2d_router_mask(x, wa, wb, router_packed_opt, thresh_mult, mask_bits, nullptr,
-                         last_bias_opt, add_residual, out, N, d, R, E, dtype, dev_status, stream);
+                         last_bias_opt, add_residual, out_init, N, d, R, E, dtype, dev_status,
+                         stream);
     nl += 1;
   }
   if (rc != D2D_OK) return rc;

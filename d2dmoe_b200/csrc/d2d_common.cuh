@@ -136,6 +136,9 @@ int launch_gate_scores_fused(const void* scores, float mult, uint32_t* mask_bits
                              cudaStream_t s);
 int launch_init_out(const void* x, const void* last_bias, int add_residual, void* out, int64_t N,
                     int d, int dtype, cudaStream_t s);
+int launch_prenorm_init(const void* x, const void* gamma, const void* beta, float eps, int kind,
+                        float gamma_offset, const void* last_bias, void* xn, void* out, int64_t N,
+                        int d, int dtype, cudaStream_t s);
 int launch_expand_mask(const uint32_t* mask_bits, void* rt, int64_t N, int E, int dtype,
                        cudaStream_t s);
 int launch_pack_mask(const void* rt, uint32_t* mask_bits, int64_t N, int E, int dtype,

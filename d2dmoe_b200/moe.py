@@ -435,6 +435,66 @@ class MoeficationMoE(MoELayer):
                             add_residual=self.add_residual_connection, accumulate=False)
         return out.view(orig_size), {self.name: (rt,)}
 
+    # -- pre-norm + residual fused around the layer -----------------------------------
+    @staticmethod
+    def _norm_args(norm):
+        """(kind, gamma, beta, eps, gamma_offset) of a normalisation module the fused pre-norm
+        pass can evaluate, or None: nn.LayerNorm over the last dimension with affine
+        parameters, torch's RMSNorm, and Gemma-style RMSNorm modules (weight applied as
+        1 + weight, transformers GemmaRMSNorm)."""
+        if isinstance(norm, nn.LayerNorm):
+            if norm.weight is None or len(norm.normalized_shape) != 1:
+                return None
+            return ops.NORM_LAYER, norm.weight, norm.bias, float(norm.eps), 0.0
+        name = type(norm).__name__
+        if "RMSNorm" in name and getattr(norm, "weight", None) is not None:
+            eps = getattr(norm, "eps", None)
+            if eps is None:
+                eps = getattr(norm, "variance_epsilon", None)
+            if eps is None:
+                eps = torch.finfo(norm.weight.dtype).eps
+            return ops.NORM_RMS, norm.weight, None, float(eps), 1.0 if "Gemma" in name else 0.0
+        return None
+
+    @torch.no_grad()
+    def forward_block(self, x, norm):
+        """``x + self(norm(x))``: the second half of an upstream transformer block
+        (architectures/moe/moe_models.py:69-76 ViT, :91-100 GPT, :148-156 Gemma:
+        ``y = ln_2(x); y, gd = mlp(y); return x + y``) with the normalisation pass and the
+        residual add folded into the layer: one pass reads x once and writes the normalised
+        rows and ``x + last_bias`` as the output's initial value, and the layer adds the expert
+        outputs to that.  Returns ``(x + out, {name: (routing_tensor,)})``.  Falls back to the
+        three separate steps when the layer is not in its fused form."""
+        na = self._norm_args(norm)
+        fused = (na is not None and x.is_cuda and self.forward_mode == "dynk_max"
+                 and isinstance(self.router, MoeficationRouter) and self.router.fusable()
+                 and not self.add_residual_connection
+                 and (x.size(-1) * x.element_size()) % 16 == 0
+                 and x.size(-1) * x.element_size() <= 8192 and x.numel() > 0)
+        if not fused:
+            y, gd = self.forward(norm(x))
+            return x + y, gd
+        self.experts._check_mode()
+        kind, gamma, beta, eps, goff = na
+        orig_size = x.size()
+        E = self.num_experts
+        x2d = x.reshape(-1, x.size(-1)).contiguous()
+        N = x2d.size(0)
+        p = self.experts.kernel_params()
+        xn = torch.empty_like(x2d)
+        out = torch.empty_like(x2d)
+        rt = torch.empty(N, E, dtype=x.dtype, device=x.device)
+        wsp = self._wsp.get(N, E, x.device)
+        ops.prenorm_init(x2d, gamma.detach().to(x.dtype),
+                         None if beta is None else beta.detach().to(x.dtype), eps, kind, xn, out,
+                         last_bias=self.last_bias.view(-1) if self.bias else None,
+                         gamma_offset=goff)
+        ops.moe_forward(xn, self.router.layers[0].weight, self.router.layers[2].weight, self.tau,
+                        p["w1"], p["b1"], p["w2"], p["act"], out, wsp, w_up=p["w_up"],
+                        add_residual=ops.OUT_PREINITIALISED, router_packed=self.router.packed(),
+                        experts_packed=self.experts.packed(), routing_out=rt)
+        return out.view(orig_size), {self.name: (rt.view(*orig_size[:-1], E),)}
+
     @torch.no_grad()
     def forward_host(self, x_host: torch.Tensor, out_host: torch.Tensor | None = None,
                      chunks: int = 4, sync: bool = True) -> torch.Tensor:
@@ -517,6 +577,34 @@ class MoeficationMoE(MoELayer):
         """The cached buffers of the last call with ``n`` tokens: bit mask, token lists,
         offsets and the device status word (for tests and diagnostics)."""
         return self._wsp.get(n, self.num_experts, device)
+
+
+def fused_vit_block_forward(self, input: torch.Tensor):
+    """Replacement for the upstream ``moe_vit_block_forward``
+    (architectures/moe/moe_models.py:56-76; bind with ``functools.partial`` like upstream does,
+    moefication.py:169-176): same computation and return value, with the FFN half run as
+    ``mlp.forward_block(x, ln_2)`` when ``mlp`` is a layer of this package."""
+    gating_data = {}
+    x = self.ln_1(input)
+    res = self.self_attention(query=x, key=x, value=x, need_weights=False)
+    if len(res) == 3:                     # MoE-fied attention returns its gating data as well
+        x, _, attn_gating_data = res
+        gating_data.update(attn_gating_data)
+    else:
+        x, _ = res
+    x = self.dropout(x)
+    x = x + input
+    if isinstance(self.mlp, MoeficationMoE):
+        out, ffn_gating_data = self.mlp.forward_block(x, self.ln_2)
+        gating_data.update(ffn_gating_data)
+        return out, gating_data
+    y = self.ln_2(x)
+    if isinstance(self.mlp, MoELayer):
+        y, ffn_gating_data = self.mlp(y)
+        gating_data.update(ffn_gating_data)
+    else:
+        y = self.mlp(y)
+    return x + y, gating_data
 
 
 def bind_upstream(moe_layers=None) -> bool:

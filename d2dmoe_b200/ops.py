@@ -175,6 +175,23 @@ def init_out(x2d, last_bias, add_residual, out):
                                _dt(out), st), "d2d_init_out")
 
 
+NORM_LAYER, NORM_RMS = 0, 1
+OUT_PREINITIALISED = 2      # add_residual value: ``out`` already holds its initial value
+
+
+def prenorm_init(x2d, gamma, beta, eps: float, kind: int, xn, out_init=None, *, last_bias=None,
+                 gamma_offset: float = 0.0):
+    """One pass over x: ``xn = norm(x)`` (the layer's input) and ``out_init = x + last_bias``
+    (the block's residual as the layer output's initial value).  Raises D2DError UNSUPPORTED for
+    rows longer than 8192 bytes or not a multiple of 16 bytes."""
+    _cu(x2d, gamma, beta, last_bias, xn, out_init)
+    N, d = x2d.shape
+    with _on(x2d) as st:
+        check(lib.d2d_prenorm_init(_ptr(x2d), _ptr(gamma), _ptr(beta), float(eps), int(kind),
+                                   float(gamma_offset), _ptr(last_bias), _ptr(xn), _ptr(out_init),
+                                   N, d, _dt(x2d), st), "d2d_prenorm_init")
+
+
 def compact(wsp: Workspace, N: int, E: int):
     with _on(wsp.mask_bits) as st:
         check(lib.d2d_compact(_ptr(wsp.mask_bits), _ptr(wsp.token_idx), _ptr(wsp.offsets), N, E,

@@ -177,6 +177,31 @@ int d2d_experts_ffn(const void* x, const int32_t* token_idx, const int32_t* offs
                     int64_t N, int d, int E, int H, int act, int dtype,
                     int* dev_status, d2d_stream_t stream);
 
+/* Pre-norm fused with the block's residual: the pass in front of the layer.  An upstream
+ * block runs  y = ln_2(x); y = mlp(y); return x + y  (architectures/moe/moe_models.py:69-76
+ * ViT, :91-100 GPT, :148-156 Gemma).  This call reads x [N, d] once and writes
+ *   xn[t,:]       = T(norm(x[t,:]))              the layer's input
+ *   out_init[t,:] = T(x[t,:] + last_bias_opt)    the layer output's initial value (NULL: skip),
+ * so that d2d_moe_forward(xn, ..., add_residual = D2D_OUT_PREINITIALISED, out = out_init)
+ * leaves x + last_bias + sum of expert outputs in out: neither a separate residual pass nor
+ * the router's initial-value writes remain.
+ *   kind D2D_NORM_LAYER: (x - mean) * rsqrt(var + eps) * gamma + beta_opt (biased variance)
+ *   kind D2D_NORM_RMS:   x * rsqrt(mean(x^2) + eps) * (gamma_offset + gamma); gamma_offset 1
+ *                        is the Gemma form, 0 the plain one.
+ * fp32 statistics, one rounding to T.  d * sizeof(T) must be a multiple of 16 and at most
+ * 8192 bytes (else D2D_ERR_UNSUPPORTED); all pointers 16-byte aligned. */
+#define D2D_NORM_LAYER 0
+#define D2D_NORM_RMS 1
+int d2d_prenorm_init(const void* x, const void* gamma, const void* beta_opt, float eps, int kind,
+                     float gamma_offset, const void* last_bias_opt, void* xn, void* out_init_opt,
+                     int64_t N, int d, int dtype, d2d_stream_t stream);
+
+/* add_residual values of d2d_moe_forward: 0 = out starts as last_bias, 1 = as last_bias + x
+ * (MoeficationMoE.add_residual_connection, architectures/moe/moefication.py:98-99),
+ * D2D_OUT_PREINITIALISED = out already holds its initial value (d2d_prenorm_init wrote it);
+ * last_bias_opt is then ignored. */
+#define D2D_OUT_PREINITIALISED 2
+
 /* The whole layer, MoeficationMoE.forward in 'dynk_max' mode
  * (architectures/moe/moefication.py:90-101): router+mask (or mask from
  * scores_in_opt when wa is NULL) -> compaction -> expert FFN.  mask_bits,

@@ -337,3 +337,26 @@ def cpu_layer_forward_module_glu(x, p: dict, tau: float, act="gelu"):
     rt[s >= thr] = 1.0
     out = experts_glu_module(x2d, rt, p["lin"], act)
     return out.view(x.shape), rt
+
+
+# --------------------------------------------------------------------------
+# pre-norm in front of the layer (block-level callers)
+# --------------------------------------------------------------------------
+def prenorm(x: torch.Tensor, gamma: torch.Tensor, beta, eps: float, kind: str,
+            gamma_offset: float = 0.0) -> torch.Tensor:
+    """The normalisation an upstream block applies before its MoE-FFN layer
+    (architectures/moe/moe_models.py:69 ``self.ln_2(x)`` = nn.LayerNorm; :148-151 Gemma's
+    RMSNorm, transformers GemmaRMSNorm: ``x.float() * rsqrt(mean(x^2) + eps) * (1 + w)``):
+    statistics and affine map in fp32 over the dtype-rounded input, one rounding to the tensor
+    dtype.  kind: "layer" | "rms"."""
+    dt = x.dtype
+    xf = x.float()
+    if kind == "layer":
+        mean = xf.mean(-1, keepdim=True)
+        var = ((xf - mean) ** 2).mean(-1, keepdim=True)
+        y = (xf - mean) * torch.rsqrt(var + eps) * gamma.float()
+        if beta is not None:
+            y = y + beta.float()
+    else:
+        y = xf * torch.rsqrt(xf.pow(2).mean(-1, keepdim=True) + eps) * (gamma_offset + gamma.float())
+    return y.to(dt)
