@@ -41,9 +41,9 @@ sys.path.insert(0, str(ROOT))
 HEADLINE = "vit_b16"
 HEADLINE_TAU = 0.9
 # dram__bytes_read.sum + dram__bytes_write.sum of one expert-kernel launch of the headline
-# workload at tau_cfg 0.9, from an ncu capture of that launch (None = no capture of the
-# current kernel yet)
-NCU_EXPERTS_TRAFFIC_BYTES = None
+# workload at tau_cfg 0.9 (50432 tokens, one layer), from the ncu capture summarised in
+# profiles/layer_kernels_vit_b16_tau0.9.md (177.1 MB read + 31.2 MB written)
+NCU_EXPERTS_TRAFFIC_BYTES = 208.3e6
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
 
 BF16, FP32 = torch.bfloat16, torch.float32
@@ -206,22 +206,34 @@ class Stack:
         for l, m in enumerate(self.mods):
             m(self.x[l % self.nbuf])
 
-    def graphed(self):
+    def block_step(self, norms, fused):
+        """The FFN half of a transformer block per layer: x + layer(norm(x)), either through
+        the module's fused ``forward_block`` or as the three separate steps."""
+        for l, m in enumerate(self.mods):
+            x = self.x[l % self.nbuf]
+            if fused:
+                m.forward_block(x, norms[l])
+            else:
+                y, _ = m(norms[l](x))
+                x + y
+
+    def graphed(self, fn=None):
         """The step captured once in a CUDA graph (the module forwards issue no host
         synchronisation and take their temporaries from the graph's pool); returns the
         replay callable, or None when capture is not possible."""
+        fn = fn or self.step
         try:
             side = torch.cuda.Stream(self.x[0].device)
             side.wait_stream(torch.cuda.current_stream())
             with torch.cuda.stream(side):
-                self.step()
+                fn()
                 side.synchronize()
                 g = torch.cuda.CUDAGraph()
                 with torch.cuda.graph(g, stream=side):
-                    self.step()
+                    fn()
             torch.cuda.current_stream().wait_stream(side)
             torch.cuda.synchronize()
-            self._graph = g
+            self._graphs = getattr(self, "_graphs", []) + [g]
             return g.replay
         except Exception as exc:      # noqa: BLE001
             print(f"# CUDA graph capture failed, timing eager launches: {exc}", file=sys.stderr)
@@ -236,7 +248,7 @@ class Stack:
 
     def launches_per_layer(self):
         from d2dmoe_b200 import _capi
-        return int(_capi.lib.d2d_last_forward_launches()) + 1     # + the routing-tensor expand
+        return int(_capi.lib.d2d_last_forward_launches())
 
     def staged(self, l, ev):
         """Layer l through the per-stage entry points with CUDA events between the stages
@@ -608,7 +620,7 @@ def run_ours(args):
                 "unit": "GB/s"}
     roof["frac"] = roof["achieved"] / roof["peak"]
     roof.update({"kernel": "experts_ffn (expert FFN tile kernel)",
-                 "traffic": NCU_EXPERTS_TRAFFIC_BYTES if (world == 1 and stack.layers == 12) else None,
+                 "traffic": NCU_EXPERTS_TRAFFIC_BYTES if (world == 1 and not args.batch) else None,
                  "peak_source": pk["source"], "avg_launch_us": ffn_s * 1e6,
                  "launches_timed": launches, "tokens_per_launch": n_local,
                  "algorithmic_bytes_per_launch": ffn_bytes, "algorithmic_flops_per_launch": fl,
@@ -647,6 +659,26 @@ def run_ours(args):
     e2e_ceiling = tokens_step_global / ceil_s
 
     check = sample_check(stack, HEADLINE_TAU) if rank == 0 else None
+
+    # ---- block level: pre-norm + layer + residual, fused against three separate steps ----
+    block = None
+    if world == 1 and not args.eager:
+        norms = [torch.nn.LayerNorm(c["d"], eps=1e-6).to(c["dtype"]).to(dev)
+                 for _ in range(stack.layers)]
+        bs = max(2, min(steps, 10))
+        block = {}
+        for key, fused in (("separate_ms_per_step", False), ("fused_ms_per_step", True)):
+            fn = stack.graphed(lambda f=fused: stack.block_step(norms, f))
+            if fn is None:
+                block = None
+                break
+            block[key] = timed(fn, bs, 3, dist) / bs
+        if block:
+            block["what"] = ("x + layer(LayerNorm(x)) per layer, CUDA-graph replay; separate = "
+                             "torch LayerNorm, module forward, torch add; fused = forward_block")
+            block["tokens_per_s_fused"] = tokens_step_global / (block["fused_ms_per_step"] * 1e-3)
+        stack._graphs = stack._graphs[:1]
+        stack.step()
 
     # ---- all five configurations with their CPU baselines (1 GPU) -------------------
     configs = None
@@ -709,13 +741,14 @@ def run_ours(args):
                 "api": "MoeficationMoE.forward_host (pinned host x -> pinned host out, 2 slices "
                        "per layer, layers pipelined); bytes are per rank"},
         # kernels per layer call: what the library counted for the last d2d_moe_forward
-        # (router+rule, compaction scan, compaction scatter, expert FFN) + the routing-tensor
-        # expansion the module returns as gating data
+        # (router + rule + routing tensor, compaction scatter, expert FFN)
         "gpu_launches": steps * stack.layers * launches_per_layer,
         "clocks": clocks, "check": check,
     }
     if replica is not None:
         line["replicas_weak_tokens_per_s"] = replica
+    if block is not None:
+        line["block_prenorm_residual"] = block
     if configs is not None:
         line["configs"] = configs
     if cpu_head is not None:

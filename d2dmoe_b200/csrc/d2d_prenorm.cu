@@ -24,7 +24,9 @@ namespace {
 constexpr int NT = 256;
 constexpr int MAXV = 16;      // 16-byte vectors per lane: d <= 32 * 16 * (16 / sizeof(T))
 
-template <typename T>
+// MAXV_ = vectors a lane holds (the register footprint, hence the number of resident warps and
+// the bytes in flight per SM, follows the row length instead of the longest row supported).
+template <typename T, int MAXV_>
 __global__ void __launch_bounds__(NT)
 prenorm_init_kernel(const T* __restrict__ x, const T* __restrict__ gamma,
                     const T* __restrict__ beta, float eps, int kind, float gamma_offset,
@@ -35,15 +37,42 @@ prenorm_init_kernel(const T* __restrict__ x, const T* __restrict__ gamma,
   const int dv = d / V;                       // vectors per row
   const int nv = (dv + 31) / 32;              // vectors per lane (<= MAXV)
   const int64_t warps = (int64_t)gridDim.x * (NT / 32);
-  for (int64_t row = (int64_t)blockIdx.x * (NT / 32) + (threadIdx.x >> 5); row < N; row += warps) {
+  // Short rows (<= 4 vectors per lane) keep the NEXT row's loads in flight while the current
+  // row is reduced and written: one row per warp at a time leaves too few bytes in flight.
+  constexpr bool PREFETCH = MAXV_ <= 4;
+  uint4 raw[MAXV_], nxt[PREFETCH ? MAXV_ : 1];
+  int64_t row = (int64_t)blockIdx.x * (NT / 32) + (threadIdx.x >> 5);
+  if (PREFETCH && row < N) {
     const uint4* xr = reinterpret_cast<const uint4*>(x + row * d);
-    uint4 raw[MAXV];
+#pragma unroll
+    for (int i = 0; i < MAXV_; ++i) {
+      const int c = lane + 32 * i;
+      if (i < nv && c < dv) raw[i] = __ldg(xr + c);
+    }
+  }
+  for (; row < N; row += warps) {
+    if (PREFETCH) {
+      if (row + warps < N) {
+        const uint4* xr = reinterpret_cast<const uint4*>(x + (row + warps) * d);
+#pragma unroll
+        for (int i = 0; i < MAXV_; ++i) {
+          const int c = lane + 32 * i;
+          if (i < nv && c < dv) nxt[i] = __ldg(xr + c);
+        }
+      }
+    } else {
+      const uint4* xr = reinterpret_cast<const uint4*>(x + row * d);
+#pragma unroll
+      for (int i = 0; i < MAXV_; ++i) {
+        const int c = lane + 32 * i;
+        if (i < nv && c < dv) raw[i] = __ldg(xr + c);
+      }
+    }
     float sum = 0.f, sq = 0.f;
 #pragma unroll
-    for (int i = 0; i < MAXV; ++i) {
+    for (int i = 0; i < MAXV_; ++i) {
       const int c = lane + 32 * i;
       if (i < nv && c < dv) {
-        raw[i] = __ldg(xr + c);
         const T* e = reinterpret_cast<const T*>(&raw[i]);
 #pragma unroll
         for (int q = 0; q < V; ++q) {
@@ -63,7 +92,7 @@ prenorm_init_kernel(const T* __restrict__ x, const T* __restrict__ gamma,
       mean = sum / (float)d;
       float var = 0.f;                        // second pass over the registers: sum (x - mean)^2
 #pragma unroll
-      for (int i = 0; i < MAXV; ++i) {
+      for (int i = 0; i < MAXV_; ++i) {
         const int c = lane + 32 * i;
         if (i < nv && c < dv) {
           const T* e = reinterpret_cast<const T*>(&raw[i]);
@@ -81,7 +110,7 @@ prenorm_init_kernel(const T* __restrict__ x, const T* __restrict__ gamma,
       rstd = rsqrtf(sq / (float)d + eps);
     }
 #pragma unroll
-    for (int i = 0; i < MAXV; ++i) {
+    for (int i = 0; i < MAXV_; ++i) {
       const int c = lane + 32 * i;
       if (i < nv && c < dv) {
         const uint4 gv = __ldg(reinterpret_cast<const uint4*>(gamma) + c);
@@ -105,6 +134,10 @@ prenorm_init_kernel(const T* __restrict__ x, const T* __restrict__ gamma,
         if (out) *(reinterpret_cast<uint4*>(out + row * d) + c) = *reinterpret_cast<const uint4*>(yo);
       }
     }
+    if (PREFETCH) {
+#pragma unroll
+      for (int i = 0; i < MAXV_; ++i) raw[i] = nxt[i];
+    }
   }
 }
 
@@ -121,14 +154,24 @@ int launch_prenorm_init(const void* x, const void* gamma, const void* beta, floa
   int64_t grid = ceil_div64(N, NT / 32);
   if (grid > 148 * 16) grid = 148 * 16;
   if (grid < 1) grid = 1;
-  if (dtype == D2D_F32)
-    prenorm_init_kernel<float><<<(unsigned)grid, NT, 0, s>>>(
-        (const float*)x, (const float*)gamma, (const float*)beta, eps, kind, gamma_offset,
-        (const float*)last_bias, (float*)xn, (float*)out, N, d);
-  else
-    prenorm_init_kernel<bf16><<<(unsigned)grid, NT, 0, s>>>(
-        (const bf16*)x, (const bf16*)gamma, (const bf16*)beta, eps, kind, gamma_offset,
-        (const bf16*)last_bias, (bf16*)xn, (bf16*)out, N, d);
+  const int nv = (d / V + 31) / 32;
+#define D2D_PRENORM_CASE(T_, NV_)                                                              \
+  prenorm_init_kernel<T_, NV_><<<(unsigned)grid, NT, 0, s>>>(                                   \
+      (const T_*)x, (const T_*)gamma, (const T_*)beta, eps, kind, gamma_offset,                 \
+      (const T_*)last_bias, (T_*)xn, (T_*)out, N, d)
+#define D2D_PRENORM_BY_NV(T_)                                                                  \
+  do {                                                                                         \
+    if (nv <= 1) D2D_PRENORM_CASE(T_, 1);                                                      \
+    else if (nv <= 2) D2D_PRENORM_CASE(T_, 2);                                                 \
+    else if (nv <= 3) D2D_PRENORM_CASE(T_, 3);                                                 \
+    else if (nv <= 4) D2D_PRENORM_CASE(T_, 4);                                                 \
+    else if (nv <= 8) D2D_PRENORM_CASE(T_, 8);                                                 \
+    else D2D_PRENORM_CASE(T_, MAXV);                                                           \
+  } while (0)
+  if (dtype == D2D_F32) D2D_PRENORM_BY_NV(float);
+  else D2D_PRENORM_BY_NV(bf16);
+#undef D2D_PRENORM_BY_NV
+#undef D2D_PRENORM_CASE
   return cudaGetLastError() == cudaSuccess ? D2D_OK : D2D_ERR_LAUNCH;
 }
 

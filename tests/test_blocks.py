@@ -169,12 +169,13 @@ def test_forward_block_falls_back_when_not_fusable():
     ident = torch.nn.Identity()                    # not a norm the fused pass knows
     out, _ = moe.forward_block(x, ident)
     y, _ = moe(x)
-    assert torch.equal(out, x + y)
+    # (the scatter-add's order differs from call to call: equal up to fp32 rounding)
+    assert O.rel_err(out.cpu(), (x + y).cpu()) <= 1e-6
     moe.forward_mode, moe.k = "topk", 2            # another gate: three separate steps
     out, _ = moe.forward_block(x, norm)
     y, _ = moe(norm(x))
-    assert torch.equal(out, x + y)
-    assert not torch.equal(out, fused)
+    assert O.rel_err(out.cpu(), (x + y).cpu()) <= 1e-6
+    assert O.rel_err(out.cpu(), fused.cpu()) > 1e-4
 
 
 @pytest.mark.gpu
