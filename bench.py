@@ -440,6 +440,65 @@ def cpu_baseline(name, tau_cfg, budget_s=6.0, reps=5, warmup=1):
                       f"{'module (GLUExpert)' if c['glu'] else 'naive'} order"}
 
 
+def router_labels_leg(stack, pk, cpu=True):
+    """Router-training label capture on one layer of the headline shape: forward mode 'all'
+    (every expert on every token) with the per-pair output norms written by the expert
+    kernel, against the upstream recipe (dense per-expert products + vector_norm) on the
+    host cores over a bounded token sample."""
+    c = stack.c
+    m = stack.mods[0]
+    x = stack.x[0]
+    n = stack.n
+    mode, m.forward_mode = m.forward_mode, "all"
+    m.experts.capture_norms("output", 2)
+    try:
+        run = lambda: m(x)      # noqa: E731
+        for _ in range(2):
+            run()
+        torch.cuda.synchronize()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        reps = 5
+        a.record()
+        for _ in range(reps):
+            run()
+        b.record()
+        torch.cuda.synchronize()
+        ms = a.elapsed_time(b) / reps
+        nz = int((m.experts.captured_norms > 0).sum().item())
+    finally:
+        m.experts.capture_norms(None)
+        m.forward_mode = mode
+    flops = float(n) * c["E"] * 4.0 * c["d"] * c["H"]
+    t_roof = flops / (pk["bf16_tflops_sustained"] * 1e12)
+    out = {"what": "MoeficationMoE.forward, mode 'all' + experts.capture_norms('output', 2): "
+                   "layer output and the [E, N] labels from one pass of the expert kernel",
+           "tokens": n, "pairs": n * c["E"], "nonzero_labels": nz, "ms_per_layer": ms,
+           "tokens_per_s": n / (ms * 1e-3),
+           "roofline": {"bound": "tensor", "achieved": flops / (ms * 1e-3) / 1e12,
+                        "peak": pk["bf16_tflops_sustained"], "unit": "TFLOP/s",
+                        "frac": t_roof / (ms * 1e-3)}}
+    if cpu:
+        from oracle import d2d_oracle as O
+        torch.set_num_threads(os.cpu_count() or 1)
+        ns = 2048
+        xc, p, _ = _cpu_tensors(c, ns)
+        xc = xc.reshape(ns, c["d"]).float()
+        pp = {k: v.float() for k, v in p.items()}
+        f = lambda: O.expert_activation_norms(xc, pp["w1"], pp["b1"], pp["w2"], c["act"],  # noqa: E731
+                                              layer="output", ord=2)
+        f()
+        ts = []
+        for _ in range(3):
+            t0 = time.perf_counter()
+            f()
+            ts.append(time.perf_counter() - t0)
+        out["cpu_baseline"] = {"value": ns / statistics.median(ts), "unit": "tokens/s",
+                               "cores": torch.get_num_threads(), "kind": "port",
+                               "sample": f"{ns} tokens of one layer, fp32, upstream recipe: dense "
+                                         "einsum per expert + torch.linalg.vector_norm, median of 3"}
+    return out
+
+
 def run_reference(args):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
@@ -660,6 +719,11 @@ def run_ours(args):
 
     check = sample_check(stack, HEADLINE_TAU) if rank == 0 else None
 
+    # ---- router-training labels as a by-product of the expert kernel (1 GPU) ---------------
+    labels = None
+    if world == 1 and rank == 0 and not args.batch:
+        labels = router_labels_leg(stack, pk, cpu=not args.no_cpu)
+
     # ---- block level: pre-norm + layer + residual, fused against three separate steps ----
     block = None
     if world == 1 and not args.eager:
@@ -749,6 +813,8 @@ def run_ours(args):
         line["replicas_weak_tokens_per_s"] = replica
     if block is not None:
         line["block_prenorm_residual"] = block
+    if labels is not None:
+        line["router_labels"] = labels
     if configs is not None:
         line["configs"] = configs
     if cpu_head is not None:

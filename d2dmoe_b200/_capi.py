@@ -38,6 +38,8 @@ SIGNATURES = {
     "d2d_compact_noalloc": (_i, [_p, _p, _p, _i64, _i, _p, _p]),
     "d2d_experts_ffn": (_i, [_p, _p, _p, _p, _p, _p, _p, _p, _p, _i, _i, _p,
                              _i64, _i, _i, _i, _i, _i, _p, _p]),
+    "d2d_experts_ffn_norms": (_i, [_p, _p, _p, _p, _p, _p, _p, _p, _p, _i, _i, _p, _p, _i, _i,
+                                   _i64, _i, _i, _i, _i, _i, _p, _p]),
     "d2d_moe_forward": (_i, [_p, _p, _p, _p, _p, _f, _p, _p, _p, _p, _p, _p, _i, _p,
                              _p, _p, _p, _i64, _i, _i, _i, _i, _i, _i, _p, _sz, _p, _p, _p]),
     "d2d_prepack_experts_bytes": (_i, [_i, _i, _i, _i, _i, C.POINTER(_sz)]),

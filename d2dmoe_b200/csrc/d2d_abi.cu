@@ -131,17 +131,25 @@ int d2d_compact(const uint32_t* mask_bits, int32_t* token_idx, int32_t* offsets,
                         (cudaStream_t)stream, false);
 }
 
-int d2d_experts_ffn(const void* x, const int32_t* token_idx, const int32_t* offsets,
-                    const void* w1, const void* b1_opt, const void* w_up_opt, const void* w2,
-                    const void* experts_packed_opt, const void* last_bias_opt, int add_residual,
-                    int accumulate, void* out, int64_t N, int d, int E, int H, int act, int dtype,
-                    int* dev_status, d2d_stream_t stream) {
+static int experts_ffn_impl(const void* x, const int32_t* token_idx, const int32_t* offsets,
+                            const void* w1, const void* b1_opt, const void* w_up_opt,
+                            const void* w2, const void* experts_packed_opt,
+                            const void* last_bias_opt, int add_residual, int accumulate,
+                            void* out, NormCapture nc, int64_t N, int d, int E, int H, int act,
+                            int dtype, int* dev_status, d2d_stream_t stream) {
   if (!x || !token_idx || !offsets || !w1 || !w2 || !out || N < 0 || d < 1 || E < 1 || H < 1)
     return D2D_ERR_BAD_ARG;
   if (!dtype_ok(dtype) || act < D2D_RELU || act > D2D_GELU_TANH) return D2D_ERR_UNSUPPORTED;
   if (!aligned(out, 16) || !aligned(x, 16)) return D2D_ERR_BAD_ARG;
+  if (nc.layer != 0 &&
+      (!nc.norms || !aligned(nc.norms, 4) || (nc.ord != 1 && nc.ord != 2) ||
+       (nc.layer != D2D_NORM_OF_INTERMEDIATE && nc.layer != D2D_NORM_OF_OUTPUT)))
+    return D2D_ERR_BAD_ARG;
   if (N == 0) return D2D_OK;
   cudaStream_t s = (cudaStream_t)stream;
+  if (nc.layer != 0 &&
+      cudaMemsetAsync(nc.norms, 0, (size_t)N * E * (dtype == D2D_F32 ? 4 : 2), s) != cudaSuccess)
+    return D2D_ERR_LAUNCH;
   if (!accumulate) {
     int rc = launch_init_out(x, last_bias_opt, add_residual, out, N, d, dtype, s);
     if (rc != D2D_OK) return rc;
@@ -149,9 +157,35 @@ int d2d_experts_ffn(const void* x, const int32_t* token_idx, const int32_t* offs
   if (experts_packed_opt && umma_experts_supported(d, E, H, w_up_opt != nullptr, dtype) &&
       aligned(experts_packed_opt, 1024))
     return launch_experts_umma(x, token_idx, offsets, experts_packed_opt, out, N, d, E, H,
-                               w_up_opt != nullptr, act, dev_status, s);
+                               w_up_opt != nullptr, act, dev_status, s, nc);
   return launch_experts_simt(x, token_idx, offsets, w1, b1_opt, w_up_opt, w2, out, N, d, E, H, act,
-                             dtype, dev_status, s);
+                             dtype, dev_status, s, nc);
+}
+
+int d2d_experts_ffn(const void* x, const int32_t* token_idx, const int32_t* offsets,
+                    const void* w1, const void* b1_opt, const void* w_up_opt, const void* w2,
+                    const void* experts_packed_opt, const void* last_bias_opt, int add_residual,
+                    int accumulate, void* out, int64_t N, int d, int E, int H, int act, int dtype,
+                    int* dev_status, d2d_stream_t stream) {
+  return experts_ffn_impl(x, token_idx, offsets, w1, b1_opt, w_up_opt, w2, experts_packed_opt,
+                          last_bias_opt, add_residual, accumulate, out, NormCapture(), N, d, E, H,
+                          act, dtype, dev_status, stream);
+}
+
+int d2d_experts_ffn_norms(const void* x, const int32_t* token_idx, const int32_t* offsets,
+                          const void* w1, const void* b1_opt, const void* w_up_opt,
+                          const void* w2, const void* experts_packed_opt,
+                          const void* last_bias_opt, int add_residual, int accumulate, void* out,
+                          void* norms, int norm_layer, int norm_ord, int64_t N, int d, int E,
+                          int H, int act, int dtype, int* dev_status, d2d_stream_t stream) {
+  NormCapture nc;
+  nc.norms = norms;
+  nc.layer = norm_layer;
+  nc.ord = norm_ord;
+  if (norm_layer == 0) return D2D_ERR_BAD_ARG;
+  return experts_ffn_impl(x, token_idx, offsets, w1, b1_opt, w_up_opt, w2, experts_packed_opt,
+                          last_bias_opt, add_residual, accumulate, out, nc, N, d, E, H, act, dtype,
+                          dev_status, stream);
 }
 
 int d2d_moe_forward(const void* x, const void* wa, const void* wb, const void* router_packed_opt,

@@ -122,6 +122,15 @@ __host__ __device__ __forceinline__ int64_t ceil_div64(int64_t a, int64_t b) { r
 // ---- internal launch interface (host side, used by d2d_abi.cu) -------------
 namespace d2d {
 
+// Optional by-product of the expert kernels: per (expert, token) vector norms over the last
+// dimension of what the expert computes for that token, norms[e * N + token] in the tensor
+// dtype (the labels router training captures with forward hooks upstream, utils.py:353-369).
+struct NormCapture {
+  void* norms = nullptr;   // [E, N]; entries of pairs outside the token lists are left alone
+  int layer = 0;           // 0 none, D2D_NORM_OF_INTERMEDIATE, D2D_NORM_OF_OUTPUT
+  int ord = 2;             // 1 (sum of magnitudes) or 2 (Euclidean)
+};
+
 int launch_router_mask_simt(const void* x, const void* wa, const void* wb, float mult,
                             uint32_t* mask_bits, void* scores, const void* last_bias,
                             int add_residual, void* out_init, int64_t N, int d, int R, int E,
@@ -153,6 +162,6 @@ int launch_compact(const uint32_t* mask_bits, int32_t* token_idx, int32_t* offse
 int launch_experts_simt(const void* x, const int32_t* token_idx, const int32_t* offsets,
                         const void* w1, const void* b1, const void* w_up, const void* w2,
                         void* out, int64_t N, int d, int E, int H, int act, int dtype,
-                        int* dev_status, cudaStream_t s);
+                        int* dev_status, cudaStream_t s, NormCapture nc = NormCapture());
 
 }  // namespace d2d

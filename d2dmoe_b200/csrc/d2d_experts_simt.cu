@@ -21,13 +21,32 @@ constexpr int CB = 128;       // output columns per pass (4 per lane)
 constexpr int WP = CB + 4;    // padded weight row
 constexpr int MAX_E = 256;
 
+// one element's share of a row's norm (ord 1: magnitude, ord 2: square)
+__device__ __forceinline__ float norm_term(float v, int ord) { return ord == 1 ? fabsf(v) : v * v; }
+
+// Row sums held as per-lane partials (lane = 4 columns): reduce over the warp and let lane 0
+// write norms[e, token] for the warp's four rows.
+template <typename T>
+__device__ __forceinline__ void write_row_norms(float* part, int ord, T* norms, int e, int64_t N,
+                                                const int* rows, int ty, int lane) {
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    float v = part[i];
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    const int t = rows[4 * ty + i];
+    if (lane == 0 && t >= 0) norms[(int64_t)e * N + t] = DT<T>::from_f(ord == 1 ? v : sqrtf(v));
+  }
+}
+
 template <typename T, bool GLU>
 __global__ void __launch_bounds__(NT)
 experts_simt_kernel(const T* __restrict__ x, const int32_t* __restrict__ token_idx,
                     const int32_t* __restrict__ offsets, const T* __restrict__ w1,
                     const T* __restrict__ b1, const T* __restrict__ w_up,
                     const T* __restrict__ w2, T* __restrict__ out, int64_t N, int d, int E, int H,
-                    int act, int* dev_status) {
+                    int act, int* dev_status, T* __restrict__ norms, int norm_layer,
+                    int norm_ord) {
   extern __shared__ float sm[];
   float* xs = sm;                              // [TM][XP]
   float* ws = xs + TM * XP;                    // [KC][WP]
@@ -78,6 +97,7 @@ experts_simt_kernel(const T* __restrict__ x, const int32_t* __restrict__ token_i
     const T* w2e = w2 + (int64_t)e * H * d;
 
     // ---- first layer: hs = act(x W1 + b1) (* x W_up) ------------------------
+    float npart[4] = {0.f, 0.f, 0.f, 0.f};      // this lane's share of its rows' norms
     for (int hc = 0; hc < H; hc += CB) {
       float acc[4][4], accu[4][4];
 #pragma unroll
@@ -163,6 +183,7 @@ experts_simt_kernel(const T* __restrict__ x, const int32_t* __restrict__ token_i
             float h = DT<T>::round(acc[i][j]);
             if (b1) h = DT<T>::round(h + DT<T>::to_f(b1[(int64_t)e * H + c]));
             h = DT<T>::round(activate(h, act));
+            if (norm_layer == D2D_NORM_OF_INTERMEDIATE) npart[i] += norm_term(h, norm_ord);
             if (GLU) h = DT<T>::round(h * DT<T>::round(accu[i][j]));
             hs[(4 * ty + i) * HP + c] = h;
           }
@@ -216,6 +237,13 @@ experts_simt_kernel(const T* __restrict__ x, const int32_t* __restrict__ token_i
         }
       }
       const int c0 = dc + 4 * lane;
+      if (norm_layer == D2D_NORM_OF_OUTPUT) {
+#pragma unroll
+        for (int i = 0; i < 4; ++i)
+#pragma unroll
+          for (int j = 0; j < 4; ++j)
+            if (c0 + j < d) npart[i] += norm_term(DT<T>::round(acc[i][j]), norm_ord);
+      }
 #pragma unroll
       for (int i = 0; i < 4; ++i) {
         const int t = rows[4 * ty + i];
@@ -231,13 +259,14 @@ experts_simt_kernel(const T* __restrict__ x, const int32_t* __restrict__ token_i
         }
       }
     }
+    if (norm_layer != 0) write_row_norms<T>(npart, norm_ord, norms, e, N, rows, ty, lane);
   }
 }
 
 template <typename T, bool GLU>
 int launch_t(const void* x, const int32_t* token_idx, const int32_t* offsets, const void* w1,
              const void* b1, const void* w_up, const void* w2, void* out, int64_t N, int d, int E,
-             int H, int act, int* dev_status, cudaStream_t s) {
+             int H, int act, int* dev_status, cudaStream_t s, NormCapture nc) {
   const int HP = ((H + 3) & ~3) + 4;
   const size_t smem =
       sizeof(float) * ((size_t)TM * XP + (size_t)KC * WP * (GLU ? 2 : 1) + (size_t)TM * HP);
@@ -249,7 +278,8 @@ int launch_t(const void* x, const int32_t* token_idx, const int32_t* offsets, co
   const int64_t max_tiles = ceil_div64(N * (int64_t)E, TM) + E;
   const int grid = (int)(max_tiles < 148 * 4 ? (max_tiles > 0 ? max_tiles : 1) : 148 * 4);
   k<<<grid, NT, smem, s>>>((const T*)x, token_idx, offsets, (const T*)w1, (const T*)b1,
-                           (const T*)w_up, (const T*)w2, (T*)out, N, d, E, H, act, dev_status);
+                           (const T*)w_up, (const T*)w2, (T*)out, N, d, E, H, act, dev_status,
+                           (T*)nc.norms, nc.norms ? nc.layer : 0, nc.ord);
   return cudaGetLastError() == cudaSuccess ? D2D_OK : D2D_ERR_LAUNCH;
 }
 
@@ -258,18 +288,18 @@ int launch_t(const void* x, const int32_t* token_idx, const int32_t* offsets, co
 int launch_experts_simt(const void* x, const int32_t* token_idx, const int32_t* offsets,
                         const void* w1, const void* b1, const void* w_up, const void* w2,
                         void* out, int64_t N, int d, int E, int H, int act, int dtype,
-                        int* dev_status, cudaStream_t s) {
+                        int* dev_status, cudaStream_t s, NormCapture nc) {
   if (E > MAX_E) return D2D_ERR_UNSUPPORTED;
   if (dtype == D2D_F32) {
     return w_up ? launch_t<float, true>(x, token_idx, offsets, w1, b1, w_up, w2, out, N, d, E, H,
-                                        act, dev_status, s)
+                                        act, dev_status, s, nc)
                 : launch_t<float, false>(x, token_idx, offsets, w1, b1, w_up, w2, out, N, d, E, H,
-                                         act, dev_status, s);
+                                         act, dev_status, s, nc);
   }
   return w_up ? launch_t<bf16, true>(x, token_idx, offsets, w1, b1, w_up, w2, out, N, d, E, H, act,
-                                     dev_status, s)
+                                     dev_status, s, nc)
               : launch_t<bf16, false>(x, token_idx, offsets, w1, b1, w_up, w2, out, N, d, E, H,
-                                      act, dev_status, s);
+                                      act, dev_status, s, nc);
 }
 
 }  // namespace d2d

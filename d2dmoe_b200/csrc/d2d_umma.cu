@@ -104,6 +104,8 @@ struct Params {
   uint32_t wait_limit;      // polls per bounded wait
   int withhold;             // test hook: CTA 0 never loads its first weight tile
   int tma_gather;           // experts: rows by TMA tile::gather4 instead of cp.async
+  bf16* norms;              // experts, optional: [E, N] norms of each computed pair's activations
+  int norm_layer, norm_ord; // D2D_NORM_OF_INTERMEDIATE / D2D_NORM_OF_OUTPUT (0: none); 1 or 2
 };
 
 Geo experts_geo(int d, int H, bool glu) {
@@ -658,9 +660,11 @@ __device__ void role_epilogue_router(const Params& p, Ctl* c, uint32_t hs, uint3
 // 16 hidden columns as 8 packed bf16 pairs, with the upstream rounding points
 // (T(x W1), + b1, activation, x T(x W_up)) done in packed bf16 arithmetic: one
 // float->bf16x2 conversion per pair instead of one conversion per rounding point.
+// nord != 0: nacc also collects the row's norm terms of the activation (before the gating
+// product), 1 = magnitudes, 2 = squares.
 template <int ACT>
 __device__ __forceinline__ void ep1_pairs(const uint32_t* v, const uint32_t* u, const uint32_t* bp,
-                                          bool glu, uint32_t* w) {
+                                          bool glu, uint32_t* w, float& nacc, int nord) {
 #pragma unroll
   for (int q = 0; q < 8; ++q) {
     __nv_bfloat162 h =
@@ -671,6 +675,10 @@ __device__ __forceinline__ void ep1_pairs(const uint32_t* v, const uint32_t* u, 
     } else {
       const float2 f = __bfloat1622float2(h);
       h = __floats2bfloat162_rn(activate(f.x, ACT), activate(f.y, ACT));
+    }
+    if (nord != 0) {
+      const float2 f = __bfloat1622float2(h);
+      nacc += nord == 1 ? fabsf(f.x) + fabsf(f.y) : fmaf(f.x, f.x, f.y * f.y);
     }
     if (glu) {
       const __nv_bfloat162 uu =
@@ -704,6 +712,11 @@ __device__ void role_ep1_experts(const Params& p, Ctl* c, uint32_t hs, uint32_t 
       bp[et] = pack_bf16x2(b.x, b.y);
     }
     asm volatile("bar.sync 2, 128;" ::: "memory");
+    // labels by-product (intermediate layer): this thread's row, its token loaded up front
+    const int nord = p.norm_layer == D2D_NORM_OF_INTERMEDIATE ? p.norm_ord : 0;
+    float nacc = 0.f;
+    int ntok = -1;
+    if (nord != 0 && r < t.nrows) ntok = p.token_idx[t.r0 + r];
     const uint32_t b1 = la ? (i & 1) : 0;
     const uint32_t acc1 = tmem + lane_base + (la ? b1 * 128 : 0);
     if (!mbar_wait_fast(smem_u32(&c->acc1_full[b1]), la ? ((i >> 1) & 1) : (i & 1), af,
@@ -721,11 +734,11 @@ __device__ void role_ep1_experts(const Params& p, Ctl* c, uint32_t hs, uint32_t 
       bb[4] = q1.x; bb[5] = q1.y; bb[6] = q1.z; bb[7] = q1.w;
       tmem_wait_ld();
       switch (p.act) {      // uniform branch around the element loop
-        case D2D_RELU: ep1_pairs<D2D_RELU>(v, u, bb, p.glu != 0, w); break;
-        case D2D_GELU: ep1_pairs<D2D_GELU>(v, u, bb, p.glu != 0, w); break;
-        case D2D_TANH: ep1_pairs<D2D_TANH>(v, u, bb, p.glu != 0, w); break;
-        case D2D_LEAKY_RELU: ep1_pairs<D2D_LEAKY_RELU>(v, u, bb, p.glu != 0, w); break;
-        default: ep1_pairs<D2D_GELU_TANH>(v, u, bb, p.glu != 0, w); break;
+        case D2D_RELU: ep1_pairs<D2D_RELU>(v, u, bb, p.glu != 0, w, nacc, nord); break;
+        case D2D_GELU: ep1_pairs<D2D_GELU>(v, u, bb, p.glu != 0, w, nacc, nord); break;
+        case D2D_TANH: ep1_pairs<D2D_TANH>(v, u, bb, p.glu != 0, w, nacc, nord); break;
+        case D2D_LEAKY_RELU: ep1_pairs<D2D_LEAKY_RELU>(v, u, bb, p.glu != 0, w, nacc, nord); break;
+        default: ep1_pairs<D2D_GELU_TANH>(v, u, bb, p.glu != 0, w, nacc, nord); break;
       }
       const uint32_t base = hs_row + (c0 >> 6) * SLOT;
       const int j0 = (c0 & 63) >> 3;
@@ -736,6 +749,8 @@ __device__ void role_ep1_experts(const Params& p, Ctl* c, uint32_t hs, uint32_t 
     mbar_arrive(smem_u32(&c->acc1_empty[b1]));     // acc1 buffer read completely
     fence_proxy_async();     // ordinary shared stores -> visible to the MMA's async reads
     mbar_arrive(smem_u32(&c->hs_full));
+    if (ntok >= 0 && ntok < p.N)
+      p.norms[(long long)t.e * p.N + ntok] = __float2bfloat16_rn(nord == 1 ? nacc : sqrtf(nacc));
   }
 }
 
@@ -750,7 +765,16 @@ __device__ void role_ep2_experts(const Params& p, Ctl* c, uint32_t stg, uint32_t
   const uint32_t lane_base = (uint32_t)(et & ~31) << 16;
   const int halves = g.nd >> 6;
   uint32_t phbits = 0, n = 0;
+  const int nord = p.norm_layer == D2D_NORM_OF_OUTPUT ? p.norm_ord : 0;
   for (int tile = blockIdx.x; tile < c->total_tiles; tile += gridDim.x) {
+    // labels by-product (output layer): thread = tile row; norm terms of the bf16 outputs
+    float nacc = 0.f;
+    int ntok = -1, ne = 0;
+    if (nord != 0) {
+      const Tile t = tile_info<MODE_EXPERTS>(p, c, tile);
+      ne = t.e;
+      if (et < t.nrows) ntok = p.token_idx[t.r0 + et];
+    }
     for (int nci = 0; nci < g.nc; ++nci) {
       const uint32_t buf = nci & 1;
       if (!mbar_wait_fast(smem_u32(&c->acc2_full[buf]), (phbits >> buf) & 1, af, p.dev_status))
@@ -779,10 +803,19 @@ __device__ void role_ep2_experts(const Params& p, Ctl* c, uint32_t stg, uint32_t
             ww[k] = pack_bf16x2(__uint_as_float(v[8 * pc + 2 * k]),
                                 __uint_as_float(v[8 * pc + 2 * k + 1]));
           st_shared_v4(dst + ((pc ^ (lane & 7)) << 4), ww[0], ww[1], ww[2], ww[3]);
+          if (nord != 0) {
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+              const float lo = __uint_as_float(ww[k] << 16), hi = __uint_as_float(ww[k] & 0xffff0000u);
+              nacc += nord == 1 ? fabsf(lo) + fabsf(hi) : fmaf(lo, lo, hi * hi);
+            }
+          }
         }
         mbar_arrive(smem_u32(&c->sfull[blk][q]));
       }
     }
+    if (ntok >= 0 && ntok < p.N)
+      p.norms[(long long)ne * p.N + ntok] = __float2bfloat16_rn(nord == 1 ? nacc : sqrtf(nacc));
   }
 }
 
@@ -1150,7 +1183,7 @@ int launch_prepack_experts(const void* w1, const void* b1, const void* w_up, con
 
 int launch_experts_umma(const void* x, const int32_t* token_idx, const int32_t* offsets,
                         const void* packed, void* out, int64_t N, int d, int E, int H, bool glu,
-                        int act, int* dev_status, cudaStream_t s) {
+                        int act, int* dev_status, cudaStream_t s, NormCapture nc) {
   Params p = {};
   p.x = (const bf16*)x;
   p.N = N;
@@ -1165,6 +1198,9 @@ int launch_experts_umma(const void* x, const int32_t* token_idx, const int32_t* 
   p.glu = glu ? 1 : 0;
   p.dev_status = dev_status;
   p.tma_gather = g_experts_kernel.load() == 2 ? 1 : 0;
+  p.norms = (bf16*)nc.norms;
+  p.norm_layer = nc.norms ? nc.layer : 0;
+  p.norm_ord = nc.ord;
   const long long max_tiles = (N * (long long)E + TILE_M - 1) / TILE_M + E;
   return launch<MODE_EXPERTS>(p, max_tiles, s);
 }

@@ -10,7 +10,8 @@ int launch_prepack_experts(const void* w1, const void* b1, const void* w_up, con
                            void* packed, int d, int E, int H, cudaStream_t s);
 int launch_experts_umma(const void* x, const int32_t* token_idx, const int32_t* offsets,
                         const void* packed, void* out, int64_t N, int d, int E, int H, bool glu,
-                        int act, int* dev_status, cudaStream_t s);
+                        int act, int* dev_status, cudaStream_t s,
+                        NormCapture nc = NormCapture());
 
 bool umma_router_supported(int d, int R, int E, int dtype);
 size_t umma_router_packed_bytes(int d, int R, int E);

@@ -142,6 +142,9 @@ class B200KernelExperts(ExpertsLayer):
         self.output_activation_extraction_stub = ExpertOutputActivationExtractionStub()
         self._wsp = _WorkspaceCache()
         self._packed = _PackedCache()
+        self._capture = None
+        self._norm_sinks = []
+        self.captured_norms = None
 
     @property
     def forward_mode(self):
@@ -167,6 +170,37 @@ class B200KernelExperts(ExpertsLayer):
         """Drop the packed weight copy (needed only after writes through ``.data``)."""
         self._packed.invalidate()
 
+    # -- router-training labels as a by-product of the expert kernel ----------------------
+    def capture_norms(self, layer, ord=2):
+        """Make every following forward also produce ``captured_norms`` [E, N]: the vector
+        norm (ord 1 or 2, over the last dimension) of each expert's ``layer`` activations
+        ('intermediate' = act(x W1 + b1), 'output' = the expert's output) for each token it
+        runs on, zero elsewhere.  This is what router training reads through forward hooks
+        on the extraction stubs upstream (methods/dynamic_sparsification/train_routers.py:
+        49-82, utils.py:353-369) without the [E, N, d] activations being materialised.
+        ``layer=None`` switches the capture off."""
+        if layer is None:
+            self._capture = None
+            return
+        if layer not in ops.NORM_OF:
+            raise ValueError(f"Unknown layer for labels construction: {layer}")
+        if ord not in (1, 2):
+            raise NotImplementedError("vector norms of ord 1 and 2 are provided")
+        self._capture = (layer, int(ord))
+
+    def _norm_args(self, N, like):
+        """Keyword arguments of ops.experts_ffn for the current capture setting."""
+        if self._capture is None:
+            return {}
+        norms = torch.empty(self.num_experts, N, dtype=like.dtype, device=like.device)
+        return dict(norms=norms, norm_layer=self._capture[0], norm_ord=self._capture[1])
+
+    def _deliver_norms(self, kw):
+        if kw:
+            self.captured_norms = kw["norms"]
+            for saved, key in self._norm_sinks:
+                saved[key] = self.captured_norms
+
     def _check_mode(self):
         if self._forward_mode not in _KERNEL_MODES:
             raise NotImplementedError(
@@ -188,8 +222,10 @@ class B200KernelExperts(ExpertsLayer):
         p = self.kernel_params()
         ops.pack_mask(rt, wsp)
         ops.compact(wsp, N, E)
+        kw = self._norm_args(N, x)
         ops.experts_ffn(x, wsp, p["w1"], p["b1"], p["w2"], p["act"], out, w_up=p["w_up"],
-                        packed=self.packed(), accumulate=False)
+                        packed=self.packed(), accumulate=False, **kw)
+        self._deliver_norms(kw)
         return out
 
 
@@ -235,6 +271,9 @@ class B200GluExperts(B200KernelExperts):
         self._forward_mode = "b200"
         self._wsp = _WorkspaceCache()
         self._packed = _PackedCache()
+        self._capture = None
+        self._norm_sinks = []
+        self.captured_norms = None
 
     def kernel_params(self):
         return dict(w1=self.layers[0].w, b1=None, w2=self.layers[1].w, w_up=self.layers[2].w,
@@ -393,7 +432,8 @@ class MoeficationMoE(MoELayer):
         last_bias = self.last_bias.view(-1) if self.bias else None
         out = torch.empty_like(x2d)
         wsp = self._wsp.get(N, E, x.device)
-        fused = (self.forward_mode == "dynk_max" and self.router is not None
+        capture = getattr(self.experts, "_capture", None) is not None
+        fused = (self.forward_mode == "dynk_max" and self.router is not None and not capture
                  and isinstance(self.router, MoeficationRouter) and self.router.fusable())
         if N == 0:
             rt = torch.zeros(*orig_size[:-1], E, dtype=x.dtype, device=x.device)
@@ -407,7 +447,7 @@ class MoeficationMoE(MoELayer):
                             router_packed=self.router.packed(),
                             experts_packed=self.experts.packed(), routing_out=rt)
             rt = rt.view(*orig_size[:-1], E)
-        elif self.forward_mode == "dynk_max":
+        elif self.forward_mode == "dynk_max" and not capture:
             # any other router: its scores come from device tensor ops, the rule and the
             # rest of the layer from the library
             s = self.router(x)
@@ -418,7 +458,7 @@ class MoeficationMoE(MoELayer):
                             add_residual=self.add_residual_connection,
                             experts_packed=self.experts.packed(), routing_out=rt)
             rt = rt.view(*orig_size[:-1], E)
-        elif self.forward_mode in ("topk", "dynk"):
+        elif self.forward_mode in ("topk", "dynk") and not capture:
             s = self.router(x)
             self._rule_mask(s.reshape(N, E).contiguous(), wsp)
             ops.compact(wsp, N, E)
@@ -427,12 +467,17 @@ class MoeficationMoE(MoELayer):
                             add_residual=self.add_residual_connection, accumulate=False)
             rt = ops.expand_mask(wsp, N, E, s.dtype).view(*orig_size[:-1], E)
         else:
+            # mode 'all' (every expert on every token: router training), and any mode while
+            # the experts capture their activation norms
             rt = self.gate(x)
             ops.pack_mask(rt.reshape(N, E).contiguous(), wsp)
             ops.compact(wsp, N, E)
+            kw = self.experts._norm_args(N, x2d) if capture else {}
             ops.experts_ffn(x2d, wsp, p["w1"], p["b1"], p["w2"], p["act"], out, w_up=p["w_up"],
                             packed=self.experts.packed(), last_bias=last_bias,
-                            add_residual=self.add_residual_connection, accumulate=False)
+                            add_residual=self.add_residual_connection, accumulate=False, **kw)
+            if capture:
+                self.experts._deliver_norms(kw)
         return out.view(orig_size), {self.name: (rt,)}
 
     # -- pre-norm + residual fused around the layer -----------------------------------
@@ -605,6 +650,60 @@ def fused_vit_block_forward(self, input: torch.Tensor):
     else:
         y = self.mlp(y)
     return x + y, gating_data
+
+
+class _NormCaptureHandle:
+    """What add_save_output_norm_hook returns per module: ``remove()`` like a torch hook handle."""
+
+    def __init__(self, experts, sink):
+        self._experts, self._sink = experts, sink
+
+    def remove(self):
+        if self._sink in self._experts._norm_sinks:
+            self._experts._norm_sinks.remove(self._sink)
+        if not self._experts._norm_sinks:
+            self._experts.capture_norms(None)
+
+
+def add_save_output_norm_hook(model, module_names, ord, dim=-1):
+    """Same contract as the upstream helper (utils.py:353-369): returns ``(saved, handles)``;
+    after each forward of ``model``, ``saved[name]`` holds
+    ``torch.linalg.vector_norm(output of module name, ord=ord, dim=dim)``.  For the modules
+    router training names inside an experts layer of this package -- the two extraction stubs
+    of B200KernelExperts, ``layers[0]`` / ``layers[1]`` of B200GluExperts
+    (methods/dynamic_sparsification/train_routers.py:49-71) -- the [E, N] norms come out of the
+    expert kernel itself; any other module gets an ordinary forward hook."""
+    saved, handles = {}, []
+    for name in module_names:
+        module = model.get_submodule(name)
+        parent = model.get_submodule(name.rsplit(".", 1)[0]) if "." in name else model
+        experts, layer = None, None
+        if isinstance(parent, B200KernelExperts):
+            if module is getattr(parent, "intermediate_activation_extraction_stub", None):
+                experts, layer = parent, "intermediate"
+            elif module is getattr(parent, "output_activation_extraction_stub", None):
+                experts, layer = parent, "output"
+        elif isinstance(parent, nn.ModuleList) and name.count(".") >= 1:
+            owner_name = name.rsplit(".", 2)[0] if name.count(".") >= 2 else ""
+            owner = model.get_submodule(owner_name) if owner_name else model
+            if isinstance(owner, B200GluExperts) and parent is owner.layers:
+                idx = int(name.rsplit(".", 1)[1])
+                if idx in (0, 1):
+                    experts, layer = owner, ("intermediate", "output")[idx]
+        if experts is None:
+            def save_norm_hook(m, _input, output, _name=name):
+                saved[_name] = torch.linalg.vector_norm(output, ord=ord, dim=dim)
+            handles.append(module.register_forward_hook(save_norm_hook))
+            continue
+        if dim != -1:
+            raise NotImplementedError("the expert kernel takes norms over the last dimension")
+        if experts._capture is not None and experts._capture != (layer, int(ord)):
+            raise NotImplementedError("one captured layer / ord per experts module at a time")
+        experts.capture_norms(layer, ord)
+        sink = (saved, name)
+        experts._norm_sinks.append(sink)
+        handles.append(_NormCaptureHandle(experts, sink))
+    return saved, handles
 
 
 def bind_upstream(moe_layers=None) -> bool:

@@ -199,16 +199,33 @@ def compact(wsp: Workspace, N: int, E: int):
               "d2d_compact")
 
 
+NORM_OF = {"intermediate": 1, "output": 2}
+
+
 def experts_ffn(x2d, wsp: Workspace, w1, b1, w2, act: str, out, *, w_up=None, packed=None,
-                last_bias=None, add_residual=False, accumulate=False):
-    _cu(x2d, w1, b1, w2, w_up, packed, last_bias, out, wsp.token_idx)
+                last_bias=None, add_residual=False, accumulate=False, norms=None,
+                norm_layer="output", norm_ord=2):
+    """Grouped expert FFN over the token lists in ``wsp`` with scatter-add into ``out``.
+    ``norms`` [E, N] (optional, dtype of x) receives the vector norm (``norm_ord`` 1 or 2) of
+    every computed pair's ``norm_layer`` ('intermediate' | 'output') activations: the labels
+    router training captures upstream (utils.py:353-369)."""
+    _cu(x2d, w1, b1, w2, w_up, packed, last_bias, out, wsp.token_idx, norms)
     N, d = x2d.shape
     E, _, H = w1.shape
     with _on(x2d) as st:
-        check(lib.d2d_experts_ffn(_ptr(x2d), _ptr(wsp.token_idx), _ptr(wsp.offsets), _ptr(w1),
-                                  _ptr(b1), _ptr(w_up), _ptr(w2), _ptr(packed), _ptr(last_bias),
-                                  int(add_residual), int(accumulate), _ptr(out), N, d, E, H,
-                                  ACT[act], _dt(x2d), _ptr(wsp.status), st), "d2d_experts_ffn")
+        if norms is None:
+            check(lib.d2d_experts_ffn(_ptr(x2d), _ptr(wsp.token_idx), _ptr(wsp.offsets), _ptr(w1),
+                                      _ptr(b1), _ptr(w_up), _ptr(w2), _ptr(packed), _ptr(last_bias),
+                                      int(add_residual), int(accumulate), _ptr(out), N, d, E, H,
+                                      ACT[act], _dt(x2d), _ptr(wsp.status), st), "d2d_experts_ffn")
+        else:
+            if norms.shape != (E, N) or norms.dtype != x2d.dtype or not norms.is_contiguous():
+                raise ValueError("norms must be a contiguous [E, N] tensor of x's dtype")
+            check(lib.d2d_experts_ffn_norms(
+                _ptr(x2d), _ptr(wsp.token_idx), _ptr(wsp.offsets), _ptr(w1), _ptr(b1), _ptr(w_up),
+                _ptr(w2), _ptr(packed), _ptr(last_bias), int(add_residual), int(accumulate),
+                _ptr(out), _ptr(norms), NORM_OF[norm_layer], int(norm_ord), N, d, E, H, ACT[act],
+                _dt(x2d), _ptr(wsp.status), st), "d2d_experts_ffn_norms")
 
 
 def moe_forward(x2d, wa, wb, tau, w1, b1, w2, act: str, out, wsp: Workspace, *, w_up=None,

@@ -177,6 +177,28 @@ int d2d_experts_ffn(const void* x, const int32_t* token_idx, const int32_t* offs
                     int64_t N, int d, int E, int H, int act, int dtype,
                     int* dev_status, d2d_stream_t stream);
 
+/* d2d_experts_ffn with the labels of router training as a by-product.  Upstream runs the
+ * layer in mode 'all' (every expert on every token, architectures/moe/moefication.py:56-58)
+ * and captures, with forward hooks on the experts' extraction stubs / layers, the vector norm
+ * over the last dimension of every expert's activations
+ * (methods/dynamic_sparsification/train_routers.py:49-71,77-82; utils.py:353-369
+ * torch.linalg.vector_norm(output, ord, dim=-1) -> [E, N]).  Here the expert kernel itself
+ * accumulates the norm of each (expert, token) pair it computes, without materialising the
+ * [E, N, d] / [E, N, H] activations:
+ *   norms[e * N + t] = T(|| a_e(t) ||_ord),   a_e(t) = act(T(x[t] W1[e]) + b1[e])   (D2D_NORM_OF_INTERMEDIATE)
+ *                                                   or T(h_e(t) W2[e])               (D2D_NORM_OF_OUTPUT)
+ * over the T-rounded elements, fp32 accumulation, one rounding to T.  ord 1 or 2.  The call
+ * first sets all E*N entries to zero; pairs outside the token lists stay zero (with the lists
+ * of an all-ones routing tensor every entry is written).  Everything else as d2d_experts_ffn. */
+#define D2D_NORM_OF_INTERMEDIATE 1
+#define D2D_NORM_OF_OUTPUT 2
+int d2d_experts_ffn_norms(const void* x, const int32_t* token_idx, const int32_t* offsets,
+                          const void* w1, const void* b1_opt, const void* w_up_opt,
+                          const void* w2, const void* experts_packed_opt,
+                          const void* last_bias_opt, int add_residual, int accumulate, void* out,
+                          void* norms, int norm_layer, int norm_ord, int64_t N, int d, int E,
+                          int H, int act, int dtype, int* dev_status, d2d_stream_t stream);
+
 /* Pre-norm fused with the block's residual: the pass in front of the layer.  An upstream
  * block runs  y = ln_2(x); y = mlp(y); return x + y  (architectures/moe/moe_models.py:69-76
  * ViT, :91-100 GPT, :148-156 Gemma).  This call reads x [N, d] once and writes

@@ -360,3 +360,30 @@ def prenorm(x: torch.Tensor, gamma: torch.Tensor, beta, eps: float, kind: str,
     else:
         y = xf * torch.rsqrt(xf.pow(2).mean(-1, keepdim=True) + eps) * (gamma_offset + gamma.float())
     return y.to(dt)
+
+
+# --------------------------------------------------------------------------
+# router-training labels: per-expert norms of what every expert computes
+# --------------------------------------------------------------------------
+def expert_activation_norms(x2d: torch.Tensor, w1, b1, w2, act: str, w_up=None, *,
+                            layer: str = "output", ord=2) -> torch.Tensor:
+    """[E, N] vector norms over the last dimension of every expert's activations on every
+    token, as router training captures them with forward hooks while the layer runs in
+    mode 'all' (methods/dynamic_sparsification/train_routers.py:49-71,77-82,204-209;
+    utils.py:353-369 ``torch.linalg.vector_norm(output, ord=ord, dim=-1)``):
+      layer "intermediate": act(x W1[e] + b1[e])      (moe_layers.py:116-124, :41-49 layers[0])
+      layer "output":       (that, times x W_up[e] in the gated form) W2[e]
+                                                      (moe_layers.py:127-133, :91-96 layers[1])
+    Every product and sum is rounded to the tensor dtype like the upstream einsum chain."""
+    dt = x2d.dtype
+    xe = x2d.unsqueeze(0)
+    h = torch.einsum("eni,eio->eno", xe, w1)
+    if b1 is not None:
+        h = h + b1.unsqueeze(-2)
+    h = activation(h, act)
+    if layer == "intermediate":
+        return torch.linalg.vector_norm(h, ord=ord, dim=-1)
+    if w_up is not None:
+        h = h * torch.einsum("eni,eio->eno", xe, w_up)
+    y = torch.einsum("eni,eio->eno", h, w2).to(dt)
+    return torch.linalg.vector_norm(y, ord=ord, dim=-1)
