@@ -623,9 +623,19 @@ def run_ours(args):
     step_q = {}
     stack.step()
     launches_per_layer = stack.launches_per_layer()
-    ms_eager = timed(stack.step, max(2, min(steps, 20)), warmup, dist) / max(2, min(steps, 20))
-    replay = None if args.eager else stack.graphed()
-    run_step = replay or stack.step
+    step_fn = stack.step
+    if args.quick and args.workload != "layer":     # profiling aids: other timed workloads
+        if args.workload == "block":
+            qnorms = [torch.nn.LayerNorm(c["d"], eps=1e-6).to(c["dtype"]).to(dev)
+                      for _ in range(stack.layers)]
+            step_fn = lambda: stack.block_step(qnorms, True)       # noqa: E731
+        else:                                           # "labels": mode 'all' + norm capture
+            for m in stack.mods:
+                m.forward_mode = "all"
+                m.experts.capture_norms("output", 2)
+    ms_eager = timed(step_fn, max(2, min(steps, 20)), warmup, dist) / max(2, min(steps, 20))
+    replay = None if args.eager else stack.graphed(step_fn)
+    run_step = replay or step_fn
     ms = timed(run_step, steps, warmup, dist, quantiles=step_q)
     value = tokens_step_global * steps / (ms * 1e-3)
     if args.quick:
@@ -636,7 +646,8 @@ def run_ours(args):
             print(json.dumps({"metric": "moe_ffn_layer_tokens_per_s", "value": value,
                               "unit": "tokens/s", "ms_per_step": ms / steps, "quick": True,
                               "eager_ms_per_step": ms_eager, "graph": replay is not None,
-                              "layers": stack.layers, "tau_cfg": HEADLINE_TAU, "clocks": clocks}))
+                              "layers": stack.layers, "tau_cfg": HEADLINE_TAU,
+                              "workload": args.workload, "clocks": clocks}))
         return
 
     # ---- tau sweep ----------------------------------------------------------------
@@ -847,6 +858,10 @@ def main():
                     help="profiling aid: tau_cfg of the headline measurement")
     ap.add_argument("--eager", action="store_true",
                     help="time eager launches instead of CUDA-graph replays of the step")
+    ap.add_argument("--workload", default="layer", choices=["layer", "block", "labels"],
+                    help="profiling aid (with --quick): time the module forward (default), the "
+                         "fused pre-norm + layer + residual block, or the mode-'all' forward "
+                         "with label capture")
     ap.add_argument("--quick", action="store_true",
                     help="profiling aid: headline timing only (no sweep, stages, e2e, CPU legs)")
     ap.add_argument("--config", default=HEADLINE, choices=list(CONFIGS),

@@ -652,6 +652,70 @@ def fused_vit_block_forward(self, input: torch.Tensor):
     return x + y, gating_data
 
 
+def _dropout_is_identity(module) -> bool:
+    drop = getattr(module, "dropout", None)
+    return drop is None or not drop.training or getattr(drop, "p", 0.0) == 0.0
+
+
+def fused_gpt_block_forward(self, input: torch.Tensor):
+    """Replacement for the upstream ``moe_gpt_block_forward``
+    (architectures/moe/moe_models.py:78-100): same computation and return value, with
+    ``h + dropout(mlp(ln_2(h)))`` run as ``mlp.forward_block(h, ln_2)`` when ``mlp`` is a layer of
+    this package and its dropout is inactive (evaluation mode)."""
+    gating_data = {}
+    ln1 = self.ln_1(input)
+    res = self.attn(query=ln1, key=ln1, value=ln1, need_weights=False) \
+        if hasattr(self.attn, "in_proj_weight") or hasattr(self.attn, "q_proj") else self.attn(ln1)
+    if isinstance(res, tuple) and len(res) == 3:     # MoE-fied attention: gating data as well
+        attn_output, _, attn_gating_data = res
+        gating_data.update(attn_gating_data)
+    else:
+        attn_output = res[0] if isinstance(res, tuple) else res
+    h = input + attn_output
+    if isinstance(self.mlp, MoeficationMoE) and _dropout_is_identity(self.mlp):
+        out, ffn_gating_data = self.mlp.forward_block(h, self.ln_2)
+        gating_data.update(ffn_gating_data)
+        return out, gating_data
+    ln2 = self.ln_2(h)
+    if isinstance(self.mlp, MoELayer):
+        mlp_out, ffn_gating_data = self.mlp(ln2)
+        if hasattr(self.mlp, "dropout"):
+            mlp_out = self.mlp.dropout(mlp_out)
+        gating_data.update(ffn_gating_data)
+    else:
+        mlp_out = self.mlp(ln2)
+    return h + mlp_out, gating_data
+
+
+def fused_gemma_decoder_forward(self, hidden_states: torch.Tensor, attention_mask: torch.Tensor,
+                                position_ids: torch.Tensor, cache_position: torch.Tensor):
+    """Replacement for the upstream ``moe_gemma_decoder_forward``
+    (architectures/moe/moe_models.py:132-160): same computation and return value, with
+    ``residual + mlp(post_attention_layernorm(residual))`` run as
+    ``mlp.forward_block(residual, post_attention_layernorm)`` (RMSNorm with the 1 + weight
+    scale, gated experts) when ``mlp`` is a layer of this package."""
+    gating_data = {}
+    residual = hidden_states
+    hidden_states = self.input_layernorm(hidden_states)
+    hidden_states, _w, _kv = self.self_attn(hidden_states=hidden_states,
+                                            attention_mask=attention_mask,
+                                            position_ids=position_ids,
+                                            cache_position=cache_position)
+    hidden_states = residual + hidden_states
+    if isinstance(self.mlp, MoeficationMoE):
+        out, ffn_gating_data = self.mlp.forward_block(hidden_states, self.post_attention_layernorm)
+        gating_data.update(ffn_gating_data)
+        return out, gating_data
+    residual = hidden_states
+    hidden_states = self.post_attention_layernorm(hidden_states)
+    if isinstance(self.mlp, MoELayer):
+        hidden_states, ffn_gating_data = self.mlp(hidden_states)
+        gating_data.update(ffn_gating_data)
+    else:
+        hidden_states = self.mlp(hidden_states)
+    return residual + hidden_states, gating_data
+
+
 class _NormCaptureHandle:
     """What add_save_output_norm_hook returns per module: ``remove()`` like a torch hook handle."""
 

@@ -226,3 +226,85 @@ def test_prenorm_rejects_rows_it_cannot_hold():
     g = torch.ones(100, device="cuda", dtype=torch.bfloat16)
     with pytest.raises(ops._capi.D2DError):
         ops.prenorm_init(x, g, None, 1e-6, ops.NORM_RMS, torch.empty_like(x))
+
+
+@pytest.mark.gpu
+def test_fused_gpt_block_forward_equals_the_unfused_block():
+    import functools
+    import d2dmoe_b200 as D
+    c, kind, eps = CASES[0]
+    g, t = load(c, kind)
+
+    class CausalSelfAttention(torch.nn.Module):     # one-argument attention, as in the GPT block
+        def __init__(self):
+            super().__init__()
+            self.c_attn = torch.nn.Linear(c.d, c.d)
+
+        def forward(self, x):
+            return torch.tanh(self.c_attn(x))
+
+    class Block(torch.nn.Module):                  # attribute names of the upstream GPT block
+        def __init__(self):
+            super().__init__()
+            self.ln_1 = torch.nn.LayerNorm(c.d, eps=eps)
+            self.attn = CausalSelfAttention()
+            self.ln_2 = torch.nn.LayerNorm(c.d, eps=eps)
+            self.mlp = None
+
+    torch.manual_seed(6)
+    blk = Block().to(c.torch_dtype)
+    with torch.no_grad():
+        blk.ln_2.weight.copy_(t["gamma"])
+        blk.ln_2.bias.copy_(t["beta"])
+    blk.mlp = _module(c, t)
+    blk.mlp.dropout = torch.nn.Dropout(0.1)        # upstream attaches it; inactive in eval mode
+    blk = blk.cuda().eval()
+    blk.forward = functools.partial(D.fused_gpt_block_forward, blk)
+    x = t["x"].cuda()
+    with torch.no_grad():
+        out, gd = blk(x)
+        h = x + blk.attn(blk.ln_1(x))
+        y, gd2 = blk.mlp(blk.ln_2(h))
+        ref = h + y
+    agree = gd[c.name][0].eq(gd2[c.name][0]).all(-1)
+    assert agree.float().mean().item() >= 0.98
+    assert O.rel_err(out[agree].float().cpu(), ref[agree].float().cpu()) <= TOL[c.dtype]
+
+
+@pytest.mark.gpu
+def test_fused_gemma_decoder_forward_equals_the_unfused_layer():
+    import functools
+    import d2dmoe_b200 as D
+    c, kind, eps = CASES[2]
+    g, t = load(c, kind)
+
+    class Attn(torch.nn.Module):                   # keyword interface of the Gemma attention
+        def __init__(self):
+            super().__init__()
+            self.o = torch.nn.Linear(c.d, c.d, bias=False)
+
+        def forward(self, hidden_states, attention_mask, position_ids, cache_position):
+            return self.o(hidden_states), None, None
+
+    class Layer(torch.nn.Module):                  # attribute names of GemmaDecoderLayer
+        def __init__(self):
+            super().__init__()
+            self.input_layernorm = _norm(c, t, kind, eps)
+            self.self_attn = Attn()
+            self.post_attention_layernorm = _norm(c, t, kind, eps)
+            self.mlp = None
+
+    torch.manual_seed(7)
+    lyr = Layer().to(c.torch_dtype)
+    lyr.mlp = _module(c, t)
+    lyr = lyr.cuda().eval()
+    lyr.forward = functools.partial(D.fused_gemma_decoder_forward, lyr)
+    x = t["x"].cuda()
+    with torch.no_grad():
+        out, gd = lyr(x, None, None, None)
+        h = x + lyr.self_attn(lyr.input_layernorm(x), None, None, None)[0]
+        y, gd2 = lyr.mlp(lyr.post_attention_layernorm(h))
+        ref = h + y
+    agree = gd[c.name][0].eq(gd2[c.name][0]).all(-1)
+    assert agree.float().mean().item() >= 0.97
+    assert O.rel_err(out[agree].float().cpu(), ref[agree].float().cpu()) <= TOL[c.dtype]
