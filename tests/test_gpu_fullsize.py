@@ -218,3 +218,58 @@ def test_full_size_configs_sampled_rows(name):
     assert O.rel_err(out.reshape(n, d)[idx.cuda()].float().cpu(), ex) <= 2e-2
     # every row was written (no row left at its pre-call contents): all finite and no row of zeros
     assert torch.isfinite(out.float()).all()
+
+
+def test_fused_block_at_full_size(layer):
+    """Pre-norm + residual folded around the layer at 50432 tokens: the fused call against
+    torch LayerNorm + layer + add on every row whose routing agrees, and against the fp64
+    evaluation (normalised row through the experts the layer chose) on sampled rows."""
+    moe, x = layer
+    g = torch.Generator(device="cuda").manual_seed(12)
+    xin = (x.float() * 1.3 + 0.2).bfloat16()
+    ln = torch.nn.LayerNorm(D, eps=1e-6).cuda().bfloat16()
+    with torch.no_grad():
+        ln.weight.copy_(1.0 + 0.1 * torch.randn(D, generator=g, device="cuda"))
+        ln.bias.copy_(0.1 * torch.randn(D, generator=g, device="cuda"))
+    out, gd = moe.forward_block(xin, ln)
+    y, gd2 = moe(ln(xin))
+    ref = xin + y
+    m = gd["moe"][0].reshape(N, E) > 0
+    agree = m.eq(gd2["moe"][0].reshape(N, E) > 0).all(-1)
+    assert agree.float().mean().item() >= 0.99
+    o2, r2 = out.reshape(N, D)[agree].float(), ref.reshape(N, D)[agree].float()
+    assert ((o2 - r2).abs().max() / r2.abs().max()).item() <= 2e-2
+    rows = torch.arange(0, N, 997, device="cuda")
+    xs = xin.reshape(N, D)[rows].cpu()
+    xn = O.prenorm(xs, ln.weight.detach().cpu(), ln.bias.detach().cpu(), 1e-6, "layer")
+    exact = O.experts_ffn_exact(xn, m[rows].cpu(), moe.experts.w1.detach().cpu(),
+                                moe.experts.b1.detach().cpu(), moe.experts.w2.detach().cpu(), "relu")
+    exact = exact + moe.last_bias.detach().cpu().double() + xs.double()
+    assert O.rel_err(out.reshape(N, D)[rows].cpu().float(), exact) <= 2e-2
+    moe.last_workspace(N, x.device).check_status()
+
+
+def test_label_capture_at_full_size(layer):
+    """Mode 'all' at 50432 tokens x 24 experts: every pair carries a label, sampled tokens
+    agree with the upstream recipe evaluated on the host, and the output is the dense FFN."""
+    moe, x = layer
+    mode = moe.forward_mode
+    moe.forward_mode = "all"
+    moe.experts.capture_norms("output", 2)
+    try:
+        out, gd = moe(x)
+        norms = moe.experts.captured_norms
+    finally:
+        moe.experts.capture_norms(None)
+        moe.forward_mode = mode
+    assert norms.shape == (E, N) and bool((norms > 0).all())
+    rows = torch.arange(0, N, 1009, device="cuda")
+    xs = x.reshape(N, D)[rows].cpu()
+    w1, b1, w2 = (p.detach().cpu() for p in (moe.experts.w1, moe.experts.b1, moe.experts.w2))
+    ref = O.expert_activation_norms(xs, w1, b1, w2, "relu", layer="output", ord=2)
+    assert O.rel_err(norms[:, rows].cpu().float(), ref.float()) <= 2e-2
+    exact = O.experts_ffn_exact(xs, torch.ones(len(rows), E, dtype=torch.bool), w1, b1, w2, "relu")
+    exact = exact + moe.last_bias.detach().cpu().double()
+    # 24 bf16 adds per element: the summation-order bound of a dense row
+    assert O.rel_err(out.reshape(N, D)[rows].cpu().float(), exact) <= 4e-2
+    moe.last_workspace(N, x.device).check_status()
