@@ -246,9 +246,12 @@ int d2d_moe_forward(const void* x, const void* wa, const void* wb, const void* r
     rt_done = true;
     nl += 1;
   } else {
-    rc = d2d_router_mask(x, wa, wb, router_packed_opt, thresh_mult, mask_bits, nullptr,
-                         last_bias_opt, add_residual, out_init, N, d, R, E, dtype, dev_status,
-                         stream);
+    // general-shape router: mask bits, routing tensor and the output's initial value
+    if (!wb || R < 1) return D2D_ERR_BAD_ARG;
+    rc = launch_router_mask_simt(x, wa, wb, thresh_mult, mask_bits, nullptr, last_bias_opt,
+                                 add_residual, out_init, N, d, R, E, dtype, dev_status,
+                                 (cudaStream_t)stream, routing_tensor_opt);
+    rt_done = true;
     nl += 1;
   }
   if (rc != D2D_OK) return rc;

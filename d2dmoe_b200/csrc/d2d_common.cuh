@@ -134,7 +134,7 @@ struct NormCapture {
 int launch_router_mask_simt(const void* x, const void* wa, const void* wb, float mult,
                             uint32_t* mask_bits, void* scores, const void* last_bias,
                             int add_residual, void* out_init, int64_t N, int d, int R, int E,
-                            int dtype, int* dev_status, cudaStream_t s);
+                            int dtype, int* dev_status, cudaStream_t s, void* rt_out = nullptr);
 int launch_gate_rule(const void* scores, int rule, int k, float tau, uint32_t* mask_bits,
                      int64_t N, int E, int dtype, cudaStream_t s);
 int launch_mask_from_scores(const void* scores, float mult, uint32_t* mask_bits, int64_t N, int E,

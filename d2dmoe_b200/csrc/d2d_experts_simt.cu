@@ -24,18 +24,16 @@ constexpr int MAX_E = 256;
 // one element's share of a row's norm (ord 1: magnitude, ord 2: square)
 __device__ __forceinline__ float norm_term(float v, int ord) { return ord == 1 ? fabsf(v) : v * v; }
 
-// Row sums held as per-lane partials (lane = 4 columns): reduce over the warp and let lane 0
-// write norms[e, token] for the warp's four rows.
-template <typename T>
-__device__ __forceinline__ void write_row_norms(float* part, int ord, T* norms, int e, int64_t N,
-                                                const int* rows, int ty, int lane) {
+// Row sums held as per-thread partials (a row's columns are spread over 8 lanes of each of
+// 4 warps): reduce over the 8 lanes, add into the row's shared cell.
+__device__ __forceinline__ void add_row_norms(const float* part, float* rown, int row0, int lc) {
 #pragma unroll
   for (int i = 0; i < 4; ++i) {
     float v = part[i];
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
-    const int t = rows[4 * ty + i];
-    if (lane == 0 && t >= 0) norms[(int64_t)e * N + t] = DT<T>::from_f(ord == 1 ? v : sqrtf(v));
+    v += __shfl_xor_sync(0xffffffffu, v, 1);
+    v += __shfl_xor_sync(0xffffffffu, v, 2);
+    v += __shfl_xor_sync(0xffffffffu, v, 4);
+    if (lc == 0) atomicAdd(&rown[row0 + 4 * i], v);
   }
 }
 
@@ -55,7 +53,16 @@ experts_simt_kernel(const T* __restrict__ x, const int32_t* __restrict__ token_i
   const int HP = ((H + 3) & ~3) + 4;
   __shared__ int tstart[MAX_E + 1];
   __shared__ int rows[TM];
+  __shared__ float rown[TM];                   // row sums of the norm by-product
   const int tid = threadIdx.x, lane = tid & 31, ty = tid >> 5;
+  // Thread tile of both products: warps 2 (rows) x 4 (columns), lanes 4 x 8; thread (i, j)
+  // holds row 16*rg + lr + 4i and column 32*cg + 4*lc + j of the 32 x 128 pass.  The lanes
+  // of a warp instruction then read 4 distinct activation vectors and 8 adjacent weight
+  // vectors: 8 shared-memory wavefronts per 64 FMAs.
+  const int rg = ty >> 2, cg = ty & 3, lr = lane >> 3, lc = lane & 7;
+  const int row0 = 16 * rg + lr, col0 = 32 * cg + 4 * lc;
+  grid_launch_dependents();
+  grid_dependency_wait();      // token lists and offsets come from the previous kernel
 
   if (tid == 0) {
     int run = 0;
@@ -90,6 +97,7 @@ experts_simt_kernel(const T* __restrict__ x, const int32_t* __restrict__ token_i
       int t = tid < nrows ? token_idx[r0 + tid] : -1;
       if (tid < nrows && (t < 0 || t >= N)) { report(dev_status, D2D_ERR_INDEX_RANGE); t = -1; }
       rows[tid] = t;
+      rown[tid] = 0.f;
     }
     __syncthreads();
     const T* w1e = w1 + (int64_t)e * d * H;
@@ -151,12 +159,12 @@ experts_simt_kernel(const T* __restrict__ x, const int32_t* __restrict__ token_i
           float4 xa[4];
 #pragma unroll
           for (int i = 0; i < 4; ++i)
-            xa[i] = *reinterpret_cast<const float4*>(&xs[(4 * ty + i) * XP + k4]);
+            xa[i] = *reinterpret_cast<const float4*>(&xs[(row0 + 4 * i) * XP + k4]);
 #pragma unroll
           for (int kk = 0; kk < 4; ++kk) {
-            const float4 wv = *reinterpret_cast<const float4*>(&ws[(k4 + kk) * WP + 4 * lane]);
+            const float4 wv = *reinterpret_cast<const float4*>(&ws[(k4 + kk) * WP + col0]);
             float4 uv = make_float4(0.f, 0.f, 0.f, 0.f);
-            if (GLU) uv = *reinterpret_cast<const float4*>(&wu[(k4 + kk) * WP + 4 * lane]);
+            if (GLU) uv = *reinterpret_cast<const float4*>(&wu[(k4 + kk) * WP + col0]);
 #pragma unroll
             for (int i = 0; i < 4; ++i) {
               const float xv = kk == 0 ? xa[i].x : kk == 1 ? xa[i].y : kk == 2 ? xa[i].z : xa[i].w;
@@ -178,14 +186,14 @@ experts_simt_kernel(const T* __restrict__ x, const int32_t* __restrict__ token_i
       for (int i = 0; i < 4; ++i)
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
-          const int c = hc + 4 * lane + j;
+          const int c = hc + col0 + j;
           if (c < H) {
             float h = DT<T>::round(acc[i][j]);
             if (b1) h = DT<T>::round(h + DT<T>::to_f(b1[(int64_t)e * H + c]));
             h = DT<T>::round(activate(h, act));
             if (norm_layer == D2D_NORM_OF_INTERMEDIATE) npart[i] += norm_term(h, norm_ord);
             if (GLU) h = DT<T>::round(h * DT<T>::round(accu[i][j]));
-            hs[(4 * ty + i) * HP + c] = h;
+            hs[(row0 + 4 * i) * HP + c] = h;
           }
         }
     }
@@ -224,11 +232,30 @@ experts_simt_kernel(const T* __restrict__ x, const int32_t* __restrict__ token_i
         }
         __syncthreads();
         const int kn = min(KC, H - kc);
-        for (int k = 0; k < kn; ++k) {
-          const float4 wv = *reinterpret_cast<const float4*>(&ws[k * WP + 4 * lane]);
+        int k = 0;
+        for (; k + 4 <= kn; k += 4) {           // four hidden columns per activation vector
+          float4 ha[4];
+#pragma unroll
+          for (int i = 0; i < 4; ++i)
+            ha[i] = *reinterpret_cast<const float4*>(&hs[(row0 + 4 * i) * HP + kc + k]);
+#pragma unroll
+          for (int kk = 0; kk < 4; ++kk) {
+            const float4 wv = *reinterpret_cast<const float4*>(&ws[(k + kk) * WP + col0]);
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+              const float hv = kk == 0 ? ha[i].x : kk == 1 ? ha[i].y : kk == 2 ? ha[i].z : ha[i].w;
+              acc[i][0] = fmaf(hv, wv.x, acc[i][0]);
+              acc[i][1] = fmaf(hv, wv.y, acc[i][1]);
+              acc[i][2] = fmaf(hv, wv.z, acc[i][2]);
+              acc[i][3] = fmaf(hv, wv.w, acc[i][3]);
+            }
+          }
+        }
+        for (; k < kn; ++k) {
+          const float4 wv = *reinterpret_cast<const float4*>(&ws[k * WP + col0]);
 #pragma unroll
           for (int i = 0; i < 4; ++i) {
-            const float hv = hs[(4 * ty + i) * HP + kc + k];
+            const float hv = hs[(row0 + 4 * i) * HP + kc + k];
             acc[i][0] = fmaf(hv, wv.x, acc[i][0]);
             acc[i][1] = fmaf(hv, wv.y, acc[i][1]);
             acc[i][2] = fmaf(hv, wv.z, acc[i][2]);
@@ -236,7 +263,7 @@ experts_simt_kernel(const T* __restrict__ x, const int32_t* __restrict__ token_i
           }
         }
       }
-      const int c0 = dc + 4 * lane;
+      const int c0 = dc + col0;
       if (norm_layer == D2D_NORM_OF_OUTPUT) {
 #pragma unroll
         for (int i = 0; i < 4; ++i)
@@ -246,7 +273,7 @@ experts_simt_kernel(const T* __restrict__ x, const int32_t* __restrict__ token_i
       }
 #pragma unroll
       for (int i = 0; i < 4; ++i) {
-        const int t = rows[4 * ty + i];
+        const int t = rows[row0 + 4 * i];
         if (t < 0 || c0 >= d) continue;
         T* o = out + (int64_t)t * d + c0;
         if (vec_ok) {
@@ -259,7 +286,13 @@ experts_simt_kernel(const T* __restrict__ x, const int32_t* __restrict__ token_i
         }
       }
     }
-    if (norm_layer != 0) write_row_norms<T>(npart, norm_ord, norms, e, N, rows, ty, lane);
+    if (norm_layer != 0) {
+      add_row_norms(npart, rown, row0, lc);
+      __syncthreads();
+      if (tid < TM && rows[tid] >= 0)
+        norms[(int64_t)e * N + rows[tid]] =
+            DT<T>::from_f(norm_ord == 1 ? rown[tid] : sqrtf(rown[tid]));
+    }
   }
 }
 
@@ -277,10 +310,9 @@ int launch_t(const void* x, const int32_t* token_idx, const int32_t* offsets, co
     return D2D_ERR_LAUNCH;
   const int64_t max_tiles = ceil_div64(N * (int64_t)E, TM) + E;
   const int grid = (int)(max_tiles < 148 * 4 ? (max_tiles > 0 ? max_tiles : 1) : 148 * 4);
-  k<<<grid, NT, smem, s>>>((const T*)x, token_idx, offsets, (const T*)w1, (const T*)b1,
-                           (const T*)w_up, (const T*)w2, (T*)out, N, d, E, H, act, dev_status,
-                           (T*)nc.norms, nc.norms ? nc.layer : 0, nc.ord);
-  return cudaGetLastError() == cudaSuccess ? D2D_OK : D2D_ERR_LAUNCH;
+  return launch_pdl(k, dim3((unsigned)grid), dim3(NT), smem, s, (const T*)x, token_idx, offsets,
+                    (const T*)w1, (const T*)b1, (const T*)w_up, (const T*)w2, (T*)out, N, d, E, H,
+                    act, dev_status, (T*)nc.norms, nc.norms ? nc.layer : 0, nc.ord);
 }
 
 }  // namespace

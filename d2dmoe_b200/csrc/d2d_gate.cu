@@ -27,7 +27,7 @@ __device__ __forceinline__ float nanmax(float a, float b) {
 
 template <typename T>
 __device__ __forceinline__ void gate_row(const float* s, int nw, float mult, int lane,
-                                         uint32_t* mask_row, int E) {
+                                         uint32_t* mask_row, int E, T* rt_row = nullptr) {
   // s[j]: this lane's score for expert lane+32j (-inf-like sentinel for e >= E is
   // handled by the caller passing valid flags through E).
   float m = -INFINITY;
@@ -40,6 +40,7 @@ __device__ __forceinline__ void gate_row(const float* s, int nw, float mult, int
     const bool keep = (lane + 32 * j < E) && (s[j] >= thr);
     const uint32_t w = __ballot_sync(0xffffffffu, keep);
     if (lane == 0) mask_row[j] = w;
+    if (rt_row && lane + 32 * j < E) rt_row[lane + 32 * j] = DT<T>::from_f(keep ? 1.f : 0.f);
   }
 }
 
@@ -48,13 +49,22 @@ __global__ void __launch_bounds__(NT)
 router_mask_simt_kernel(const T* __restrict__ x, const T* __restrict__ wa,
                         const T* __restrict__ wb, float mult, uint32_t* __restrict__ mask_bits,
                         T* __restrict__ scores, const T* __restrict__ last_bias, int add_residual,
-                        T* __restrict__ out_init, int64_t N, int d, int R, int E) {
+                        T* __restrict__ out_init, int64_t N, int d, int R, int E,
+                        T* __restrict__ rt_out) {
   extern __shared__ float sm[];
   float* xs = sm;                      // [TM][KP]
   float* wsm = xs + TM * KP;           // [RC][KP]
   float* hs = wsm + RC * KP;           // [TM][R]
   const int tid = threadIdx.x, lane = tid & 31, ty = tid >> 5;
+  // GEMM1 thread tile: warps 2 (rows) x 4 (hidden columns), lanes 4 x 8; thread (i, j) holds
+  // row 16*rg + lr + 4i and column 32*cg + lc + 8j.  The lanes of a warp instruction then read
+  // 4 distinct x vectors and 8 distinct weight vectors, each set in distinct banks: 8
+  // shared-memory wavefronts per 64 FMAs.
+  const int rg = ty >> 2, cg = ty & 3, lr = lane >> 3, lc = lane & 7;
+  const int row0 = 16 * rg + lr, col0 = 32 * cg + lc;
   const int64_t t0 = (int64_t)blockIdx.x * TM;
+  grid_launch_dependents();
+  grid_dependency_wait();      // x may come from the previous kernel of the stream
   // vector staging needs rows that start on a 4-element boundary
   const bool vec = (d % 4 == 0) && ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(wa)) % 16 == 0);
 
@@ -106,10 +116,10 @@ router_mask_simt_kernel(const T* __restrict__ x, const T* __restrict__ wa,
         float4 xa[4], wv[4];
 #pragma unroll
         for (int i = 0; i < 4; ++i)
-          xa[i] = *reinterpret_cast<const float4*>(&xs[(4 * ty + i) * KP + k4]);
+          xa[i] = *reinterpret_cast<const float4*>(&xs[(row0 + 4 * i) * KP + k4]);
 #pragma unroll
         for (int j = 0; j < 4; ++j)
-          wv[j] = *reinterpret_cast<const float4*>(&wsm[(lane + 32 * j) * KP + k4]);
+          wv[j] = *reinterpret_cast<const float4*>(&wsm[(col0 + 8 * j) * KP + k4]);
 #pragma unroll
         for (int i = 0; i < 4; ++i)
 #pragma unroll
@@ -125,11 +135,20 @@ router_mask_simt_kernel(const T* __restrict__ x, const T* __restrict__ wa,
     for (int i = 0; i < 4; ++i)
 #pragma unroll
       for (int j = 0; j < 4; ++j) {
-        const int c = rc + lane + 32 * j;
-        if (c < R) hs[(4 * ty + i) * R + c] = fmaxf(DT<T>::round(acc[i][j]), 0.f);
+        const int c = rc + col0 + 8 * j;
+        if (c < R) hs[(row0 + 4 * i) * R + c] = fmaxf(DT<T>::round(acc[i][j]), 0.f);
       }
   }
   __syncthreads();
+
+  // Wb [E, R] into the (now free) weight staging area as [E][R + 1] floats when it fits: the
+  // second product then reads it conflict-free instead of with one strided global load per k
+  const int RP = R + 1;
+  const bool wb_s = (int64_t)E * RP <= RC * KP;
+  if (wb_s) {
+    for (int i = tid; i < E * R; i += NT) wsm[(i / R) * RP + (i % R)] = DT<T>::to_f(wb[i]);
+    __syncthreads();
+  }
 
   // scores + gate: warp ty owns rows 4ty..4ty+3, lane owns experts lane+32j
   const int nw = (E + 31) / 32;
@@ -139,9 +158,10 @@ router_mask_simt_kernel(const T* __restrict__ x, const T* __restrict__ wa,
     float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
     if (e < E) {
       const T* wrow = wb + (int64_t)e * R;
+      const float* wsr = wsm + e * RP;
       const float* h0 = hs + (4 * ty) * R;
       for (int k = 0; k < R; ++k) {
-        const float w = DT<T>::to_f(wrow[k]);
+        const float w = wb_s ? wsr[k] : DT<T>::to_f(wrow[k]);
         a0 = fmaf(h0[k], w, a0);
         a1 = fmaf(h0[R + k], w, a1);
         a2 = fmaf(h0[2 * R + k], w, a2);
@@ -160,16 +180,18 @@ router_mask_simt_kernel(const T* __restrict__ x, const T* __restrict__ wa,
     if (scores)
       for (int j = 0; j < nw; ++j)
         if (lane + 32 * j < E) scores[t * E + lane + 32 * j] = DT<T>::from_f(sc[i][j]);
-    gate_row<T>(sc[i], nw, mult, lane, mask_bits + t * nw, E);
+    gate_row<T>(sc[i], nw, mult, lane, mask_bits + t * nw, E, rt_out ? rt_out + t * E : nullptr);
   }
 
   if (out_init) {
     const int rows = (int)min((int64_t)TM, N - t0);
-    for (int64_t i = tid; i < (int64_t)rows * d; i += NT) {
-      const int r = (int)(i / d), c = (int)(i % d);
-      float v = last_bias ? DT<T>::to_f(last_bias[c]) : 0.f;
-      if (add_residual) v = DT<T>::round(v) + DT<T>::to_f(x[(t0 + r) * d + c]);
-      out_init[(t0 + r) * d + c] = DT<T>::from_f(v);
+    for (int c = tid; c < d; c += NT) {          // thread = column, rows inside
+      const float lb = last_bias ? DT<T>::round(DT<T>::to_f(last_bias[c])) : 0.f;
+      for (int r = 0; r < rows; ++r) {
+        float v = lb;
+        if (add_residual) v = lb + DT<T>::to_f(x[(t0 + r) * d + c]);
+        out_init[(t0 + r) * d + c] = DT<T>::from_f(v);
+      }
     }
   }
 }
@@ -536,7 +558,7 @@ inline int grid_for(int64_t work, int per_block, int cap) {
 int launch_router_mask_simt(const void* x, const void* wa, const void* wb, float mult,
                             uint32_t* mask_bits, void* scores, const void* last_bias,
                             int add_residual, void* out_init, int64_t N, int d, int R, int E,
-                            int dtype, int* dev_status, cudaStream_t s) {
+                            int dtype, int* dev_status, cudaStream_t s, void* rt_out) {
   (void)dev_status;
   if (E > 256 || R > 1024) return D2D_ERR_UNSUPPORTED;
   const size_t smem = sizeof(float) * ((size_t)TM * KP + (size_t)RC * KP + (size_t)TM * R);
@@ -547,16 +569,16 @@ int launch_router_mask_simt(const void* x, const void* wa, const void* wb, float
     err = cudaFuncSetAttribute(router_mask_simt_kernel<float>,
                                cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (err != cudaSuccess) return D2D_ERR_LAUNCH;
-    router_mask_simt_kernel<float><<<(unsigned)grid, NT, smem, s>>>(
+    return launch_pdl(router_mask_simt_kernel<float>, dim3((unsigned)grid), dim3(NT), smem, s,
         (const float*)x, (const float*)wa, (const float*)wb, mult, mask_bits, (float*)scores,
-        (const float*)last_bias, add_residual, (float*)out_init, N, d, R, E);
+        (const float*)last_bias, add_residual, (float*)out_init, N, d, R, E, (float*)rt_out);
   } else {
     err = cudaFuncSetAttribute(router_mask_simt_kernel<bf16>,
                                cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (err != cudaSuccess) return D2D_ERR_LAUNCH;
-    router_mask_simt_kernel<bf16><<<(unsigned)grid, NT, smem, s>>>(
+    return launch_pdl(router_mask_simt_kernel<bf16>, dim3((unsigned)grid), dim3(NT), smem, s,
         (const bf16*)x, (const bf16*)wa, (const bf16*)wb, mult, mask_bits, (bf16*)scores,
-        (const bf16*)last_bias, add_residual, (bf16*)out_init, N, d, R, E);
+        (const bf16*)last_bias, add_residual, (bf16*)out_init, N, d, R, E, (bf16*)rt_out);
   }
   return cudaGetLastError() == cudaSuccess ? D2D_OK : D2D_ERR_LAUNCH;
 }
