@@ -44,36 +44,37 @@ __device__ __forceinline__ void gate_row(const float* s, int nw, float mult, int
   }
 }
 
-template <typename T>
+// TM_ tokens per CTA: 32, or 16 when 32-token tiles would leave SMs without a tile.
+// GEMM1 thread tile: the 8 warps as RG (rows) x CG (hidden columns), lanes 4 x 8; thread (i, j)
+// holds row 16*rg + lr + 4i and column CW*cg + lc + 8j.  The lanes of a warp instruction then
+// read 4 distinct x vectors and 8 distinct weight vectors, each set in distinct banks.
+template <typename T, int TM_>
 __global__ void __launch_bounds__(NT)
 router_mask_simt_kernel(const T* __restrict__ x, const T* __restrict__ wa,
                         const T* __restrict__ wb, float mult, uint32_t* __restrict__ mask_bits,
                         T* __restrict__ scores, const T* __restrict__ last_bias, int add_residual,
                         T* __restrict__ out_init, int64_t N, int d, int R, int E,
                         T* __restrict__ rt_out) {
+  constexpr int RG = TM_ / 16, CG = 8 / RG, CW = RC / CG, CPT = CW / 8, RPW = TM_ / 8;
   extern __shared__ float sm[];
-  float* xs = sm;                      // [TM][KP]
-  float* wsm = xs + TM * KP;           // [RC][KP]
-  float* hs = wsm + RC * KP;           // [TM][R]
+  float* xs = sm;                      // [TM_][KP]
+  float* wsm = xs + TM_ * KP;          // [RC][KP]
+  float* hs = wsm + RC * KP;           // [TM_][R]
   const int tid = threadIdx.x, lane = tid & 31, ty = tid >> 5;
-  // GEMM1 thread tile: warps 2 (rows) x 4 (hidden columns), lanes 4 x 8; thread (i, j) holds
-  // row 16*rg + lr + 4i and column 32*cg + lc + 8j.  The lanes of a warp instruction then read
-  // 4 distinct x vectors and 8 distinct weight vectors, each set in distinct banks: 8
-  // shared-memory wavefronts per 64 FMAs.
-  const int rg = ty >> 2, cg = ty & 3, lr = lane >> 3, lc = lane & 7;
-  const int row0 = 16 * rg + lr, col0 = 32 * cg + lc;
-  const int64_t t0 = (int64_t)blockIdx.x * TM;
+  const int rg = ty / CG, cg = ty % CG, lr = lane >> 3, lc = lane & 7;
+  const int row0 = 16 * rg + lr, col0 = CW * cg + lc;
+  const int64_t t0 = (int64_t)blockIdx.x * TM_;
   grid_launch_dependents();
   grid_dependency_wait();      // x may come from the previous kernel of the stream
   // vector staging needs rows that start on a 4-element boundary
   const bool vec = (d % 4 == 0) && ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(wa)) % 16 == 0);
 
   for (int rc = 0; rc < R; rc += RC) {
-    float acc[4][4];
+    float acc[4][CPT];
 #pragma unroll
     for (int i = 0; i < 4; ++i)
 #pragma unroll
-      for (int j = 0; j < 4; ++j) acc[i][j] = 0.f;
+      for (int j = 0; j < CPT; ++j) acc[i][j] = 0.f;
     // Vector path: one 4-element vector per thread and pass (row = tid / 8 (+32 per pass),
     // k = 4*(tid%8)).  The vectors of k-chunk kc+1 are loaded into registers before the
     // products of chunk kc start, so the load latency hides behind the arithmetic.
@@ -82,7 +83,7 @@ router_mask_simt_kernel(const T* __restrict__ x, const T* __restrict__ wa,
     float4 px = z, pw[RC / 32];
     auto prefetch = [&](int kc) {
       const int64_t t = t0 + vr;
-      px = (t < N && kc + vk < d) ? load4(x + t * d + kc + vk) : z;
+      px = (vr < TM_ && t < N && kc + vk < d) ? load4(x + t * d + kc + vk) : z;
 #pragma unroll
       for (int j = 0; j < RC / 32; ++j) {
         const int c = vr + 32 * j;
@@ -93,13 +94,13 @@ router_mask_simt_kernel(const T* __restrict__ x, const T* __restrict__ wa,
     for (int kc = 0; kc < d; kc += KC) {
       __syncthreads();
       if (vec) {
-        *reinterpret_cast<float4*>(&xs[vr * KP + vk]) = px;
+        if (vr < TM_) *reinterpret_cast<float4*>(&xs[vr * KP + vk]) = px;
 #pragma unroll
         for (int j = 0; j < RC / 32; ++j)
           *reinterpret_cast<float4*>(&wsm[(vr + 32 * j) * KP + vk]) = pw[j];
         if (kc + KC < d) prefetch(kc + KC);
       } else {
-        for (int i = tid; i < TM * KC; i += NT) {
+        for (int i = tid; i < TM_ * KC; i += NT) {
           const int r = i / KC, k = i % KC;
           const int64_t t = t0 + r;
           xs[r * KP + k] = (t < N && kc + k < d) ? DT<T>::to_f(x[t * d + kc + k]) : 0.f;
@@ -111,30 +112,41 @@ router_mask_simt_kernel(const T* __restrict__ x, const T* __restrict__ wa,
         }
       }
       __syncthreads();
-#pragma unroll
-      for (int k4 = 0; k4 < KC; k4 += 4) {
-        float4 xa[4], wv[4];
-#pragma unroll
-        for (int i = 0; i < 4; ++i)
-          xa[i] = *reinterpret_cast<const float4*>(&xs[(row0 + 4 * i) * KP + k4]);
-#pragma unroll
-        for (int j = 0; j < 4; ++j)
-          wv[j] = *reinterpret_cast<const float4*>(&wsm[(col0 + 8 * j) * KP + k4]);
+      // Two register sets of operand vectors: the loads of k-group g+1 are issued before the
+      // FMAs of group g (8 warps per SM do not hide the shared-memory latency otherwise).
+      float4 xa[2][4], wv[2][CPT];
+      auto load_set = [&](int k4, int b) {
 #pragma unroll
         for (int i = 0; i < 4; ++i)
+          xa[b][i] = *reinterpret_cast<const float4*>(&xs[(row0 + 4 * i) * KP + k4]);
 #pragma unroll
-          for (int j = 0; j < 4; ++j) {
-            acc[i][j] = fmaf(xa[i].x, wv[j].x, acc[i][j]);
-            acc[i][j] = fmaf(xa[i].y, wv[j].y, acc[i][j]);
-            acc[i][j] = fmaf(xa[i].z, wv[j].z, acc[i][j]);
-            acc[i][j] = fmaf(xa[i].w, wv[j].w, acc[i][j]);
+        for (int j = 0; j < CPT; ++j)
+          wv[b][j] = *reinterpret_cast<const float4*>(&wsm[(col0 + 8 * j) * KP + k4]);
+      };
+      auto fma_set = [&](int b) {
+#pragma unroll
+        for (int i = 0; i < 4; ++i)
+#pragma unroll
+          for (int j = 0; j < CPT; ++j) {
+            acc[i][j] = fmaf(xa[b][i].x, wv[b][j].x, acc[i][j]);
+            acc[i][j] = fmaf(xa[b][i].y, wv[b][j].y, acc[i][j]);
+            acc[i][j] = fmaf(xa[b][i].z, wv[b][j].z, acc[i][j]);
+            acc[i][j] = fmaf(xa[b][i].w, wv[b][j].w, acc[i][j]);
           }
+      };
+      load_set(0, 0);
+#pragma unroll
+      for (int k4 = 0; k4 < KC; k4 += 8) {
+        load_set(k4 + 4, 1);
+        fma_set(0);
+        if (k4 + 8 < KC) load_set(k4 + 8, 0);
+        fma_set(1);
       }
     }
 #pragma unroll
     for (int i = 0; i < 4; ++i)
 #pragma unroll
-      for (int j = 0; j < 4; ++j) {
+      for (int j = 0; j < CPT; ++j) {
         const int c = rc + col0 + 8 * j;
         if (c < R) hs[(row0 + 4 * i) * R + c] = fmaxf(DT<T>::round(acc[i][j]), 0.f);
       }
@@ -150,32 +162,30 @@ router_mask_simt_kernel(const T* __restrict__ x, const T* __restrict__ wa,
     __syncthreads();
   }
 
-  // scores + gate: warp ty owns rows 4ty..4ty+3, lane owns experts lane+32j
+  // scores + gate: warp ty owns rows RPW*ty .. RPW*ty + RPW - 1, lane owns experts lane + 32j
   const int nw = (E + 31) / 32;
-  float sc[4][8];   // [row][word]  (E <= 256)
+  float sc[RPW][8];   // [row][word]  (E <= 256)
   for (int j = 0; j < nw; ++j) {
     const int e = lane + 32 * j;
-    float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
+    float a[RPW];
+#pragma unroll
+    for (int i = 0; i < RPW; ++i) a[i] = 0.f;
     if (e < E) {
       const T* wrow = wb + (int64_t)e * R;
       const float* wsr = wsm + e * RP;
-      const float* h0 = hs + (4 * ty) * R;
+      const float* h0 = hs + (RPW * ty) * R;
       for (int k = 0; k < R; ++k) {
         const float w = wb_s ? wsr[k] : DT<T>::to_f(wrow[k]);
-        a0 = fmaf(h0[k], w, a0);
-        a1 = fmaf(h0[R + k], w, a1);
-        a2 = fmaf(h0[2 * R + k], w, a2);
-        a3 = fmaf(h0[3 * R + k], w, a3);
+#pragma unroll
+        for (int i = 0; i < RPW; ++i) a[i] = fmaf(h0[i * R + k], w, a[i]);
       }
     }
-    sc[0][j] = fabsf(DT<T>::round(a0));
-    sc[1][j] = fabsf(DT<T>::round(a1));
-    sc[2][j] = fabsf(DT<T>::round(a2));
-    sc[3][j] = fabsf(DT<T>::round(a3));
+#pragma unroll
+    for (int i = 0; i < RPW; ++i) sc[i][j] = fabsf(DT<T>::round(a[i]));
   }
 #pragma unroll
-  for (int i = 0; i < 4; ++i) {
-    const int64_t t = t0 + 4 * ty + i;
+  for (int i = 0; i < RPW; ++i) {
+    const int64_t t = t0 + RPW * ty + i;
     if (t >= N) break;   // warp-uniform
     if (scores)
       for (int j = 0; j < nw; ++j)
@@ -184,7 +194,7 @@ router_mask_simt_kernel(const T* __restrict__ x, const T* __restrict__ wa,
   }
 
   if (out_init) {
-    const int rows = (int)min((int64_t)TM, N - t0);
+    const int rows = (int)min((int64_t)TM_, N - t0);
     for (int c = tid; c < d; c += NT) {          // thread = column, rows inside
       const float lb = last_bias ? DT<T>::round(DT<T>::to_f(last_bias[c])) : 0.f;
       for (int r = 0; r < rows; ++r) {
@@ -553,6 +563,23 @@ inline int grid_for(int64_t work, int per_block, int cap) {
   return (int)g;
 }
 
+template <typename T, int TM_>
+int launch_router_simt_t(const void* x, const void* wa, const void* wb, float mult,
+                         uint32_t* mask_bits, void* scores, const void* last_bias,
+                         int add_residual, void* out_init, int64_t N, int d, int R, int E,
+                         cudaStream_t s, void* rt_out) {
+  const size_t smem = sizeof(float) * ((size_t)TM_ * KP + (size_t)RC * KP + (size_t)TM_ * R);
+  const int64_t grid = ceil_div64(N, TM_);
+  if (grid > 0x7fffffffLL) return D2D_ERR_UNSUPPORTED;
+  auto k = router_mask_simt_kernel<T, TM_>;
+  if (cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) !=
+      cudaSuccess)
+    return D2D_ERR_LAUNCH;
+  return launch_pdl(k, dim3((unsigned)grid), dim3(NT), smem, s, (const T*)x, (const T*)wa,
+                    (const T*)wb, mult, mask_bits, (T*)scores, (const T*)last_bias, add_residual,
+                    (T*)out_init, N, d, R, E, (T*)rt_out);
+}
+
 }  // namespace
 
 int launch_router_mask_simt(const void* x, const void* wa, const void* wb, float mult,
@@ -561,26 +588,14 @@ int launch_router_mask_simt(const void* x, const void* wa, const void* wb, float
                             int dtype, int* dev_status, cudaStream_t s, void* rt_out) {
   (void)dev_status;
   if (E > 256 || R > 1024) return D2D_ERR_UNSUPPORTED;
-  const size_t smem = sizeof(float) * ((size_t)TM * KP + (size_t)RC * KP + (size_t)TM * R);
-  const int64_t grid = ceil_div64(N, TM);
-  if (grid > 0x7fffffffLL) return D2D_ERR_UNSUPPORTED;
-  cudaError_t err;
-  if (dtype == D2D_F32) {
-    err = cudaFuncSetAttribute(router_mask_simt_kernel<float>,
-                               cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    if (err != cudaSuccess) return D2D_ERR_LAUNCH;
-    return launch_pdl(router_mask_simt_kernel<float>, dim3((unsigned)grid), dim3(NT), smem, s,
-        (const float*)x, (const float*)wa, (const float*)wb, mult, mask_bits, (float*)scores,
-        (const float*)last_bias, add_residual, (float*)out_init, N, d, R, E, (float*)rt_out);
-  } else {
-    err = cudaFuncSetAttribute(router_mask_simt_kernel<bf16>,
-                               cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    if (err != cudaSuccess) return D2D_ERR_LAUNCH;
-    return launch_pdl(router_mask_simt_kernel<bf16>, dim3((unsigned)grid), dim3(NT), smem, s,
-        (const bf16*)x, (const bf16*)wa, (const bf16*)wb, mult, mask_bits, (bf16*)scores,
-        (const bf16*)last_bias, add_residual, (bf16*)out_init, N, d, R, E, (bf16*)rt_out);
-  }
-  return cudaGetLastError() == cudaSuccess ? D2D_OK : D2D_ERR_LAUNCH;
+  // 16-token tiles while 32-token tiles would not give every SM of a B200 a tile
+  const bool small = ceil_div64(N, 32) < 148;
+#define D2D_ROUTER_SIMT(T_, TM_)                                                                \
+  launch_router_simt_t<T_, TM_>(x, wa, wb, mult, mask_bits, scores, last_bias, add_residual,   \
+                                out_init, N, d, R, E, s, rt_out)
+  if (dtype == D2D_F32) return small ? D2D_ROUTER_SIMT(float, 16) : D2D_ROUTER_SIMT(float, 32);
+  return small ? D2D_ROUTER_SIMT(bf16, 16) : D2D_ROUTER_SIMT(bf16, 32);
+#undef D2D_ROUTER_SIMT
 }
 
 int launch_mask_from_scores(const void* scores, float mult, uint32_t* mask_bits, int64_t N, int E,
