@@ -75,6 +75,7 @@ struct Geo {
   int nb2;       // ring B2 stages (W2 pieces, consumed by the GEMM2 warp)
   int na;        // ring A stages
   int stg;       // 16 KB slots of epilogue staging (experts: 2 = 32 rows x 128 B per warp)
+  int hsl;       // 16 KB slots of the hidden tile in shared memory (0: it is kept in tensor memory)
   long long w1_bytes, bias_off, stride;   // packed layout per expert
 };
 
@@ -118,9 +119,11 @@ Geo experts_geo(int d, int H, bool glu) {
   g.nd = (d % 128 == 0) ? 128 : 64;
   g.nc = d / g.nd;
   g.stg = 2;                       // 8 epilogue warps x 4 KB
+  // ungated experts keep the hidden tile in tensor memory (in place over accumulator 1)
+  g.hsl = glu ? g.kc2 : 0;
   g.na = 4;
   g.nb = glu ? 4 : 3;
-  g.nb2 = min(NB_MAX, SLOTS_TOTAL - g.na - g.nb - g.kc2 - g.stg);
+  g.nb2 = min(NB_MAX, SLOTS_TOTAL - g.na - g.nb - g.hsl - g.stg);
   g.w1_bytes = (long long)g.kc1 * g.nsub * g.nsubw * 128;
   g.bias_off = g.w1_bytes + (long long)g.nc * g.kc2 * g.nd * 128;
   g.stride = (g.bias_off + 512 + 1023) / 1024 * 1024;
@@ -137,9 +140,10 @@ Geo router_geo(int d, int R, int E) {
   g.nd = (E + 15) / 16 * 16;
   g.nc = 1;
   g.stg = 1;                       // one slot holds the last_bias row for the TMA row stores
+  g.hsl = g.kc2;
   g.na = g.kc2 > 2 ? 4 : 5;
   g.nb = 4;
-  g.nb2 = min(NB_MAX, SLOTS_TOTAL - g.na - g.nb - g.kc2 - g.stg);
+  g.nb2 = min(NB_MAX, SLOTS_TOTAL - g.na - g.nb - g.hsl - g.stg);
   g.w1_bytes = (long long)g.kc1 * g.nsub * g.nsubw * 128;
   g.bias_off = g.w1_bytes + (long long)g.nc * g.kc2 * g.nd * 128;
   g.stride = (g.bias_off + 512 + 1023) / 1024 * 1024;
@@ -205,6 +209,12 @@ __device__ __forceinline__ Tile tile_info(const Params& p, const Ctl* c, int til
 // buffered and GEMM1 of the next tile is issued before GEMM2 of the current one, so the
 // tensor pipe works while the epilogue warps turn acc1 into the hidden tile.
 __device__ __forceinline__ bool lookahead(const Geo& g) { return g.nsub == 1; }
+
+// Ungated expert form: epilogue 1 writes the bf16 hidden tile back into tensor memory, in
+// place over the accumulator-1 buffer it has just read (two bf16 per column: 64 columns for
+// 128 hidden units), and GEMM2 takes its A operand from there.  Nothing of the hidden tile
+// passes through shared memory, and the accumulator buffer is released by GEMM2's commit.
+__device__ __forceinline__ bool hidden_in_tmem(const Geo& g) { return g.hsl == 0; }
 
 // ---------------------------------------------------------------------------
 // roles
@@ -439,10 +449,12 @@ __device__ void role_mma2(const Params& p, Ctl* c, uint32_t ringB2, uint32_t hs,
   const uint32_t fullB2 = smem_u32(c->fullB2), emptyB2 = smem_u32(c->emptyB2);
   const uint32_t nb2 = g.nb2;
   const int nc = g.nc, kc2 = g.kc2, total = c->total_tiles;
+  const bool ht = hidden_in_tmem(g);
   uint32_t s = 0, ph = 0, accbits = 0, i = 0;
   for (int tile = blockIdx.x; tile < total; tile += gridDim.x, ++i) {
     if (!mbar_wait_fast(smem_u32(&c->hs_full), i & 1, af, p.dev_status)) return;
     tc_fence_after();
+    const uint32_t hbuf = tmem + (i & 1) * 128;      // hidden tile of this tile (tensor memory)
     for (int nci = 0; nci < nc; ++nci) {
       const uint32_t buf = nci & 1;
       const uint32_t acc = tmem + 256 + buf * 128;
@@ -459,9 +471,14 @@ __device__ void role_mma2(const Params& p, Ctl* c, uint32_t ringB2, uint32_t hs,
         const int ksteps = min(4, (g.K2 - k2 * 64) >> 4);
 #pragma unroll
         for (int k = 0; k < 4; ++k)
-          if (k < ksteps)
-            umma_bf16(acc, ((uint64_t)hi << 32) | (hlo + 2 * k), ((uint64_t)hi << 32) | (blo + 2 * k),
-                      idesc2, (k2 | k) != 0);
+          if (k < ksteps) {
+            if (ht)
+              umma_bf16_ta(acc, hbuf + k2 * 32 + k * 8, ((uint64_t)hi << 32) | (blo + 2 * k), idesc2,
+                           (k2 | k) != 0);
+            else
+              umma_bf16(acc, ((uint64_t)hi << 32) | (hlo + 2 * k),
+                        ((uint64_t)hi << 32) | (blo + 2 * k), idesc2, (k2 | k) != 0);
+          }
         umma_commit(emptyB2 + 8 * s);
         if (++s == nb2) {
           s = 0;
@@ -470,7 +487,10 @@ __device__ void role_mma2(const Params& p, Ctl* c, uint32_t ringB2, uint32_t hs,
       }
       umma_commit(smem_u32(&c->acc2_full[buf]));
     }
-    umma_commit(smem_u32(&c->hs_empty));
+    if (ht)
+      umma_commit(smem_u32(&c->acc1_empty[i & 1]));   // hidden tile read: GEMM1 may reuse the buffer
+    else
+      umma_commit(smem_u32(&c->hs_empty));
   }
 }
 
@@ -722,7 +742,8 @@ __device__ void role_ep1_experts(const Params& p, Ctl* c, uint32_t hs, uint32_t 
     if (!mbar_wait_fast(smem_u32(&c->acc1_full[b1]), la ? ((i >> 1) & 1) : (i & 1), af,
                         p.dev_status))
       return;
-    if (!mbar_wait_fast(smem_u32(&c->hs_empty), (i & 1) ^ 1, af, p.dev_status)) return;
+    const bool ht = hidden_in_tmem(g);
+    if (!ht && !mbar_wait_fast(smem_u32(&c->hs_empty), (i & 1) ^ 1, af, p.dev_status)) return;
     tc_fence_after();
     for (int c0 = 0; c0 < g.nsubw; c0 += 16) {
       uint32_t v[16], u[16], w[8], bb[8];
@@ -740,14 +761,24 @@ __device__ void role_ep1_experts(const Params& p, Ctl* c, uint32_t hs, uint32_t 
         case D2D_LEAKY_RELU: ep1_pairs<D2D_LEAKY_RELU>(v, u, bb, p.glu != 0, w, nacc, nord); break;
         default: ep1_pairs<D2D_GELU_TANH>(v, u, bb, p.glu != 0, w, nacc, nord); break;
       }
-      const uint32_t base = hs_row + (c0 >> 6) * SLOT;
-      const int j0 = (c0 & 63) >> 3;
-      st_shared_v4(base + (((j0) ^ (r & 7)) << 4), w[0], w[1], w[2], w[3]);
-      st_shared_v4(base + (((j0 + 1) ^ (r & 7)) << 4), w[4], w[5], w[6], w[7]);
+      if (ht) {
+        // in place: columns [c0/2, c0/2 + 8) lie inside the blocks this thread has read
+        tmem_st8(acc1 + (c0 >> 1), w);
+      } else {
+        const uint32_t base = hs_row + (c0 >> 6) * SLOT;
+        const int j0 = (c0 & 63) >> 3;
+        st_shared_v4(base + (((j0) ^ (r & 7)) << 4), w[0], w[1], w[2], w[3]);
+        st_shared_v4(base + (((j0 + 1) ^ (r & 7)) << 4), w[4], w[5], w[6], w[7]);
+      }
     }
-    tc_fence_before();
-    mbar_arrive(smem_u32(&c->acc1_empty[b1]));     // acc1 buffer read completely
-    fence_proxy_async();     // ordinary shared stores -> visible to the MMA's async reads
+    if (ht) {
+      tmem_wait_st();
+      tc_fence_before();
+    } else {
+      tc_fence_before();
+      mbar_arrive(smem_u32(&c->acc1_empty[b1]));     // acc1 buffer read completely
+      fence_proxy_async();     // ordinary shared stores -> visible to the MMA's async reads
+    }
     mbar_arrive(smem_u32(&c->hs_full));
     if (ntok >= 0 && ntok < p.N)
       p.norms[(long long)t.e * p.N + ntok] = __float2bfloat16_rn(nord == 1 ? nacc : sqrtf(nacc));
@@ -891,9 +922,9 @@ mlp_tiles_kernel(const Params p, const __grid_constant__ CUtensorMap tmx) {
   const uint32_t ringB = ringA + p.g.na * SLOT;
   const uint32_t ringB2 = ringB + p.g.nb * SLOT;
   const uint32_t hs = ringB2 + p.g.nb2 * SLOT;
-  const uint32_t stg = hs + p.g.kc2 * SLOT;
+  const uint32_t stg = hs + p.g.hsl * SLOT;
   Ctl* c = reinterpret_cast<Ctl*>(
-      aligned + (size_t)(p.g.na + p.g.nb + p.g.nb2 + p.g.kc2 + p.g.stg) * SLOT);
+      aligned + (size_t)(p.g.na + p.g.nb + p.g.nb2 + p.g.hsl + p.g.stg) * SLOT);
   const int tid = threadIdx.x, warp = tid >> 5;
   // Programmatic dependent launch: the next kernel of the stream may be scheduled as soon as
   // every CTA of this one has passed this point (its CTAs still wait for this grid to
@@ -918,7 +949,10 @@ mlp_tiles_kernel(const Params p, const __grid_constant__ CUtensorMap tmx) {
     mbar_init(smem_u32(&c->hs_empty), 1);
     for (int i = 0; i < 2; ++i) {
       mbar_init(smem_u32(&c->acc1_full[i]), 1);
-      mbar_init(smem_u32(&c->acc1_empty[i]), EP1_THREADS);
+      // released by epilogue 1 (all its threads), or by GEMM2's commit when the hidden tile
+      // stays in the accumulator's columns
+      mbar_init(smem_u32(&c->acc1_empty[i]),
+                (MODE == MODE_EXPERTS && hidden_in_tmem(p.g)) ? 1 : EP1_THREADS);
       mbar_init(smem_u32(&c->acc2_full[i]), 1);
       mbar_init(smem_u32(&c->acc2_empty[i]), 128);
       for (int q = 0; q < 4; ++q) {
@@ -1111,7 +1145,7 @@ static_assert(1024 + (size_t)SLOTS_TOTAL * SLOT + sizeof(Ctl) + 64 <= 232448,
               "shared-memory plan exceeds the 227 KB a CTA may use");
 
 size_t smem_bytes(const Geo& g) {
-  return 1024 + (size_t)(g.na + g.nb + g.nb2 + g.kc2 + g.stg) * SLOT + sizeof(Ctl) + 64;
+  return 1024 + (size_t)(g.na + g.nb + g.nb2 + g.hsl + g.stg) * SLOT + sizeof(Ctl) + 64;
 }
 
 template <int MODE>
