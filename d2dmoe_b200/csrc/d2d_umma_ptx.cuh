@@ -168,6 +168,41 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t* v) {
       : "r"(taddr)
       : "memory");
 }
+// 16 lanes x 64 columns in the accumulator-fragment layout: registers 4n..4n+3 hold column
+// block n (8 columns): v[4n], v[4n+1] = row lane/4, columns 8n + 2*(lane%4) + {0, 1};
+// v[4n+2], v[4n+3] = row lane/4 + 8, same columns.  The four lanes of a quad hold one row.
+__device__ __forceinline__ void tmem_ld_16x256b_x8(uint32_t taddr, uint32_t* v) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.16x256b.x8.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]),
+        "=r"(v[7]), "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]),
+        "=r"(v[14]), "=r"(v[15]), "=r"(v[16]), "=r"(v[17]), "=r"(v[18]), "=r"(v[19]),
+        "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]), "=r"(v[24]), "=r"(v[25]),
+        "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
+      : "r"(taddr)
+      : "memory");
+}
+// 4 x 4 transpose inside a quad of lanes (m = lane % 4): lane m gives w[n] (its two columns of
+// column block n) and receives t[j] = lane j's w[m]: the eight consecutive columns of block m.
+__device__ __forceinline__ void quad_transpose(const uint32_t* w, int m, uint32_t* t) {
+  const bool hi2 = (m & 2) != 0, hi1 = (m & 1) != 0;
+  // with lane m ^ 2: blocks {0,1} gather in lanes 0,1 and blocks {2,3} in lanes 2,3
+  const uint32_t x0 = __shfl_xor_sync(0xffffffffu, hi2 ? w[0] : w[2], 2);
+  const uint32_t x1 = __shfl_xor_sync(0xffffffffu, hi2 ? w[1] : w[3], 2);
+  // a[k]: block (m & 2) + k from the lower lane of the pair, b[k]: from the upper lane
+  const uint32_t a0 = hi2 ? x0 : w[0], a1 = hi2 ? x1 : w[1];
+  const uint32_t b0 = hi2 ? w[2] : x0, b1 = hi2 ? w[3] : x1;
+  // with lane m ^ 1: each lane keeps block m and passes the other one on
+  const uint32_t y0 = __shfl_xor_sync(0xffffffffu, hi1 ? a0 : a1, 1);
+  const uint32_t y1 = __shfl_xor_sync(0xffffffffu, hi1 ? b0 : b1, 1);
+  const uint32_t ka = hi1 ? a1 : a0, kb = hi1 ? b1 : b0;
+  t[0] = hi1 ? y0 : ka;
+  t[1] = hi1 ? ka : y0;
+  t[2] = hi1 ? y1 : kb;
+  t[3] = hi1 ? kb : y1;
+}
 __device__ __forceinline__ uint4 ld_shared_v4(uint32_t addr) {
   uint4 r;
   asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];"
