@@ -109,11 +109,12 @@ struct Params {
   uint32_t wait_limit;      // polls per bounded wait
   int withhold;             // test hook: CTA 0 never loads its first weight tile
   int tma_gather;           // experts: rows by TMA tile::gather4 instead of cp.async
+  int out_tma;              // experts: output adds by TMA bulk reduce from staged rows
   bf16* norms;              // experts, optional: [E, N] norms of each computed pair's activations
   int norm_layer, norm_ord; // D2D_NORM_OF_INTERMEDIATE / D2D_NORM_OF_OUTPUT (0: none); 1 or 2
 };
 
-Geo experts_geo(int d, int H, bool glu) {
+Geo experts_geo(int d, int H, bool glu, bool out_tma = false) {
   Geo g;
   g.kc1 = d / 64;
   g.nsub = glu ? 2 : 1;
@@ -122,11 +123,13 @@ Geo experts_geo(int d, int H, bool glu) {
   g.kc2 = (H + 63) / 64;
   g.nd = (d % 128 == 0) ? 128 : 64;
   g.nc = d / g.nd;
-  g.stg = 0;                       // the output rows are added straight from registers
+  // output rows: added straight from registers, or (selectable) staged as 128 rows x (256 + 16)
+  // bytes per chunk, two chunks, and added by TMA bulk reduces
+  g.stg = out_tma ? 5 : 0;
   // ungated experts keep the hidden tile in tensor memory (in place over accumulator 1)
   g.hsl = glu ? g.kc2 : 0;
-  g.na = glu ? 4 : 5;
-  g.nb = 4;
+  g.na = out_tma ? 3 : (glu ? 4 : 5);
+  g.nb = out_tma ? 3 : 4;
   g.nb2 = min(NB_MAX, SLOTS_TOTAL - g.na - g.nb - g.hsl - g.stg);
   g.w1_bytes = (long long)g.kc1 * g.nsub * g.nsubw * 128;
   g.bias_off = g.w1_bytes + (long long)g.nc * g.kc2 * g.nd * 128;
@@ -880,6 +883,68 @@ __device__ void role_ep2_experts(const Params& p, Ctl* c, uint32_t tmem, int et)
   }
 }
 
+// Selectable form of epilogue 2: accumulator 2 -> bf16 -> this thread's row of a staging tile
+// (row pitch 256 + 16 bytes: conflict-free 16-byte stores) -> one TMA bulk reduce
+// (cp.reduce.async.bulk .add.noftz.bf16, 256 bytes) per row and chunk into out[token].  The adds
+// then leave the SM through the TMA unit instead of the load/store unit that also carries the
+// row gather.  Thread = tile row; two staging tiles alternate, reuse is ordered by the
+// issuing thread's own bulk groups.
+constexpr uint32_t OUT_PITCH = 272;
+__device__ void role_ep2_experts_tma(const Params& p, Ctl* c, uint32_t stg, uint32_t tmem, int et) {
+  volatile int* af = &c->abort_flag;
+  const Geo& g = p.g;
+  const uint32_t lane_base = (uint32_t)(et & ~31) << 16;
+  const int nord = p.norm_layer == D2D_NORM_OF_OUTPUT ? p.norm_ord : 0;
+  uint32_t phbits = 0, nrun = 0;
+  for (int tile = blockIdx.x; tile < c->total_tiles; tile += gridDim.x) {
+    const Tile t = tile_info<MODE_EXPERTS>(p, c, tile);
+    long long tok = et < t.nrows ? (long long)p.token_idx[t.r0 + et] : -1;
+    if (tok >= p.N) tok = -1;          // out-of-range indices are reported by the producer
+    bf16* orow = tok < 0 ? nullptr : p.out + tok * p.d;
+    float nacc = 0.f;
+    for (int nci = 0; nci < g.nc; ++nci) {
+      const uint32_t buf = nci & 1;
+      if (!mbar_wait_fast(smem_u32(&c->acc2_full[buf]), (phbits >> buf) & 1, af, p.dev_status))
+        return;
+      phbits ^= 1u << buf;
+      tc_fence_after();
+      bulk_wait_read_1();              // the reduce that last read this staging tile is done with it
+      const uint32_t row = stg + (nrun++ & 1) * (TILE_M * OUT_PITCH) + et * OUT_PITCH;
+      for (int hf = 0; hf < 2; ++hf) {
+        uint32_t v[64];
+        tmem_ld32(tmem + lane_base + 256 + buf * 128 + hf * 64, v);
+        tmem_ld32(tmem + lane_base + 256 + buf * 128 + hf * 64 + 32, v + 32);
+        tmem_wait_ld();
+        if (hf == 1) {                 // accumulator buffer read completely: hand it back
+          tc_fence_before();
+          mbar_arrive(smem_u32(&c->acc2_empty[buf]));
+        }
+#pragma unroll
+        for (int pc = 0; pc < 8; ++pc) {
+          uint32_t ww[4];
+#pragma unroll
+          for (int k = 0; k < 4; ++k)
+            ww[k] = pack_bf16x2(__uint_as_float(v[8 * pc + 2 * k]),
+                                __uint_as_float(v[8 * pc + 2 * k + 1]));
+          st_shared_v4(row + hf * 128 + pc * 16, ww[0], ww[1], ww[2], ww[3]);
+          if (nord != 0) {
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+              const float lo = __uint_as_float(ww[k] << 16), hi = __uint_as_float(ww[k] & 0xffff0000u);
+              nacc += nord == 1 ? fabsf(lo) + fabsf(hi) : fmaf(lo, lo, hi * hi);
+            }
+          }
+        }
+      }
+      fence_proxy_async();             // this thread's stores -> visible to its bulk reduce
+      if (orow) bulk_red_add_bf16(orow + nci * 128, row, 256);
+      bulk_commit();
+    }
+    if (nord != 0 && tok >= 0)
+      p.norms[(long long)t.e * p.N + tok] = __float2bfloat16_rn(nord == 1 ? nacc : sqrtf(nacc));
+  }
+}
+
 // ---------------------------------------------------------------------------
 // kernel
 // ---------------------------------------------------------------------------
@@ -988,7 +1053,12 @@ mlp_tiles_kernel(const Params p, const __grid_constant__ CUtensorMap tmx) {
   if (MODE == MODE_EXPERTS && warp < 4) {
     role_ep1_experts(p, c, hs, tmem, tid);
   } else if (MODE == MODE_EXPERTS && warp < 8) {
-    role_ep2_experts(p, c, tmem, tid - 128);
+    if (p.out_tma) {
+      role_ep2_experts_tma(p, c, stg, tmem, tid - 128);
+      bulk_wait_all();     // the reduces read shared memory: finish before the CTA ends
+    } else {
+      role_ep2_experts(p, c, tmem, tid - 128);
+    }
   } else if (warp < 8) {
     role_epilogue_router(p, c, hs, stg, tmem, tid);
     bulk_wait_all();       // TMA row stores read shared memory: finish before the CTA ends
@@ -1189,7 +1259,10 @@ int launch_experts_umma(const void* x, const int32_t* token_idx, const int32_t* 
   p.N = N;
   p.d = d;
   p.packed = (const uint8_t*)packed;
-  p.g = experts_geo(d, H, glu);
+  // selectable output path (test hook 3): only for the 128-column chunks of ungated experts
+  const bool out_tma = g_experts_kernel.load() == 3 && !glu && d % 128 == 0;
+  p.g = experts_geo(d, H, glu, out_tma);
+  p.out_tma = out_tma ? 1 : 0;
   p.token_idx = token_idx;
   p.offsets = offsets;
   p.E = E;
@@ -1206,7 +1279,7 @@ int launch_experts_umma(const void* x, const int32_t* token_idx, const int32_t* 
 }
 
 void umma_debug_select_experts_kernel(int which) {
-  g_experts_kernel.store(which == 2 ? 2 : 0);
+  g_experts_kernel.store(which == 2 || which == 3 ? which : 0);
 }
 
 void umma_debug_configure(int wait_limit_log2, int withhold_weight_tile) {

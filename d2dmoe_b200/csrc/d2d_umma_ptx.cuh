@@ -220,6 +220,19 @@ __device__ __forceinline__ void bulk_s2g(void* gdst, uint32_t ssrc, uint32_t byt
 __device__ __forceinline__ void bulk_commit() {
   asm volatile("cp.async.bulk.commit_group;" ::: "memory");
 }
+// TMA reduce-add of one contiguous run of bf16 from shared memory into global memory (the L2
+// does the adds); completion is tracked per issuing thread in bulk groups.
+__device__ __forceinline__ void bulk_red_add_bf16(void* gdst, uint32_t ssrc, uint32_t bytes) {
+  asm volatile(
+      "cp.reduce.async.bulk.global.shared::cta.bulk_group.add.noftz.bf16 [%0], [%1], %2;" ::"l"(
+          gdst),
+      "r"(ssrc), "r"(bytes)
+      : "memory");
+}
+// all but the newest bulk group of this thread have finished READING shared memory
+__device__ __forceinline__ void bulk_wait_read_1() {
+  asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
+}
 __device__ __forceinline__ void bulk_wait_all() {
   asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
 }
