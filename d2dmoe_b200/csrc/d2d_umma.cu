@@ -11,29 +11,25 @@
 //             bits (and, on request, as the 0/1 routing tensor); the same CTA writes the
 //             layer output's initial value and the compaction's counts table.
 //
-// Both are one persistent kernel (one CTA per SM, 480 threads; tile = 128 rows): GEMM1 (K = d)
-// into a double-buffered TMEM accumulator, an epilogue that turns it into the bf16 A operand of
-// GEMM2, GEMM2 (K = hidden width) per 128-column chunk into a second double-buffered TMEM
-// accumulator, and a second epilogue.
+// Both are one persistent kernel (one CTA per SM: 480 threads in the router form, 608 in
+// the experts form; tile = 128 rows): GEMM1 (K = d) into a double-buffered TMEM accumulator,
+// an epilogue that turns it into the bf16 A operand of GEMM2 in shared memory, GEMM2
+// (K = hidden width) per 128-column chunk into a second double-buffered TMEM accumulator,
+// and a second epilogue.
 //
 // Warp roles:
 //   experts form
-//     warps 0-3   epilogue 1: accumulator 1 -> + b1, activation (x up-projection) -> hidden tile.
-//                 Ungated experts: written back into TENSOR memory, in place over the
-//                 accumulator buffer just read; GEMM2 takes its A operand from there and its
-//                 commit releases the buffer.  Gated experts (accumulator 1 = gate | up, no
-//                 second buffer): hidden tile in shared memory.
-//     warps 4-7   accumulator 2 -> bf16 -> out[token] with red.global.add.noftz.v4.bf16x2
-//                 straight from registers: the accumulator is read in the fragment layout
-//                 (a quad of lanes = one row), a transpose inside the quad gives each lane 8
-//                 consecutive columns.  No shared-memory staging.
+//     warps 0-3   epilogue 1: accumulator 1 -> + b1, activation (x up-projection) -> hidden tile
+//     warps 4-7   accumulator 2 -> bf16 -> two alternating 4 KB staging blocks per warp
+//     warps 15-18 read the blocks back row-contiguous and add them to out[token] with
+//                 red.global.add.noftz.v4.bf16x2 (4 cache lines per instruction)
 //     warps 11-14 gather the tile's token rows of x with 16-byte cp.async into ring A in the
 //                 128-byte-swizzled K-major layout the MMA descriptors expect; stage barriers
 //                 are signalled by cp.async.mbarrier.arrive.  (Selectable instead: warp 11
 //                 gathers them with TMA tile::gather4 copies, four rows per copy.)
 //   router form
-//     warps 0-7   two epilogue groups of four: epilogue 1 (ReLU hidden tile, shared memory), then
-//                 group 0: |.|, row max, threshold, mask word, the row of the 0/1 routing tensor,
+//     warps 0-7   two epilogue groups of four: epilogue 1 (ReLU hidden tile), then group 0:
+//                 |.|, row max, threshold, mask word, the row of the 0/1 routing tensor,
 //                 per-tile expert counts for the compaction; warp 7 issues the output's
 //                 initial rows as TMA row stores
 //     warp 11     one lane issues one tiled TMA box (128 rows x 64 columns of x) per stage
@@ -62,8 +58,8 @@ constexpr int NA_MAX = 6;            // ring A stages (upper bound)
 constexpr int NB_MAX = 6;            // ring B stages (upper bound)
 constexpr int SLOTS_TOTAL = 14;      // ring A + ring B + hidden tile + staging (224 KB)
 constexpr int NTHREADS = 480;            // router form
-constexpr int NTHREADS_EXPERTS = 480;    // same warp count; four of the warps gather rows
-constexpr int WARP_MMA1 = 8, WARP_MMA2 = 9, WARP_BULK = 10, WARP_PROD0 = 11, WARP_END = 15;
+constexpr int NTHREADS_EXPERTS = 608;    // + four warps that write the output rows
+constexpr int WARP_MMA1 = 8, WARP_MMA2 = 9, WARP_BULK = 10, WARP_PROD0 = 11, WARP_WR0 = 15;
 constexpr int MAX_E = 128;
 constexpr int MODE_EXPERTS = 0, MODE_ROUTER = 1;
 
@@ -78,8 +74,7 @@ struct Geo {
   int nb;        // ring B1 stages (W1 tiles, consumed by the GEMM1 warp)
   int nb2;       // ring B2 stages (W2 pieces, consumed by the GEMM2 warp)
   int na;        // ring A stages
-  int stg;       // 16 KB slots of epilogue staging (router: the last_bias row for its row stores)
-  int hsl;       // 16 KB slots of the hidden tile in shared memory (0: it is kept in tensor memory)
+  int stg;       // 16 KB slots of epilogue staging (experts: 2 = 32 rows x 128 B per warp)
   long long w1_bytes, bias_off, stride;   // packed layout per expert
 };
 
@@ -109,12 +104,11 @@ struct Params {
   uint32_t wait_limit;      // polls per bounded wait
   int withhold;             // test hook: CTA 0 never loads its first weight tile
   int tma_gather;           // experts: rows by TMA tile::gather4 instead of cp.async
-  int out_tma;              // experts: output adds by TMA bulk reduce from staged rows
   bf16* norms;              // experts, optional: [E, N] norms of each computed pair's activations
   int norm_layer, norm_ord; // D2D_NORM_OF_INTERMEDIATE / D2D_NORM_OF_OUTPUT (0: none); 1 or 2
 };
 
-Geo experts_geo(int d, int H, bool glu, bool out_tma = false) {
+Geo experts_geo(int d, int H, bool glu) {
   Geo g;
   g.kc1 = d / 64;
   g.nsub = glu ? 2 : 1;
@@ -123,14 +117,10 @@ Geo experts_geo(int d, int H, bool glu, bool out_tma = false) {
   g.kc2 = (H + 63) / 64;
   g.nd = (d % 128 == 0) ? 128 : 64;
   g.nc = d / g.nd;
-  // output rows: added straight from registers, or (selectable) staged as 128 rows x (256 + 16)
-  // bytes per chunk, two chunks, and added by TMA bulk reduces
-  g.stg = out_tma ? 5 : 0;
-  // ungated experts keep the hidden tile in tensor memory (in place over accumulator 1)
-  g.hsl = glu ? g.kc2 : 0;
-  g.na = out_tma ? 3 : (glu ? 4 : 5);
-  g.nb = out_tma ? 3 : 4;
-  g.nb2 = min(NB_MAX, SLOTS_TOTAL - g.na - g.nb - g.hsl - g.stg);
+  g.stg = 2;                       // 8 epilogue warps x 4 KB
+  g.na = 4;
+  g.nb = glu ? 4 : 3;
+  g.nb2 = min(NB_MAX, SLOTS_TOTAL - g.na - g.nb - g.kc2 - g.stg);
   g.w1_bytes = (long long)g.kc1 * g.nsub * g.nsubw * 128;
   g.bias_off = g.w1_bytes + (long long)g.nc * g.kc2 * g.nd * 128;
   g.stride = (g.bias_off + 512 + 1023) / 1024 * 1024;
@@ -147,10 +137,9 @@ Geo router_geo(int d, int R, int E) {
   g.nd = (E + 15) / 16 * 16;
   g.nc = 1;
   g.stg = 1;                       // one slot holds the last_bias row for the TMA row stores
-  g.hsl = g.kc2;
   g.na = g.kc2 > 2 ? 4 : 5;
   g.nb = 4;
-  g.nb2 = min(NB_MAX, SLOTS_TOTAL - g.na - g.nb - g.hsl - g.stg);
+  g.nb2 = min(NB_MAX, SLOTS_TOTAL - g.na - g.nb - g.kc2 - g.stg);
   g.w1_bytes = (long long)g.kc1 * g.nsub * g.nsubw * 128;
   g.bias_off = g.w1_bytes + (long long)g.nc * g.kc2 * g.nd * 128;
   g.stride = (g.bias_off + 512 + 1023) / 1024 * 1024;
@@ -164,6 +153,7 @@ struct Ctl {
   unsigned long long fullA[NA_MAX], emptyA[NA_MAX], fullB[NB_MAX], emptyB[NB_MAX];
   unsigned long long fullB2[NB_MAX], emptyB2[NB_MAX];
   unsigned long long acc1_full[2], acc1_empty[2], hs_full, hs_empty, acc2_full[2], acc2_empty[2];
+  unsigned long long sfull[2][4], sempty[2][4];   // staging unit of (epilogue group, row quarter)
   uint32_t tmem_base;
   int abort_flag;
   int wait_limit;                  // must follow abort_flag (mbar_wait reads abort_flag[1])
@@ -215,12 +205,6 @@ __device__ __forceinline__ Tile tile_info(const Params& p, const Ctl* c, int til
 // buffered and GEMM1 of the next tile is issued before GEMM2 of the current one, so the
 // tensor pipe works while the epilogue warps turn acc1 into the hidden tile.
 __device__ __forceinline__ bool lookahead(const Geo& g) { return g.nsub == 1; }
-
-// Ungated expert form: epilogue 1 writes the bf16 hidden tile back into tensor memory, in
-// place over the accumulator-1 buffer it has just read (two bf16 per column: 64 columns for
-// 128 hidden units), and GEMM2 takes its A operand from there.  Nothing of the hidden tile
-// passes through shared memory, and the accumulator buffer is released by GEMM2's commit.
-__device__ __forceinline__ bool hidden_in_tmem(const Geo& g) { return g.hsl == 0; }
 
 // ---------------------------------------------------------------------------
 // roles
@@ -455,12 +439,10 @@ __device__ void role_mma2(const Params& p, Ctl* c, uint32_t ringB2, uint32_t hs,
   const uint32_t fullB2 = smem_u32(c->fullB2), emptyB2 = smem_u32(c->emptyB2);
   const uint32_t nb2 = g.nb2;
   const int nc = g.nc, kc2 = g.kc2, total = c->total_tiles;
-  const bool ht = hidden_in_tmem(g);
   uint32_t s = 0, ph = 0, accbits = 0, i = 0;
   for (int tile = blockIdx.x; tile < total; tile += gridDim.x, ++i) {
     if (!mbar_wait_fast(smem_u32(&c->hs_full), i & 1, af, p.dev_status)) return;
     tc_fence_after();
-    const uint32_t hbuf = tmem + (i & 1) * 128;      // hidden tile of this tile (tensor memory)
     for (int nci = 0; nci < nc; ++nci) {
       const uint32_t buf = nci & 1;
       const uint32_t acc = tmem + 256 + buf * 128;
@@ -477,14 +459,9 @@ __device__ void role_mma2(const Params& p, Ctl* c, uint32_t ringB2, uint32_t hs,
         const int ksteps = min(4, (g.K2 - k2 * 64) >> 4);
 #pragma unroll
         for (int k = 0; k < 4; ++k)
-          if (k < ksteps) {
-            if (ht)
-              umma_bf16_ta(acc, hbuf + k2 * 32 + k * 8, ((uint64_t)hi << 32) | (blo + 2 * k), idesc2,
-                           (k2 | k) != 0);
-            else
-              umma_bf16(acc, ((uint64_t)hi << 32) | (hlo + 2 * k),
-                        ((uint64_t)hi << 32) | (blo + 2 * k), idesc2, (k2 | k) != 0);
-          }
+          if (k < ksteps)
+            umma_bf16(acc, ((uint64_t)hi << 32) | (hlo + 2 * k), ((uint64_t)hi << 32) | (blo + 2 * k),
+                      idesc2, (k2 | k) != 0);
         umma_commit(emptyB2 + 8 * s);
         if (++s == nb2) {
           s = 0;
@@ -493,10 +470,7 @@ __device__ void role_mma2(const Params& p, Ctl* c, uint32_t ringB2, uint32_t hs,
       }
       umma_commit(smem_u32(&c->acc2_full[buf]));
     }
-    if (ht)
-      umma_commit(smem_u32(&c->acc1_empty[i & 1]));   // hidden tile read: GEMM1 may reuse the buffer
-    else
-      umma_commit(smem_u32(&c->hs_empty));
+    umma_commit(smem_u32(&c->hs_empty));
   }
 }
 
@@ -748,8 +722,7 @@ __device__ void role_ep1_experts(const Params& p, Ctl* c, uint32_t hs, uint32_t 
     if (!mbar_wait_fast(smem_u32(&c->acc1_full[b1]), la ? ((i >> 1) & 1) : (i & 1), af,
                         p.dev_status))
       return;
-    const bool ht = hidden_in_tmem(g);
-    if (!ht && !mbar_wait_fast(smem_u32(&c->hs_empty), (i & 1) ^ 1, af, p.dev_status)) return;
+    if (!mbar_wait_fast(smem_u32(&c->hs_empty), (i & 1) ^ 1, af, p.dev_status)) return;
     tc_fence_after();
     for (int c0 = 0; c0 < g.nsubw; c0 += 16) {
       uint32_t v[16], u[16], w[8], bb[8];
@@ -767,158 +740,61 @@ __device__ void role_ep1_experts(const Params& p, Ctl* c, uint32_t hs, uint32_t 
         case D2D_LEAKY_RELU: ep1_pairs<D2D_LEAKY_RELU>(v, u, bb, p.glu != 0, w, nacc, nord); break;
         default: ep1_pairs<D2D_GELU_TANH>(v, u, bb, p.glu != 0, w, nacc, nord); break;
       }
-      if (ht) {
-        // in place: columns [c0/2, c0/2 + 8) lie inside the blocks this thread has read
-        tmem_st8(acc1 + (c0 >> 1), w);
-      } else {
-        const uint32_t base = hs_row + (c0 >> 6) * SLOT;
-        const int j0 = (c0 & 63) >> 3;
-        st_shared_v4(base + (((j0) ^ (r & 7)) << 4), w[0], w[1], w[2], w[3]);
-        st_shared_v4(base + (((j0 + 1) ^ (r & 7)) << 4), w[4], w[5], w[6], w[7]);
-      }
+      const uint32_t base = hs_row + (c0 >> 6) * SLOT;
+      const int j0 = (c0 & 63) >> 3;
+      st_shared_v4(base + (((j0) ^ (r & 7)) << 4), w[0], w[1], w[2], w[3]);
+      st_shared_v4(base + (((j0 + 1) ^ (r & 7)) << 4), w[4], w[5], w[6], w[7]);
     }
-    if (ht) {
-      tmem_wait_st();
-      tc_fence_before();
-    } else {
-      tc_fence_before();
-      mbar_arrive(smem_u32(&c->acc1_empty[b1]));     // acc1 buffer read completely
-      fence_proxy_async();     // ordinary shared stores -> visible to the MMA's async reads
-    }
+    tc_fence_before();
+    mbar_arrive(smem_u32(&c->acc1_empty[b1]));     // acc1 buffer read completely
+    fence_proxy_async();     // ordinary shared stores -> visible to the MMA's async reads
     mbar_arrive(smem_u32(&c->hs_full));
     if (ntok >= 0 && ntok < p.N)
       p.norms[(long long)t.e * p.N + ntok] = __float2bfloat16_rn(nord == 1 ? nacc : sqrtf(nacc));
   }
 }
 
-// Warps 4-7: accumulator 2 -> bf16 -> output rows, straight from registers.  The accumulator
-// is read in the fragment layout (tcgen05.ld 16x256b: the four lanes of a quad hold one row,
-// two columns each per 8-column block); a 4 x 4 transpose inside the quad gives every lane
-// eight consecutive bf16 columns = one 16-byte red, so a warp instruction adds 64-byte runs
-// of 8 rows.  No shared-memory staging and no hand-over to other warps: the shared-memory
-// pipe and the load/store unit carry only the row gather and these reds.
-// Warp q owns tile rows 32q..32q+31; a thread's rows are 32q + 16h + lane/4 + 8s.
-__device__ void role_ep2_experts(const Params& p, Ctl* c, uint32_t tmem, int et) {
+// Warps 4-7: accumulator 2 -> bf16 -> staging blocks.  Warp q owns two 32-row x 128-byte
+// blocks and fills them alternately; writer warp q adds them to the output rows.  This
+// role never touches global memory, so the accumulators are handed back to the GEMM2
+// warp as fast as the write path drains.
+__device__ void role_ep2_experts(const Params& p, Ctl* c, uint32_t stg, uint32_t tmem, int et) {
   volatile int* af = &c->abort_flag;
   const Geo& g = p.g;
   const int lane = et & 31, q = et >> 5;
-  const int m = lane & 3, rr = lane >> 2;
+  const uint32_t lane_base = (uint32_t)(et & ~31) << 16;
   const int halves = g.nd >> 6;
+  uint32_t phbits = 0, n = 0;
   const int nord = p.norm_layer == D2D_NORM_OF_OUTPUT ? p.norm_ord : 0;
-  uint32_t phbits = 0;
   for (int tile = blockIdx.x; tile < c->total_tiles; tile += gridDim.x) {
-    const Tile t = tile_info<MODE_EXPERTS>(p, c, tile);
-    bf16* orow[2][2];
-    long long tokr[2][2];
-    float nacc[2][2] = {{0.f, 0.f}, {0.f, 0.f}};
-#pragma unroll
-    for (int h = 0; h < 2; ++h)
-#pragma unroll
-      for (int s2 = 0; s2 < 2; ++s2) {
-        const int row = 32 * q + 16 * h + rr + 8 * s2;
-        long long tok = row < t.nrows ? (long long)p.token_idx[t.r0 + row] : -1;
-        if (tok >= p.N) tok = -1;      // out-of-range indices are reported by the producer
-        tokr[h][s2] = tok;
-        orow[h][s2] = tok < 0 ? nullptr : p.out + tok * p.d + 8 * m;
-      }
+    // labels by-product (output layer): thread = tile row; norm terms of the bf16 outputs
+    float nacc = 0.f;
+    int ntok = -1, ne = 0;
+    if (nord != 0) {
+      const Tile t = tile_info<MODE_EXPERTS>(p, c, tile);
+      ne = t.e;
+      if (et < t.nrows) ntok = p.token_idx[t.r0 + et];
+    }
     for (int nci = 0; nci < g.nc; ++nci) {
       const uint32_t buf = nci & 1;
       if (!mbar_wait_fast(smem_u32(&c->acc2_full[buf]), (phbits >> buf) & 1, af, p.dev_status))
         return;
       phbits ^= 1u << buf;
       tc_fence_after();
-      for (int hf = 0; hf < halves; ++hf) {
-        uint32_t v[2][32];
-#pragma unroll
-        for (int h = 0; h < 2; ++h)
-          tmem_ld_16x256b_x8(tmem + ((uint32_t)(32 * q + 16 * h) << 16) + 256 + buf * 128 + hf * 64,
-                             v[h]);
+      for (int hf = 0; hf < halves; ++hf, ++n) {
+        uint32_t v[64];
+        tmem_ld32(tmem + lane_base + 256 + buf * 128 + hf * 64, v);
+        tmem_ld32(tmem + lane_base + 256 + buf * 128 + hf * 64 + 32, v + 32);
         tmem_wait_ld();
         if (hf == halves - 1) {     // accumulator buffer read completely: hand it back
           tc_fence_before();
           mbar_arrive(smem_u32(&c->acc2_empty[buf]));
         }
-        const int col = nci * g.nd + hf * 64;
-#pragma unroll
-        for (int h = 0; h < 2; ++h)
-#pragma unroll
-          for (int g2 = 0; g2 < 2; ++g2) {       // 32 columns: four 8-column blocks
-            uint32_t wa[4], wb[4], ta[4], tb[4];
-#pragma unroll
-            for (int n = 0; n < 4; ++n) {
-              const int r0 = 16 * g2 + 4 * n;
-              wa[n] = pack_bf16x2(__uint_as_float(v[h][r0]), __uint_as_float(v[h][r0 + 1]));
-              wb[n] = pack_bf16x2(__uint_as_float(v[h][r0 + 2]), __uint_as_float(v[h][r0 + 3]));
-            }
-            if (nord != 0) {
-#pragma unroll
-              for (int n = 0; n < 4; ++n) {
-                const float al = __uint_as_float(wa[n] << 16), ah = __uint_as_float(wa[n] & 0xffff0000u);
-                const float bl = __uint_as_float(wb[n] << 16), bh = __uint_as_float(wb[n] & 0xffff0000u);
-                nacc[h][0] += nord == 1 ? fabsf(al) + fabsf(ah) : fmaf(al, al, ah * ah);
-                nacc[h][1] += nord == 1 ? fabsf(bl) + fabsf(bh) : fmaf(bl, bl, bh * bh);
-              }
-            }
-            quad_transpose(wa, m, ta);
-            quad_transpose(wb, m, tb);
-            if (orow[h][0]) red_add_bf16x8(orow[h][0] + col + 32 * g2, ta[0], ta[1], ta[2], ta[3]);
-            if (orow[h][1]) red_add_bf16x8(orow[h][1] + col + 32 * g2, tb[0], tb[1], tb[2], tb[3]);
-          }
-      }
-    }
-    if (nord != 0) {
-      // a row's columns are spread over its quad: reduce, lane 0 of the quad writes
-#pragma unroll
-      for (int h = 0; h < 2; ++h)
-#pragma unroll
-        for (int s2 = 0; s2 < 2; ++s2) {
-          float vsum = nacc[h][s2];
-          vsum += __shfl_xor_sync(0xffffffffu, vsum, 1);
-          vsum += __shfl_xor_sync(0xffffffffu, vsum, 2);
-          if (m == 0 && tokr[h][s2] >= 0)
-            p.norms[(long long)t.e * p.N + tokr[h][s2]] =
-                __float2bfloat16_rn(nord == 1 ? vsum : sqrtf(vsum));
-        }
-    }
-  }
-}
-
-// Selectable form of epilogue 2: accumulator 2 -> bf16 -> this thread's row of a staging tile
-// (row pitch 256 + 16 bytes: conflict-free 16-byte stores) -> one TMA bulk reduce
-// (cp.reduce.async.bulk .add.noftz.bf16, 256 bytes) per row and chunk into out[token].  The adds
-// then leave the SM through the TMA unit instead of the load/store unit that also carries the
-// row gather.  Thread = tile row; two staging tiles alternate, reuse is ordered by the
-// issuing thread's own bulk groups.
-constexpr uint32_t OUT_PITCH = 272;
-__device__ void role_ep2_experts_tma(const Params& p, Ctl* c, uint32_t stg, uint32_t tmem, int et) {
-  volatile int* af = &c->abort_flag;
-  const Geo& g = p.g;
-  const uint32_t lane_base = (uint32_t)(et & ~31) << 16;
-  const int nord = p.norm_layer == D2D_NORM_OF_OUTPUT ? p.norm_ord : 0;
-  uint32_t phbits = 0, nrun = 0;
-  for (int tile = blockIdx.x; tile < c->total_tiles; tile += gridDim.x) {
-    const Tile t = tile_info<MODE_EXPERTS>(p, c, tile);
-    long long tok = et < t.nrows ? (long long)p.token_idx[t.r0 + et] : -1;
-    if (tok >= p.N) tok = -1;          // out-of-range indices are reported by the producer
-    bf16* orow = tok < 0 ? nullptr : p.out + tok * p.d;
-    float nacc = 0.f;
-    for (int nci = 0; nci < g.nc; ++nci) {
-      const uint32_t buf = nci & 1;
-      if (!mbar_wait_fast(smem_u32(&c->acc2_full[buf]), (phbits >> buf) & 1, af, p.dev_status))
-        return;
-      phbits ^= 1u << buf;
-      tc_fence_after();
-      bulk_wait_read_1();              // the reduce that last read this staging tile is done with it
-      const uint32_t row = stg + (nrun++ & 1) * (TILE_M * OUT_PITCH) + et * OUT_PITCH;
-      for (int hf = 0; hf < 2; ++hf) {
-        uint32_t v[64];
-        tmem_ld32(tmem + lane_base + 256 + buf * 128 + hf * 64, v);
-        tmem_ld32(tmem + lane_base + 256 + buf * 128 + hf * 64 + 32, v + 32);
-        tmem_wait_ld();
-        if (hf == 1) {                 // accumulator buffer read completely: hand it back
-          tc_fence_before();
-          mbar_arrive(smem_u32(&c->acc2_empty[buf]));
-        }
+        const uint32_t blk = n & 1;
+        if (!mbar_wait_fast(smem_u32(&c->sempty[blk][q]), ((n >> 1) & 1) ^ 1, af, p.dev_status))
+          return;
+        const uint32_t dst = stg + (blk * 4 + q) * 4096 + lane * 128;
+        // piece XOR row: conflict-free 16-byte stores
 #pragma unroll
         for (int pc = 0; pc < 8; ++pc) {
           uint32_t ww[4];
@@ -926,7 +802,7 @@ __device__ void role_ep2_experts_tma(const Params& p, Ctl* c, uint32_t stg, uint
           for (int k = 0; k < 4; ++k)
             ww[k] = pack_bf16x2(__uint_as_float(v[8 * pc + 2 * k]),
                                 __uint_as_float(v[8 * pc + 2 * k + 1]));
-          st_shared_v4(row + hf * 128 + pc * 16, ww[0], ww[1], ww[2], ww[3]);
+          st_shared_v4(dst + ((pc ^ (lane & 7)) << 4), ww[0], ww[1], ww[2], ww[3]);
           if (nord != 0) {
 #pragma unroll
             for (int k = 0; k < 4; ++k) {
@@ -935,13 +811,69 @@ __device__ void role_ep2_experts_tma(const Params& p, Ctl* c, uint32_t stg, uint
             }
           }
         }
+        mbar_arrive(smem_u32(&c->sfull[blk][q]));
       }
-      fence_proxy_async();             // this thread's stores -> visible to its bulk reduce
-      if (orow) bulk_red_add_bf16(orow + nci * 128, row, 256);
-      bulk_commit();
     }
-    if (nord != 0 && tok >= 0)
-      p.norms[(long long)t.e * p.N + tok] = __float2bfloat16_rn(nord == 1 ? nacc : sqrtf(nacc));
+    if (ntok >= 0 && ntok < p.N)
+      p.norms[(long long)ne * p.N + ntok] = __float2bfloat16_rn(nord == 1 ? nacc : sqrtf(nacc));
+  }
+}
+
+// Writer warps: warp q adds the staged bf16 blocks of row quarter q to the output rows.
+// The global write path takes about 24 bytes per clock and SM for vector reds whichever
+// warps issue them, so it gets warps of its own.  A lane reads its rows back
+// row-contiguous (8 lanes cover one row's 128 bytes), so one red instruction touches 4
+// cache lines instead of 32.
+__device__ void role_writer(const Params& p, Ctl* c, uint32_t stg, int wt) {
+  volatile int* af = &c->abort_flag;
+  const Geo& g = p.g;
+  const int lane = wt & 31, q = wt >> 5;
+  const int rl = lane >> 3, pl = lane & 7;
+  const int halves = g.nd >> 6;
+  uint32_t n = 0;
+  int tile = blockIdx.x;
+  const int total = c->total_tiles, step = gridDim.x;
+  Tile t = {0, 0, 0};
+  long long tok = -1;
+  if (tile < total) {
+    t = tile_info<MODE_EXPERTS>(p, c, tile);
+    const int r = q * 32 + lane;
+    if (r < t.nrows) tok = p.token_idx[t.r0 + r];
+  }
+  for (; tile < total; tile += step) {
+    if (tok < 0 || tok >= p.N) tok = -1;      // out-of-range indices are reported by the producer
+    bf16* orow[8];
+#pragma unroll
+    for (int it = 0; it < 8; ++it) {
+      const long long tk = __shfl_sync(0xffffffffu, tok, it * 4 + rl);
+      orow[it] = tk < 0 ? nullptr : p.out + tk * p.d + pl * 8;
+    }
+    // rows of the next tile: the load is in flight while this tile's blocks are written
+    tok = -1;
+    if (tile + step < total) {
+      t = tile_info<MODE_EXPERTS>(p, c, tile + step);
+      const int r = q * 32 + lane;
+      if (r < t.nrows) tok = p.token_idx[t.r0 + r];
+    }
+    for (int nci = 0; nci < g.nc; ++nci) {
+      for (int hf = 0; hf < halves; ++hf, ++n) {
+        const uint32_t blk = n & 1;
+        const uint32_t src = stg + (blk * 4 + q) * 4096;
+        if (!mbar_wait_fast(smem_u32(&c->sfull[blk][q]), (n >> 1) & 1, af, p.dev_status)) return;
+        uint4 val[8];
+#pragma unroll
+        for (int it = 0; it < 8; ++it) {      // all shared loads first, then all reds
+          const int rr = it * 4 + rl;
+          val[it] = ld_shared_v4(src + rr * 128 + ((pl ^ (rr & 7)) << 4));
+        }
+        mbar_arrive(smem_u32(&c->sempty[blk][q]));   // block may be overwritten
+        const int col = nci * g.nd + hf * 64;
+#pragma unroll
+        for (int it = 0; it < 8; ++it)
+          if (orow[it])
+            red_add_bf16x8(orow[it] + col, val[it].x, val[it].y, val[it].z, val[it].w);
+      }
+    }
   }
 }
 
@@ -959,9 +891,9 @@ mlp_tiles_kernel(const Params p, const __grid_constant__ CUtensorMap tmx) {
   const uint32_t ringB = ringA + p.g.na * SLOT;
   const uint32_t ringB2 = ringB + p.g.nb * SLOT;
   const uint32_t hs = ringB2 + p.g.nb2 * SLOT;
-  const uint32_t stg = hs + p.g.hsl * SLOT;
+  const uint32_t stg = hs + p.g.kc2 * SLOT;
   Ctl* c = reinterpret_cast<Ctl*>(
-      aligned + (size_t)(p.g.na + p.g.nb + p.g.nb2 + p.g.hsl + p.g.stg) * SLOT);
+      aligned + (size_t)(p.g.na + p.g.nb + p.g.nb2 + p.g.kc2 + p.g.stg) * SLOT);
   const int tid = threadIdx.x, warp = tid >> 5;
   // Programmatic dependent launch: the next kernel of the stream may be scheduled as soon as
   // every CTA of this one has passed this point (its CTAs still wait for this grid to
@@ -986,12 +918,13 @@ mlp_tiles_kernel(const Params p, const __grid_constant__ CUtensorMap tmx) {
     mbar_init(smem_u32(&c->hs_empty), 1);
     for (int i = 0; i < 2; ++i) {
       mbar_init(smem_u32(&c->acc1_full[i]), 1);
-      // released by epilogue 1 (all its threads), or by GEMM2's commit when the hidden tile
-      // stays in the accumulator's columns
-      mbar_init(smem_u32(&c->acc1_empty[i]),
-                (MODE == MODE_EXPERTS && hidden_in_tmem(p.g)) ? 1 : EP1_THREADS);
+      mbar_init(smem_u32(&c->acc1_empty[i]), EP1_THREADS);
       mbar_init(smem_u32(&c->acc2_full[i]), 1);
       mbar_init(smem_u32(&c->acc2_empty[i]), 128);
+      for (int q = 0; q < 4; ++q) {
+        mbar_init(smem_u32(&c->sfull[i][q]), 32);
+        mbar_init(smem_u32(&c->sempty[i][q]), 32);
+      }
     }
     c->abort_flag = 0;
     c->wait_limit = (int)p.wait_limit;
@@ -1053,12 +986,7 @@ mlp_tiles_kernel(const Params p, const __grid_constant__ CUtensorMap tmx) {
   if (MODE == MODE_EXPERTS && warp < 4) {
     role_ep1_experts(p, c, hs, tmem, tid);
   } else if (MODE == MODE_EXPERTS && warp < 8) {
-    if (p.out_tma) {
-      role_ep2_experts_tma(p, c, stg, tmem, tid - 128);
-      bulk_wait_all();     // the reduces read shared memory: finish before the CTA ends
-    } else {
-      role_ep2_experts(p, c, tmem, tid - 128);
-    }
+    role_ep2_experts(p, c, stg, tmem, tid - 128);
   } else if (warp < 8) {
     role_epilogue_router(p, c, hs, stg, tmem, tid);
     bulk_wait_all();       // TMA row stores read shared memory: finish before the CTA ends
@@ -1071,13 +999,15 @@ mlp_tiles_kernel(const Params p, const __grid_constant__ CUtensorMap tmx) {
   } else if (warp == WARP_BULK) {
     if (elect_one()) role_bulk<MODE>(p, c, ringB, ringB2);
     __syncwarp();
-  } else if (warp < WARP_END) {
+  } else if (warp < WARP_WR0) {
     if (MODE == MODE_EXPERTS && !p.tma_gather) {
       role_producer_cpasync(p, c, ringA, tid - WARP_PROD0 * 32);
       cp_async_wait_all();
     } else if (warp == WARP_PROD0) {
       role_producer<MODE>(p, c, &tmx, ringA, tid & 31);
     }
+  } else if (MODE == MODE_EXPERTS) {
+    role_writer(p, c, stg, tid - WARP_WR0 * 32);
   }
 
   // A launch that gave up may still have copies and MMAs in flight that use this CTA's
@@ -1181,7 +1111,7 @@ static_assert(1024 + (size_t)SLOTS_TOTAL * SLOT + sizeof(Ctl) + 64 <= 232448,
               "shared-memory plan exceeds the 227 KB a CTA may use");
 
 size_t smem_bytes(const Geo& g) {
-  return 1024 + (size_t)(g.na + g.nb + g.nb2 + g.hsl + g.stg) * SLOT + sizeof(Ctl) + 64;
+  return 1024 + (size_t)(g.na + g.nb + g.nb2 + g.kc2 + g.stg) * SLOT + sizeof(Ctl) + 64;
 }
 
 template <int MODE>
@@ -1259,10 +1189,7 @@ int launch_experts_umma(const void* x, const int32_t* token_idx, const int32_t* 
   p.N = N;
   p.d = d;
   p.packed = (const uint8_t*)packed;
-  // selectable output path (test hook 3): only for the 128-column chunks of ungated experts
-  const bool out_tma = g_experts_kernel.load() == 3 && !glu && d % 128 == 0;
-  p.g = experts_geo(d, H, glu, out_tma);
-  p.out_tma = out_tma ? 1 : 0;
+  p.g = experts_geo(d, H, glu);
   p.token_idx = token_idx;
   p.offsets = offsets;
   p.E = E;
@@ -1279,7 +1206,7 @@ int launch_experts_umma(const void* x, const int32_t* token_idx, const int32_t* 
 }
 
 void umma_debug_select_experts_kernel(int which) {
-  g_experts_kernel.store(which == 2 || which == 3 ? which : 0);
+  g_experts_kernel.store(which == 2 ? 2 : 0);
 }
 
 void umma_debug_configure(int wait_limit_log2, int withhold_weight_tile) {

@@ -128,17 +128,6 @@ __device__ __forceinline__ void umma_bf16(uint32_t tmem_d, uint64_t adesc, uint6
       "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
       : "memory");
 }
-// The same product with the A operand in tensor memory: lane = row, each 32-bit column holds
-// two consecutive K elements (8 columns per K = 16 step).
-__device__ __forceinline__ void umma_bf16_ta(uint32_t tmem_d, uint32_t tmem_a, uint64_t bdesc,
-                                             uint32_t idesc, uint32_t accumulate) {
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "setp.ne.b32 p, %4, 0;\n\t"
-      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}" ::"r"(tmem_d),
-      "r"(tmem_a), "l"(bdesc), "r"(idesc), "r"(accumulate)
-      : "memory");
-}
 // mbarrier arrives once every MMA issued so far by this thread has completed
 __device__ __forceinline__ void umma_commit(uint32_t bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(
@@ -168,41 +157,6 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t* v) {
       : "r"(taddr)
       : "memory");
 }
-// 16 lanes x 64 columns in the accumulator-fragment layout: registers 4n..4n+3 hold column
-// block n (8 columns): v[4n], v[4n+1] = row lane/4, columns 8n + 2*(lane%4) + {0, 1};
-// v[4n+2], v[4n+3] = row lane/4 + 8, same columns.  The four lanes of a quad hold one row.
-__device__ __forceinline__ void tmem_ld_16x256b_x8(uint32_t taddr, uint32_t* v) {
-  asm volatile(
-      "tcgen05.ld.sync.aligned.16x256b.x8.b32 "
-      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
-      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
-      : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]),
-        "=r"(v[7]), "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]),
-        "=r"(v[14]), "=r"(v[15]), "=r"(v[16]), "=r"(v[17]), "=r"(v[18]), "=r"(v[19]),
-        "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]), "=r"(v[24]), "=r"(v[25]),
-        "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
-      : "r"(taddr)
-      : "memory");
-}
-// 4 x 4 transpose inside a quad of lanes (m = lane % 4): lane m gives w[n] (its two columns of
-// column block n) and receives t[j] = lane j's w[m]: the eight consecutive columns of block m.
-__device__ __forceinline__ void quad_transpose(const uint32_t* w, int m, uint32_t* t) {
-  const bool hi2 = (m & 2) != 0, hi1 = (m & 1) != 0;
-  // with lane m ^ 2: blocks {0,1} gather in lanes 0,1 and blocks {2,3} in lanes 2,3
-  const uint32_t x0 = __shfl_xor_sync(0xffffffffu, hi2 ? w[0] : w[2], 2);
-  const uint32_t x1 = __shfl_xor_sync(0xffffffffu, hi2 ? w[1] : w[3], 2);
-  // a[k]: block (m & 2) + k from the lower lane of the pair, b[k]: from the upper lane
-  const uint32_t a0 = hi2 ? x0 : w[0], a1 = hi2 ? x1 : w[1];
-  const uint32_t b0 = hi2 ? w[2] : x0, b1 = hi2 ? w[3] : x1;
-  // with lane m ^ 1: each lane keeps block m and passes the other one on
-  const uint32_t y0 = __shfl_xor_sync(0xffffffffu, hi1 ? a0 : a1, 1);
-  const uint32_t y1 = __shfl_xor_sync(0xffffffffu, hi1 ? b0 : b1, 1);
-  const uint32_t ka = hi1 ? a1 : a0, kb = hi1 ? b1 : b0;
-  t[0] = hi1 ? y0 : ka;
-  t[1] = hi1 ? ka : y0;
-  t[2] = hi1 ? y1 : kb;
-  t[3] = hi1 ? kb : y1;
-}
 __device__ __forceinline__ uint4 ld_shared_v4(uint32_t addr) {
   uint4 r;
   asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];"
@@ -220,31 +174,8 @@ __device__ __forceinline__ void bulk_s2g(void* gdst, uint32_t ssrc, uint32_t byt
 __device__ __forceinline__ void bulk_commit() {
   asm volatile("cp.async.bulk.commit_group;" ::: "memory");
 }
-// TMA reduce-add of one contiguous run of bf16 from shared memory into global memory (the L2
-// does the adds); completion is tracked per issuing thread in bulk groups.
-__device__ __forceinline__ void bulk_red_add_bf16(void* gdst, uint32_t ssrc, uint32_t bytes) {
-  asm volatile(
-      "cp.reduce.async.bulk.global.shared::cta.bulk_group.add.noftz.bf16 [%0], [%1], %2;" ::"l"(
-          gdst),
-      "r"(ssrc), "r"(bytes)
-      : "memory");
-}
-// all but the newest bulk group of this thread have finished READING shared memory
-__device__ __forceinline__ void bulk_wait_read_1() {
-  asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
-}
 __device__ __forceinline__ void bulk_wait_all() {
   asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
-}
-// 8 registers of this thread's lane into 8 consecutive columns
-__device__ __forceinline__ void tmem_st8(uint32_t taddr, const uint32_t* v) {
-  asm volatile(
-      "tcgen05.st.sync.aligned.32x32b.x8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};" ::"r"(taddr),
-      "r"(v[0]), "r"(v[1]), "r"(v[2]), "r"(v[3]), "r"(v[4]), "r"(v[5]), "r"(v[6]), "r"(v[7])
-      : "memory");
-}
-__device__ __forceinline__ void tmem_wait_st() {
-  asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
 }
 __device__ __forceinline__ void tmem_wait_ld() {
   asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");

@@ -258,10 +258,7 @@ int d2d_debug_configure(int wait_limit_log2, int withhold_weight_tile);
 /* Test hook, no upstream counterpart.  How the bf16 expert kernel brings the rows of an
  * expert's token list into shared memory: which = 0 or 1: 16-byte cp.async per row piece
  * (default, the faster one on B200); 2: TMA gathers (cp.async.bulk.tensor tile::gather4, four
- * rows per copy), kept so that the two can be compared on any workload; 3: default row path,
- * but the output adds of ungated experts leave the SM as TMA bulk reduces
- * (cp.reduce.async.bulk, 256 bytes per row and 128-column chunk, from staged rows) instead of
- * 16-byte reds from registers. */
+ * rows per copy), kept so that the two can be compared on any workload. */
 int d2d_debug_select_experts_kernel(int which);
 
 /* One-time re-layout of the weights into the shared-memory tile images the

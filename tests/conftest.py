@@ -25,8 +25,8 @@ def pytest_collection_modifyitems(config, items):
 @pytest.fixture(scope="session", autouse=True)
 def _experts_kernel_choice():
     """D2D_TEST_EXPERTS_KERNEL=2 runs the whole suite with the bf16 expert kernel gathering
-    its token rows by TMA (tile::gather4) instead of the default 16-byte cp.async, =3 with its
-    output adds issued as TMA bulk reduces, so that every parity case reaches every path."""
+    its token rows by TMA (tile::gather4) instead of the default 16-byte cp.async, so that
+    every parity case reaches both row paths."""
     import os
     which = int(os.environ.get("D2D_TEST_EXPERTS_KERNEL", "0"))
     if which:
