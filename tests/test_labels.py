@@ -137,3 +137,37 @@ def test_norm_capture_argument_checks():
     moe(x)
     assert saved["router"].shape == (c.B, c.S)
     handles[0].remove()
+
+
+def test_norm_hook_helper_on_host_modules():
+    """Host-side contract of the helper (no GPU): an ordinary module gets the upstream forward
+    hook, an experts stub switches the capture of its experts module on, remove() undoes both."""
+    import d2dmoe_b200 as D
+    torch.manual_seed(0)
+    model = torch.nn.Sequential(torch.nn.Linear(8, 6), torch.nn.ReLU())
+    saved, handles = D.add_save_output_norm_hook(model, ["0"], ord=2, dim=-1)
+    x = torch.randn(5, 8)
+    model(x)
+    assert torch.allclose(saved["0"], torch.linalg.vector_norm(model[0](x), ord=2, dim=-1))
+    handles[0].remove()
+    saved.clear()
+    model(x)
+    assert not saved
+
+    moe = D.MoeficationMoE("m", 16, 4, True, 8, torch.nn.ReLU, experts_class="custom_kernel")
+    name = "experts.output_activation_extraction_stub"
+    saved, handles = D.add_save_output_norm_hook(moe, [name], ord=1, dim=-1)
+    assert moe.experts._capture == ("output", 1)
+    with pytest.raises(NotImplementedError):      # one layer / ord per experts module at a time
+        D.add_save_output_norm_hook(moe, ["experts.intermediate_activation_extraction_stub"], 2)
+    handles[0].remove()
+    assert moe.experts._capture is None and not moe.experts._norm_sinks
+
+    glu = D.MoeficationMoE("g", 16, 4, False, 8, torch.nn.GELU, experts_class="execute_all",
+                           add_intermediate_gating=True)
+    saved, handles = D.add_save_output_norm_hook(glu, ["experts.layers.0"], ord=2, dim=-1)
+    assert glu.experts._capture == ("intermediate", 2)
+    handles[0].remove()
+    saved, handles = D.add_save_output_norm_hook(glu, ["experts.layers.1"], ord=2, dim=-1)
+    assert glu.experts._capture == ("output", 2)
+    handles[0].remove()
