@@ -511,7 +511,12 @@ class MoeficationMoE(MoELayer):
         outputs to that.  Returns ``(x + out, {name: (routing_tensor,)})``.  Falls back to the
         three separate steps when the layer is not in its fused form."""
         na = self._norm_args(norm)
+        # (affine parameters in another dtype than x -- mixed-precision norms -- keep the
+        # framework's own normalisation: the fused pass computes in the dtype of x)
         fused = (na is not None and x.is_cuda and self.forward_mode == "dynk_max"
+                 and na[1].dtype == x.dtype and (na[2] is None or na[2].dtype == x.dtype)
+                 and na[1].device == x.device
+                 and getattr(self.experts, "_capture", None) is None
                  and isinstance(self.router, MoeficationRouter) and self.router.fusable()
                  and not self.add_residual_connection
                  and (x.size(-1) * x.element_size()) % 16 == 0
@@ -530,8 +535,8 @@ class MoeficationMoE(MoELayer):
         out = torch.empty_like(x2d)
         rt = torch.empty(N, E, dtype=x.dtype, device=x.device)
         wsp = self._wsp.get(N, E, x.device)
-        ops.prenorm_init(x2d, gamma.detach().to(x.dtype),
-                         None if beta is None else beta.detach().to(x.dtype), eps, kind, xn, out,
+        ops.prenorm_init(x2d, gamma.detach().contiguous(),
+                         None if beta is None else beta.detach().contiguous(), eps, kind, xn, out,
                          last_bias=self.last_bias.view(-1) if self.bias else None,
                          gamma_offset=goff)
         ops.moe_forward(xn, self.router.layers[0].weight, self.router.layers[2].weight, self.tau,

@@ -308,3 +308,36 @@ def test_fused_gemma_decoder_forward_equals_the_unfused_layer():
     agree = gd[c.name][0].eq(gd2[c.name][0]).all(-1)
     assert agree.float().mean().item() >= 0.97
     assert O.rel_err(out[agree].float().cpu(), ref[agree].float().cpu()) <= TOL[c.dtype]
+
+
+@pytest.mark.gpu
+def test_forward_block_keeps_the_framework_norm_for_mixed_precision_and_capture():
+    c, kind, eps = CASES[0]
+    g, t = load(c, kind)
+    moe, norm = _module(c, t), _norm(c, t, kind, eps)
+    x = t["x"].cuda()
+    fused, _ = moe.forward_block(x, norm)
+    # parameters of the norm in another dtype than x: three separate steps, same result class
+    norm32 = torch.nn.LayerNorm(c.d, eps=eps).cuda()
+    with torch.no_grad():
+        norm32.weight.copy_(t["gamma"].float())
+        norm32.bias.copy_(t["beta"].float())
+
+    class Mixed(torch.nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.weight, self.bias, self.eps = norm32.weight, norm32.bias, eps
+            self.normalized_shape = (c.d,)
+
+        def forward(self, v):
+            return norm32(v.float()).to(v.dtype)
+    mixed = Mixed()
+    assert moe._norm_args(mixed) is None           # not an nn.LayerNorm: ordinary route
+    out, _ = moe.forward_block(x, mixed)
+    assert O.rel_err(out.float().cpu(), fused.float().cpu()) <= TOL[c.dtype]
+    # while the experts capture labels the block runs unfused and the capture still happens
+    moe.experts.capture_norms("output", 2)
+    out3, _ = moe.forward_block(x, norm)
+    assert moe.experts.captured_norms is not None
+    assert O.rel_err(out3.float().cpu(), fused.float().cpu()) <= TOL[c.dtype]
+    moe.experts.capture_norms(None)
