@@ -160,6 +160,7 @@ struct Ctl {
   int total_tiles;
   alignas(16) float bias_s[128];   // (read as float4) b1 of the current tile's expert
   int total_full;                  // experts: number of full 128-row tiles (they come first)
+  int dense_tpe;                   // experts: > 0 = every expert lists all N tokens: tiles per expert
   uint8_t pidx[MAX_E];             // experts: expert of the k-th partial (tail) tile
   union {
     int tstart[MAX_E + 1];  // experts: first FULL tile of each expert
@@ -179,6 +180,17 @@ __device__ __forceinline__ Tile tile_info(const Params& p, const Ctl* c, int til
     t.r0 = tile * TILE_M;
     t.nrows = (int)min((long long)TILE_M, p.N - (long long)t.r0);
   } else {
+    // Every expert runs on every token (mode 'all' upstream: router training, label capture):
+    // token-tile-major order, the E tiles of one 128-token window next to each other, so that
+    // the window's rows of x and out are read from and added to in L2 instead of being
+    // streamed through DRAM once per expert.
+    if (c->dense_tpe > 0) {
+      const int j = tile / p.E;
+      t.e = tile - j * p.E;
+      t.r0 = p.offsets[t.e] + j * TILE_M;
+      t.nrows = (int)min((long long)TILE_M, p.N - (long long)j * TILE_M);
+      return t;
+    }
     // Tile order: every full 128-row tile (expert-major), then the experts' partial tail
     // tiles.  With the static round-robin over CTAs the last, incomplete round of a launch
     // is then made of the cheap partial tiles.
@@ -938,6 +950,7 @@ mlp_tiles_kernel(const Params p, const __grid_constant__ CUtensorMap tmx) {
     // scans across the warp of the full-tile counts and of the "has a partial tile" flags
     const int lane = tid & 31;
     int off[5], nt[4], pt[4], sum = 0, psum = 0;
+    bool all_n = true;               // every expert of this lane lists exactly N tokens
 #pragma unroll
     for (int q = 0; q < 5; ++q) {
       const int e = 4 * lane + q;
@@ -947,6 +960,7 @@ mlp_tiles_kernel(const Params p, const __grid_constant__ CUtensorMap tmx) {
     for (int q = 0; q < 4; ++q) {
       const int e = 4 * lane + q;
       const int n = e < p.E ? off[q + 1] - off[q] : 0;
+      if (e < p.E && n != p.N) all_n = false;
       if (e < p.E && (n < 0 || off[q + 1] > p.N * (long long)p.E))
         report(p.dev_status, D2D_ERR_INDEX_RANGE);
       nt[q] = n > 0 ? n / TILE_M : 0;
@@ -972,9 +986,11 @@ mlp_tiles_kernel(const Params p, const __grid_constant__ CUtensorMap tmx) {
       run += nt[q];
       prun += pt[q];
     }
+    const bool dense = __all_sync(0xffffffffu, all_n) && p.N > 0 && p.E > 1;
     if (lane == 31) {
       c->total_full = incl;
       c->total_tiles = incl + pincl;
+      c->dense_tpe = dense ? (int)((p.N + TILE_M - 1) / TILE_M) : 0;    // same tile count either way
     }
   }
   if (warp == WARP_MMA1) tmem_alloc(smem_u32(&c->tmem_base), 512);
