@@ -341,3 +341,32 @@ def test_forward_block_keeps_the_framework_norm_for_mixed_precision_and_capture(
     assert moe.experts.captured_norms is not None
     assert O.rel_err(out3.float().cpu(), fused.float().cpu()) <= TOL[c.dtype]
     moe.experts.capture_norms(None)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16], ids=["fp32", "bf16"])
+@pytest.mark.parametrize("kind", ["layer", "rms"])
+def test_prenorm_init_shapes_against_the_oracle(dtype, kind):
+    """Row lengths from one vector per row to the longest supported (every register-footprint
+    variant of the kernel), ragged row counts, with and without the initial-value output."""
+    from d2dmoe_b200 import ops
+    es = 4 if dtype == torch.float32 else 2
+    g = torch.Generator().manual_seed(40)
+    tol = 2e-6 if dtype == torch.float32 else 2.0 ** -8
+    for d in (16 // es, 40, 64, 200, 768, 1024, 2048, 8192 // es):
+        for n in (1, 33, 257):
+            x = (torch.randn(n, d, generator=g) * 1.7 + 0.4).to(dtype)
+            gamma = (1.0 + 0.1 * torch.randn(d, generator=g)).to(dtype)
+            beta = (0.1 * torch.randn(d, generator=g)).to(dtype) if kind == "layer" else None
+            lb = (0.05 * torch.randn(d, generator=g)).to(dtype)
+            goff = 1.0 if kind == "rms" else 0.0
+            ref = O.prenorm(x, gamma, beta, 1e-6, kind, goff).float()
+            xd = x.cuda()
+            xn = torch.full_like(xd, float("nan"))
+            init = torch.full_like(xd, float("nan"))
+            ops.prenorm_init(xd, gamma.cuda(), None if beta is None else beta.cuda(), 1e-6,
+                             ops.NORM_LAYER if kind == "layer" else ops.NORM_RMS, xn, init,
+                             last_bias=lb.cuda(), gamma_offset=goff)
+            assert O.rel_err(xn.cpu().float(), ref) <= tol, (d, n)
+            want = (x.float() + lb.float()).to(dtype).float()
+            assert torch.equal(init.cpu().float(), want), (d, n)
