@@ -64,3 +64,28 @@ def test_misaligned_buffers_are_rejected_before_any_launch():
                              None, 0, 1, a(base), 256, 768, 24, 128, 0, 1, None, None)
     assert rc == 1
     assert lib.d2d_debug_configure(0, 0) == 0
+
+
+def test_argument_checks_of_the_block_level_and_label_entry_points():
+    """d2d_prenorm_init and d2d_experts_ffn_norms refuse bad arguments on the host before any
+    CUDA call (the pointers below are never dereferenced)."""
+    import ctypes as C
+    from d2dmoe_b200 import _capi
+    lib = _capi.lib
+    a = lambda v: C.c_void_p(v)                                             # noqa: E731
+    base = 0x7f0000000000
+    # labels: ord must be 1 or 2, the layer 1 or 2, the norms buffer present
+    args = lambda norms, layer, ordv: (a(base), a(base), a(base), a(base), None, None, a(base),  # noqa: E731
+                                       None, None, 0, 1, a(base), norms, layer, ordv,
+                                       256, 768, 24, 128, 0, 1, None, None)
+    assert lib.d2d_experts_ffn_norms(*args(a(base), 2, 3)) == 1
+    assert lib.d2d_experts_ffn_norms(*args(a(base), 3, 2)) == 1
+    assert lib.d2d_experts_ffn_norms(*args(a(base), 0, 2)) == 1
+    assert lib.d2d_experts_ffn_norms(*args(None, 2, 2)) == 1
+    # pre-norm: rows longer than 8 KB or not a multiple of 16 bytes are unsupported, pointers
+    # must be 16-byte aligned
+    pn = lambda x, d: lib.d2d_prenorm_init(x, a(base), None, 1e-6, 0, 0.0, None, a(base),   # noqa: E731
+                                           a(base), 16, d, 1, None)
+    assert pn(a(base), 8200) == 2                       # D2D_ERR_UNSUPPORTED
+    assert pn(a(base), 100) == 2
+    assert pn(a(base + 2), 768) == 1                    # D2D_ERR_BAD_ARG
